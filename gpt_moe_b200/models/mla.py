@@ -1,0 +1,194 @@
+"""Multi-head latent attention (MLA).
+
+One joint low-rank KV projection per token: `kv_down_proj` emits a latent of `kv_rank` plus one
+shared RoPE key of `rope_dim`; `kv_up_proj` expands the normalised latent into per-head content
+keys and values.  Queries are `content_dim + rope_dim` wide (optionally through a low-rank
+`q_down_proj`/`q_norm`).  QK-norm is taken over the concatenated [content | rope] key and query;
+softmax scale is (content+rope)^-0.5.  Parameter names and semantics follow the reference's MLA
+experiment (`experiments/073-mla-current-kv768.patch:240-384`).
+
+For generation the module keeps a latent cache (`MLACache`: latent, rope key and per-head key
+gain per token) and decodes with absorbed weights: scores are taken directly against the latent
+(`q_content @ W_k` folded into the query) and the context is produced in latent space and
+expanded by `W_v` afterwards (same patch, lines 394-460).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch import Tensor
+
+from ..ops import api
+from ..ops import reference as ref
+from .attention import AttentionContext
+from .linear import Linear
+from .rotary import Rotary
+
+
+@dataclass
+class MLACache:
+    latent: Tensor      # [B, S, kv_rank]
+    rope: Tensor        # [B, S, rope_dim]
+    key_gain: Tensor    # [B, S, n_kv_heads]  (QK-norm gain * clamped k_scale of the expanded key)
+    length: int = 0
+
+
+class MLAttention(nn.Module):
+    def __init__(self, gpt_config, training_config, layer_idx: int = 0) -> None:
+        super().__init__()
+        self.n_heads = gpt_config.n_heads
+        self.is_full_attention = layer_idx in gpt_config.full_attention_layers
+        self.n_kv_heads = gpt_config.global_n_kv_heads if self.is_full_attention else gpt_config.n_kv_heads
+        assert self.n_heads % self.n_kv_heads == 0
+        self.group = self.n_heads // self.n_kv_heads
+        self.q_rank, self.kv_rank = gpt_config.mla_q_rank, gpt_config.mla_kv_rank
+        self.content_dim, self.rope_dim = gpt_config.mla_qk_content_dim, gpt_config.mla_qk_rope_dim
+        self.value_dim = gpt_config.mla_value_dim
+        self.head_size = self.content_dim + self.rope_dim
+        self.attn_dim = self.n_heads * self.value_dim
+        if self.q_rank < 0 or min(self.kv_rank, self.content_dim, self.value_dim) <= 0 or self.rope_dim < 0 or self.rope_dim % 2:
+            raise ValueError("MLA needs q_rank >= 0, positive kv_rank/content/value dims and an even rope_dim >= 0")
+        uses_rope = gpt_config.pos_encoding_type.lower() == "rope"
+        if uses_rope != bool(self.rope_dim):
+            raise ValueError("MLA: mla_qk_rope_dim must be > 0 with RoPE and 0 without")
+        h = gpt_config.hidden_size
+        if self.q_rank:
+            self.q_down_proj = Linear(h, self.q_rank, role="q_proj", bias=gpt_config.use_bias)
+            self.q_norm = nn.RMSNorm(self.q_rank, eps=gpt_config.mla_norm_eps)
+        self.q_proj = Linear(self.q_rank or h, self.n_heads * self.head_size, role="q_proj", bias=gpt_config.use_bias)
+        self.kv_down_proj = Linear(h, self.kv_rank + self.rope_dim, role="k_proj", bias=gpt_config.use_bias)
+        self.kv_norm = nn.RMSNorm(self.kv_rank, eps=gpt_config.mla_norm_eps)
+        self.kv_up_proj = Linear(self.kv_rank, self.n_kv_heads * (self.content_dim + self.value_dim),
+                                 role="k_proj", bias=gpt_config.use_bias)
+        self.out_proj = Linear(self.attn_dim, h, role="out_proj", bias=gpt_config.use_bias)
+        theta = gpt_config.global_rope_theta if self.is_full_attention else gpt_config.rope_base_theta
+        self.rotary = Rotary(self.rope_dim, theta, training_config.max_seq_len) if self.rope_dim else None
+        self.use_qk_norm = gpt_config.use_qk_norm
+        self.qk_norm_type = gpt_config.qk_norm_type
+        self.qk_scale_min, self.qk_scale_max, self.qk_eps = gpt_config.qk_scale_min, gpt_config.qk_scale_max, gpt_config.qk_eps
+        if self.use_qk_norm:
+            self.q_scale = nn.Parameter(torch.full((1, self.n_heads, 1, 1), gpt_config.qk_scale_init))
+            self.k_scale = nn.Parameter(torch.full((1, self.n_kv_heads, 1, 1), gpt_config.qk_scale_init))
+        self.is_causal = gpt_config.is_causal
+        self.use_flex_attention = gpt_config.use_flex_attention
+        self.softmax_scale = self.head_size ** -0.5
+        self.softcap = gpt_config.attn_logit_softcap if gpt_config.use_attn_logit_softcapping else 0.0
+        self.tanh_backend = gpt_config.tanh_backend
+
+    # ---- projections ---------------------------------------------------------------------------
+    def _project(self, x: Tensor, start_pos: int = 0) -> Tuple[Tensor, Tensor, Tensor]:
+        """-> query [B,T,H,content+rope] (rope part rotated), normalised latent [B,T,kv_rank], rotated rope key [B,T,1,rope]."""
+        b, t, _ = x.shape
+        query = x
+        if self.q_rank:
+            query = api.rms_norm(self.q_down_proj(query), self.q_norm.weight, self.q_norm.eps)
+        query = self.q_proj(query).view(b, t, self.n_heads, self.head_size)
+        compressed = self.kv_down_proj(x)
+        latent, rope = compressed.split((self.kv_rank, self.rope_dim), dim=-1)
+        latent = api.rms_norm(latent.contiguous(), self.kv_norm.weight, self.kv_norm.eps).to(compressed.dtype)
+        rope = rope.reshape(b, t, 1, self.rope_dim)
+        if self.rotary is not None:
+            cos = self.rotary.cos_cached[start_pos:start_pos + t]
+            sin = self.rotary.sin_cached[start_pos:start_pos + t]
+            q_content, q_rope = query.split((self.content_dim, self.rope_dim), dim=-1)
+            q_rope = ref.apply_rope(q_rope, cos, sin)
+            rope = ref.apply_rope(rope, cos, sin)
+            query = torch.cat((q_content, q_rope), dim=-1)
+        return query, latent, rope
+
+    def _gain(self, x: Tensor, scale: Tensor) -> Tensor:
+        sq = x.pow(2)
+        stat = sq.mean(dim=-1, keepdim=True) if self.qk_norm_type == "rms" else sq.sum(dim=-1, keepdim=True)
+        gain = torch.rsqrt(stat + self.qk_eps).to(x.dtype)
+        return gain * scale.clamp(self.qk_scale_min, self.qk_scale_max).reshape(1, 1, -1, 1).to(x.dtype)
+
+    def _expand(self, query: Tensor, latent: Tensor, rope: Tensor, ctx: AttentionContext) -> Tuple[Tensor, Tensor]:
+        b, t = latent.shape[:2]
+        kv = self.kv_up_proj(latent).view(b, t, self.n_kv_heads, self.content_dim + self.value_dim)
+        k_content, value = kv.split((self.content_dim, self.value_dim), dim=-1)
+        key = torch.cat((k_content, rope.expand(-1, -1, self.n_kv_heads, -1)), dim=-1)
+        if self.use_qk_norm:
+            query = query * self._gain(query, self.q_scale)
+            key_gain = self._gain(key, self.k_scale)
+            key = key * key_gain
+        else:
+            key_gain = torch.ones_like(key[..., :1])
+        out = api.attention(
+            query, key, value.contiguous(), causal=self.is_causal,
+            window=None if (self.is_full_attention or not self.use_flex_attention) else ctx.window,
+            scale=self.softmax_scale, softcap_value=self.softcap, tanh_backend=self.tanh_backend,
+            attn_mask=ctx.attn_mask, document_ids=ctx.document_ids)
+        return out, key_gain
+
+    def forward(self, x: Tensor, ctx: AttentionContext) -> Tensor:
+        b, t, _ = x.shape
+        query, latent, rope = self._project(x)
+        out, _ = self._expand(query, latent, rope, ctx)
+        return self.out_proj(out.reshape(b, t, self.attn_dim))
+
+    # ---- cached generation ---------------------------------------------------------------------
+    def allocate_cache(self, batch_size: int, max_seq_len: int, *, device, dtype) -> MLACache:
+        return MLACache(torch.zeros(batch_size, max_seq_len, self.kv_rank, device=device, dtype=dtype),
+                        torch.zeros(batch_size, max_seq_len, self.rope_dim, device=device, dtype=dtype),
+                        torch.zeros(batch_size, max_seq_len, self.n_kv_heads, device=device, dtype=dtype))
+
+    @torch.no_grad()
+    def forward_cached(self, x: Tensor, cache: MLACache, window: Optional[int] = None) -> Tensor:
+        """Append x's tokens to the cache and attend over the whole cache with absorbed weights."""
+        if self.training or not self.is_causal:
+            raise ValueError("MLA cached forward requires causal attention in eval mode")
+        b, t, _ = x.shape
+        start, end = cache.length, cache.length + t
+        if end > cache.latent.size(1) or b != cache.latent.size(0):
+            raise ValueError("MLA cache capacity or batch size mismatch")
+        query, latent, rope = self._project(x, start)
+        cache.latent[:, start:end] = latent
+        cache.rope[:, start:end] = rope[:, :, 0]
+        w = self.kv_up_proj.weight.view(self.n_kv_heads, self.content_dim + self.value_dim, self.kv_rank)
+        w_k, w_v = w[:, :self.content_dim].float(), w[:, self.content_dim:].float()
+        # key gain of the new tokens needs their expanded keys (norm is over [content | rope])
+        k_content = torch.einsum("btr,hdr->bthd", latent.float(), w_k)
+        key = torch.cat((k_content, rope.float().expand(-1, -1, self.n_kv_heads, -1)), dim=-1)
+        if self.use_qk_norm:
+            cache.key_gain[:, start:end] = self._gain(key, self.k_scale)[..., 0].to(cache.key_gain.dtype)
+            query = query * self._gain(query, self.q_scale)
+        else:
+            cache.key_gain[:, start:end] = 1.0
+        cache.length = end
+        q_content, q_rope = query.float().split((self.content_dim, self.rope_dim), dim=-1)
+        q_content = q_content.view(b, t, self.n_kv_heads, self.group, self.content_dim)
+        q_latent = torch.einsum("bthgd,hdr->bthgr", q_content, w_k).reshape(b, t, self.n_heads, self.kv_rank)
+        context = api_mla_decode(q_latent, q_rope, cache.latent[:, :end], cache.rope[:, :end], cache.key_gain[:, :end],
+                                 start, self.softmax_scale, self.softcap, self.tanh_backend,
+                                 None if (self.is_full_attention or window is None) else int(window))
+        context = context.view(b, t, self.n_kv_heads, self.group, self.kv_rank)
+        out = torch.einsum("bthgr,hdr->bthgd", context, w_v).reshape(b, t, self.attn_dim)
+        return self.out_proj(out.to(x.dtype))
+
+
+def api_mla_decode(q_latent: Tensor, q_rope: Tensor, latent: Tensor, rope: Tensor, key_gain: Tensor,
+                   start_pos: int, scale: float, softcap_value: float, tanh_backend: str,
+                   window: Optional[int]) -> Tensor:
+    """Absorbed-weight MLA decode: score = (q_latent . latent + q_rope . rope) * key_gain * scale over
+    the cache, causal (query i sits at absolute position start_pos+i), optional window/softcap;
+    returns the context in latent space [B,T,H,kv_rank] (fp32).
+    Reference kernel: `experiments/073-mla-current-kv768.patch:456-673`."""
+    b, t, h, r = q_latent.shape
+    s_len = latent.shape[1]
+    hkv = key_gain.shape[-1]
+    g = h // hkv
+    lat, rp = latent.float(), rope.float()
+    score = torch.einsum("bthr,bsr->bhts", q_latent.float(), lat) + torch.einsum("bthd,bsd->bhts", q_rope.float(), rp)
+    gain = key_gain.float().permute(0, 2, 1).repeat_interleave(g, dim=1)[:, :, None, :]
+    score = ref.softcap(score * gain * scale, softcap_value, tanh_backend)
+    qpos = torch.arange(start_pos, start_pos + t, device=score.device)[:, None]
+    kpos = torch.arange(s_len, device=score.device)[None, :]
+    keep = kpos <= qpos
+    if window is not None:
+        keep &= (qpos - kpos) <= window
+    score = score.masked_fill(~keep, float("-inf"))
+    return torch.einsum("bhts,bsr->bthr", torch.softmax(score, dim=-1), lat)
