@@ -27,7 +27,7 @@ def _common_training(batch: int, seq: int, window: int, precision: str) -> Train
         gpu_batch_size_train=batch, gpu_batch_size_val=batch, seq_len_train=seq, seq_len_val=seq,
         total_tokens_per_step_train=0, use_synthetic_data=True,
         linear_config=default_linear_config(precision), export_full_model_at_end=False,
-        kernel_warmup_train_steps=1,
+        kernel_warmup_train_steps=1, val_tokens=2 * batch * seq,
     )
     _fixed_schedules(tc, batch, window)
     return tc

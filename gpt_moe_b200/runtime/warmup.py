@@ -1,0 +1,62 @@
+"""Kernel warm-up before the timed loop.
+
+The reference runs real train steps on random tokens for every scheduled batch size plus one
+validation forward so that compilation and autotuning happen before step 0, then restores model,
+optimizer and RNG state (`runtime/warmup.py:12-269`).  Nothing is compiled or autotuned here, but
+first launches still pay for CUDA module loading, allocator growth and (on the fused path)
+symmetric-memory rendezvous, so the same procedure is kept: warm up, then restore exactly.
+"""
+from __future__ import annotations
+
+import copy
+import time
+
+import torch
+
+from ..parallel import dist_utils as du
+
+
+def kernel_warmup(run, num_train_steps: int = 2) -> float:
+    trainer = run.trainer
+    if num_train_steps <= 0 or run.parallel_mode == "pp":
+        return 0.0
+    cfg = run.training_config
+    t0 = time.time()
+    model_state = copy.deepcopy(run.raw_gpt_model.state_dict())
+    opt_state = {k: copy.deepcopy(o.state_dict()) for k, o in run.optimizers.items()}
+    cpu_rng = torch.get_rng_state()
+    cuda_rng = torch.cuda.get_rng_state() if trainer.device_type == "cuda" else None
+    saved = (trainer.train_tokens_processed, trainer.schedule_state())
+    vocab = trainer.gpt_config.vocab_size
+    for batch_size in sorted(set(cfg.batch_size_schedule_values)):
+        trainer.current_batch_size = batch_size
+        for _ in range(num_train_steps):
+            batches = []
+            for _ in range(cfg.grad_accum_mini_steps):
+                ids = torch.randint(0, vocab, (batch_size, cfg.seq_len_train + 1))
+                batches.append((ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), None))
+            trainer.train_step(batches, read_losses=False)
+    run.gpt_model.eval()
+    with torch.no_grad(), run.ctx:
+        ids = torch.randint(0, vocab, (cfg.gpu_batch_size_val, cfg.seq_len_val + 1))
+        run.gpt_model(trainer._to_device(ids[:, :-1].contiguous()), trainer._to_device(ids[:, 1:].contiguous()))
+    # restore
+    run.raw_gpt_model.load_state_dict(model_state)
+    for k, o in run.optimizers.items():
+        o.load_state_dict(opt_state[k])
+    if hasattr(trainer.engine, "refresh_from_parameters"):
+        trainer.engine.refresh_from_parameters()
+    torch.set_rng_state(cpu_rng)
+    if cuda_rng is not None:
+        torch.cuda.set_rng_state(cuda_rng)
+    trainer.train_tokens_processed = saved[0]
+    for key, value in saved[1].items():
+        setattr(trainer, key, value)
+    run.raw_gpt_model.sliding_window_size.fill_(trainer.current_window_size)
+    du.barrier()
+    elapsed = du.max_over_ranks(time.time() - t0, run.device)
+    if run.master_process:
+        message = f"kernel warmup: {elapsed:.2f} s (max over ranks)"
+        print(message)
+        run.log_buffer.append(message)
+    return elapsed
