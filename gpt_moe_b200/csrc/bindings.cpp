@@ -1,0 +1,152 @@
+// Python bindings (pybind11 through torch's extension headers).  Kernels live in .cu files that do not
+// include torch headers; this file converts tensors to raw pointers, builds TMA descriptors and launches.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include <cstring>
+#include <list>
+#include <unordered_map>
+
+#include "gemm/gemm.h"
+#include "kernels.h"
+
+namespace {
+
+#define GM_CHECK(cond, msg) TORCH_CHECK(cond, "gpt_moe_b200: ", msg)
+
+cudaStream_t current_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int sm_count() {
+    static int sms = 0;
+    if (sms == 0) sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    return sms;
+}
+
+// One status word per device: kernels write a non-zero code when a bounded wait gives up.
+torch::Tensor& status_tensor(int device) {
+    static std::unordered_map<int, torch::Tensor> words;
+    auto it = words.find(device);
+    if (it == words.end()) {
+        it = words.emplace(device, torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA, device))).first;
+    }
+    return it->second;
+}
+
+int64_t read_status() {
+    int device = at::cuda::current_device();
+    return status_tensor(device).item<int32_t>();
+}
+void reset_status() { status_tensor(at::cuda::current_device()).zero_(); }
+
+// ---- tensor map cache -----------------------------------------------------------------------------
+struct MapKey {
+    const void* ptr; uint64_t cols, rows, batch, rs, bs; uint32_t bc, br; int eb, sw;
+    bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+        size_t h = 1469598103934665603ull;
+        for (size_t i = 0; i < sizeof(MapKey) / 8; ++i) h = (h ^ w[i]) * 1099511628211ull;
+        return h;
+    }
+};
+const CUtensorMap& cached_map(const void* ptr, int elem_bytes, uint64_t cols, uint64_t rows, uint64_t batch,
+                              uint64_t row_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_cols, uint32_t box_rows, int swizzle) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    MapKey key;
+    std::memset(&key, 0, sizeof(key));
+    key.ptr = ptr; key.cols = cols; key.rows = rows; key.batch = batch; key.rs = row_stride_bytes; key.bs = batch_stride_bytes;
+    key.bc = box_cols; key.br = box_rows; key.eb = elem_bytes; key.sw = swizzle;
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    if (cache.size() > 8192) cache.clear();
+    CUtensorMap map;
+    GM_CHECK(reinterpret_cast<uintptr_t>(ptr) % 16 == 0, "TMA base address must be 16-byte aligned");
+    GM_CHECK(row_stride_bytes % 16 == 0 && (batch == 1 || batch_stride_bytes % 16 == 0), "TMA strides must be multiples of 16 bytes");
+    GM_CHECK(gm::make_tensor_map(&map, ptr, elem_bytes, cols, rows, batch, row_stride_bytes, batch_stride_bytes, box_cols, box_rows, swizzle),
+             "cuTensorMapEncodeTiled failed");
+    return cache.emplace(key, map).first->second;
+}
+
+// operand map for the bf16 GEMM: `t` is [rows, cols] or [batch, rows, cols] with cols contiguous
+const CUtensorMap& operand_map(const torch::Tensor& t, bool mn_major, int tile_rows_k_major) {
+    GM_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16, "GEMM operands must be CUDA bf16 tensors");
+    GM_CHECK(t.dim() == 2 || t.dim() == 3, "GEMM operands must be 2-D or 3-D");
+    GM_CHECK(t.stride(-1) == 1, "GEMM operands must have a contiguous last dimension");
+    const uint64_t batch = t.dim() == 3 ? t.size(0) : 1;
+    const uint64_t rows = t.size(-2), cols = t.size(-1);
+    const uint64_t rs = t.stride(-2) * 2, bs = t.dim() == 3 ? t.stride(0) * 2 : 0;
+    return cached_map(t.data_ptr(), 2, cols, rows, batch, rs, bs, 64, mn_major ? 64 : tile_rows_k_major, 128);
+}
+
+// D[.., M, N] = alpha * op(A) op(B)^T + beta * C, optionally accumulated into an fp32 D.
+//   a_mn = false: a is [.., M, K];  a_mn = true: a is [.., K, M]   (same for b with N)
+//   mode 1 (grouped M): a [rows, K], b [E, N, K] or [E, K, N], d [rows, N]; tile_expert/num_m_tiles on device
+//   mode 2 (grouped K): a [rows, M] (a_mn), b [rows, N] (b_mn), d [E, M, N]; seg_ends on device
+void gemm_bf16(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& d, bool a_mn, bool b_mn, double alpha,
+               double beta, const c10::optional<torch::Tensor>& c, bool accumulate, int64_t mode,
+               const c10::optional<torch::Tensor>& tile_expert, const c10::optional<torch::Tensor>& num_m_tiles,
+               const c10::optional<torch::Tensor>& seg_ends) {
+    c10::cuda::CUDAGuard guard(a.device());
+    gm::GemmParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.mode = static_cast<int>(mode);
+    GM_CHECK(d.is_cuda() && d.stride(-1) == 1, "GEMM output must be a CUDA tensor with a contiguous last dimension");
+    GM_CHECK(d.scalar_type() == torch::kBFloat16 || d.scalar_type() == torch::kFloat32, "GEMM output must be bf16 or fp32");
+    p.M = d.size(-2);
+    p.N = d.size(-1);
+    p.batch = d.dim() == 3 ? d.size(0) : 1;
+    if (mode == gm::GEMM_GROUPED_K) {
+        GM_CHECK(a_mn && b_mn, "grouped-K GEMM reads both operands MN-major");
+        GM_CHECK(seg_ends.has_value() && seg_ends->scalar_type() == torch::kInt32, "grouped-K GEMM needs int32 seg_ends");
+        GM_CHECK(a.size(-1) == p.M && b.size(-1) == p.N && a.size(0) == b.size(0), "grouped-K operand shapes");
+        p.K = 0;
+        p.seg_ends = seg_ends->data_ptr<int>();
+    } else {
+        p.K = a_mn ? a.size(-2) : a.size(-1);
+        GM_CHECK((b_mn ? b.size(-2) : b.size(-1)) == p.K, "GEMM contraction sizes differ");
+        GM_CHECK((b_mn ? b.size(-1) : b.size(-2)) == p.N, "GEMM: B does not match the output width");
+        if (mode == gm::GEMM_GROUPED_M) {
+            GM_CHECK(tile_expert.has_value() && num_m_tiles.has_value(), "grouped-M GEMM needs tile_expert and num_m_tiles");
+            GM_CHECK(!a_mn && a.dim() == 2 && b.dim() == 3 && d.dim() == 2, "grouped-M operand ranks");
+            p.tile_expert = tile_expert->data_ptr<int>();
+            p.num_m_tiles = num_m_tiles->data_ptr<int>();
+        } else {
+            GM_CHECK((a_mn ? a.size(-1) : a.size(-2)) == p.M, "GEMM: A does not match the output height");
+        }
+    }
+    p.D = d.data_ptr();
+    p.ldd = d.stride(-2);
+    p.d_batch_stride = d.dim() == 3 ? d.stride(0) : 0;
+    p.out_fp32 = d.scalar_type() == torch::kFloat32;
+    p.accumulate = accumulate;
+    GM_CHECK(!accumulate || p.out_fp32, "accumulation needs an fp32 output");
+    p.alpha = static_cast<float>(alpha);
+    p.beta = static_cast<float>(beta);
+    if (c.has_value()) {
+        GM_CHECK(c->scalar_type() == torch::kBFloat16 && c->stride(-1) == 1, "C must be bf16 with a contiguous last dimension");
+        p.C = c->data_ptr();
+        p.ldc = c->stride(-2);
+        p.c_batch_stride = c->dim() == 3 ? c->stride(0) : 0;
+    }
+    GM_CHECK(p.ldd % 8 == 0 && (p.C == nullptr || p.ldc % 8 == 0), "output row pitch must be a multiple of 8 elements");
+    p.status = status_tensor(a.device().index()).data_ptr<int>();
+    const CUtensorMap& ta = operand_map(a, a_mn, 128);
+    const CUtensorMap& tb = operand_map(b, b_mn, 256);
+    cudaError_t e = gm::launch_gemm_bf16(ta, tb, p, a_mn, b_mn, sm_count(), current_stream());
+    GM_CHECK(e == cudaSuccess, cudaGetErrorString(e));
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("read_status", &read_status, "status word of the current device (0 = no bounded wait gave up)");
+    m.def("reset_status", &reset_status);
+    m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("a_mn") = false, py::arg("b_mn") = false,
+          py::arg("alpha") = 1.0, py::arg("beta") = 0.0, py::arg("c") = py::none(), py::arg("accumulate") = false,
+          py::arg("mode") = 0, py::arg("tile_expert") = py::none(), py::arg("num_m_tiles") = py::none(),
+          py::arg("seg_ends") = py::none());
+    gm::register_kernels(m);
+}

@@ -1,0 +1,330 @@
+// Memory-bound row kernels: RMSNorm (forward / backward, optionally fused with the residual update) and
+// RoPE + per-head QK-norm (forward / backward).  One warp owns one row; statistics are fp32.
+//
+// Reference counterparts: `model/linear/fp8/custom/rms_norm.py:14-91` (RMSNorm gain / backward),
+// `model/attention/qk_norm_rope.py:21-150` (RoPE -> QK-norm -> clamped learned scale),
+// `experiments/057-fused-attention-residual-rmsnorm.patch` (residual + RMSNorm).
+#include "../common/ptx.cuh"
+#include "../kernels_decl.h"
+
+namespace gm {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+    uint2 raw;
+    raw.x = pack_bf16x2(v.x, v.y);
+    raw.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+constexpr int NORM_WARPS = 8;
+// A row of d elements is covered by d/128 chunks of 128 (32 lanes x 4); the chunk count is a template
+// parameter so the per-lane row copy stays in registers.  Supported: d = 128*{1,2,4,6,8,12,16} (up to 2048).
+
+// x_new = alpha*x + beta*branch (when branch != nullptr; written to x_out), y = rmsnorm(x_new) * w
+template <typename TX, int MAX_CHUNKS>
+__global__ void __launch_bounds__(NORM_WARPS * 32)
+rmsnorm_fwd_kernel(const TX* __restrict__ x, const __nv_bfloat16* __restrict__ branch, const float* __restrict__ alpha,
+                   const float* __restrict__ beta, TX* __restrict__ x_out, const float* __restrict__ w,
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int d, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int chunks = d >> 7;
+    const float a = alpha ? *alpha : 1.f, b = beta ? *beta : 1.f;
+    float4 v[MAX_CHUNKS];
+    float ss = 0.f;
+    const long long base = static_cast<long long>(row) * d;
+#pragma unroll
+    for (int c = 0; c < MAX_CHUNKS; ++c) {
+        if (c < chunks) {
+            const int col = (c * 32 + lane) * 4;
+            float4 t = load4<TX>(x + base + col);
+            if (branch) {
+                const float4 r = load4<__nv_bfloat16>(branch + base + col);
+                t.x = a * t.x + b * r.x; t.y = a * t.y + b * r.y; t.z = a * t.z + b * r.z; t.w = a * t.w + b * r.w;
+                store4<TX>(x_out + base + col, t);
+            }
+            v[c] = t;
+            ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+        }
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / d + eps);
+    if (lane == 0 && rstd) rstd[row] = r;
+#pragma unroll
+    for (int c = 0; c < MAX_CHUNKS; ++c) {
+        if (c < chunks) {
+            const int col = (c * 32 + lane) * 4;
+            float4 g = w ? *reinterpret_cast<const float4*>(w + col) : make_float4(1.f, 1.f, 1.f, 1.f);
+            store4<__nv_bfloat16>(y + base + col, make_float4(v[c].x * r * g.x, v[c].y * r * g.y, v[c].z * r * g.z, v[c].w * r * g.w));
+        }
+    }
+}
+
+// dx = rstd * (w*dy - xhat * mean(w*dy*xhat)) (+ dres), dw partial per block (deterministic two-pass reduce).
+template <typename TX, int MAX_CHUNKS>
+__global__ void __launch_bounds__(NORM_WARPS * 32)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
+                   const float* __restrict__ rstd, const TX* __restrict__ dres, TX* __restrict__ dx,
+                   float* __restrict__ dw_partial, int rows, int d) {
+    extern __shared__ float smem_dw[];      // [NORM_WARPS][d]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int chunks = d >> 7;
+    float4 acc[MAX_CHUNKS];
+#pragma unroll
+    for (int c = 0; c < MAX_CHUNKS; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int row = blockIdx.x * NORM_WARPS + warp; row < rows; row += gridDim.x * NORM_WARPS) {
+        const long long base = static_cast<long long>(row) * d;
+        const float r = rstd[row];
+        float4 xh[MAX_CHUNKS], g[MAX_CHUNKS];
+        float dot = 0.f;
+#pragma unroll
+        for (int c = 0; c < MAX_CHUNKS; ++c) {
+            if (c < chunks) {
+                const int col = (c * 32 + lane) * 4;
+                const float4 xv = load4<TX>(x + base + col);
+                const float4 dv = load4<__nv_bfloat16>(dy + base + col);
+                const float4 wv = w ? *reinterpret_cast<const float4*>(w + col) : make_float4(1.f, 1.f, 1.f, 1.f);
+                xh[c] = make_float4(xv.x * r, xv.y * r, xv.z * r, xv.w * r);
+                acc[c].x += dv.x * xh[c].x; acc[c].y += dv.y * xh[c].y; acc[c].z += dv.z * xh[c].z; acc[c].w += dv.w * xh[c].w;
+                g[c] = make_float4(dv.x * wv.x, dv.y * wv.y, dv.z * wv.z, dv.w * wv.w);
+                dot += g[c].x * xh[c].x + g[c].y * xh[c].y + g[c].z * xh[c].z + g[c].w * xh[c].w;
+            }
+        }
+        dot = warp_sum(dot) / d;
+#pragma unroll
+        for (int c = 0; c < MAX_CHUNKS; ++c) {
+            if (c < chunks) {
+                const int col = (c * 32 + lane) * 4;
+                float4 o = make_float4(r * (g[c].x - xh[c].x * dot), r * (g[c].y - xh[c].y * dot),
+                                       r * (g[c].z - xh[c].z * dot), r * (g[c].w - xh[c].w * dot));
+                if (dres) {
+                    const float4 e = load4<TX>(dres + base + col);
+                    o.x += e.x; o.y += e.y; o.z += e.z; o.w += e.w;
+                }
+                store4<TX>(dx + base + col, o);
+            }
+        }
+    }
+    if (dw_partial == nullptr) return;
+#pragma unroll
+    for (int c = 0; c < MAX_CHUNKS; ++c) {
+        if (c < chunks) *reinterpret_cast<float4*>(smem_dw + warp * d + (c * 32 + lane) * 4) = acc[c];
+    }
+    __syncthreads();
+    for (int col = threadIdx.x; col < d; col += blockDim.x) {
+        float s = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < NORM_WARPS; ++wi) s += smem_dw[wi * d + col];
+        dw_partial[static_cast<long long>(blockIdx.x) * d + col] = s;
+    }
+}
+
+// out[col] = sum over rows of partial[row][col]  (second pass of the deterministic column reductions)
+__global__ void column_sum_kernel(const float* __restrict__ partial, float* __restrict__ out, int rows, int cols, int accumulate) {
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= cols) return;
+    float s = 0.f;
+    for (int r = 0; r < rows; ++r) s += partial[static_cast<long long>(r) * cols + col];
+    out[col] = accumulate ? out[col] + s : s;
+}
+
+bool norm_dim_supported(int d) {
+    const int c = d / 128;
+    return d % 128 == 0 && (c == 1 || c == 2 || c == 4 || c == 6 || c == 8 || c == 12 || c == 16);
+}
+
+#define GM_DISPATCH_CHUNKS(d, CALL)        \
+    switch ((d) / 128) {                   \
+        case 1: { CALL(1); } break;        \
+        case 2: { CALL(2); } break;        \
+        case 4: { CALL(4); } break;        \
+        case 6: { CALL(6); } break;        \
+        case 8: { CALL(8); } break;        \
+        case 12: { CALL(12); } break;      \
+        case 16: { CALL(16); } break;      \
+        default: return false;             \
+    }
+
+bool launch_rmsnorm_fwd(const void* x, bool x_fp32, const void* branch, const float* alpha, const float* beta, void* x_out,
+                        const float* w, void* y, float* rstd, int rows, int d, float eps, cudaStream_t s) {
+    if (!norm_dim_supported(d)) return false;
+    const int blocks = (rows + NORM_WARPS - 1) / NORM_WARPS;
+#define GM_FWD(C)                                                                                                              \
+    if (x_fp32)                                                                                                                \
+        rmsnorm_fwd_kernel<float, C><<<blocks, NORM_WARPS * 32, 0, s>>>(                                                       \
+            static_cast<const float*>(x), static_cast<const __nv_bfloat16*>(branch), alpha, beta, static_cast<float*>(x_out), w, \
+            static_cast<__nv_bfloat16*>(y), rstd, rows, d, eps);                                                               \
+    else                                                                                                                       \
+        rmsnorm_fwd_kernel<__nv_bfloat16, C><<<blocks, NORM_WARPS * 32, 0, s>>>(                                               \
+            static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(branch), alpha, beta,                      \
+            static_cast<__nv_bfloat16*>(x_out), w, static_cast<__nv_bfloat16*>(y), rstd, rows, d, eps);
+    GM_DISPATCH_CHUNKS(d, GM_FWD)
+#undef GM_FWD
+    return true;
+}
+
+int rmsnorm_bwd_blocks(int rows) { return min(1184, (rows + NORM_WARPS - 1) / NORM_WARPS); }
+
+bool launch_rmsnorm_bwd(const void* dy, const void* x, bool x_fp32, const float* w, const float* rstd, const void* dres, void* dx,
+                        float* dw_partial, float* dw, int dw_accumulate, int rows, int d, cudaStream_t s) {
+    if (!norm_dim_supported(d)) return false;
+    const int blocks = rmsnorm_bwd_blocks(rows);
+    const size_t smem = dw_partial ? static_cast<size_t>(NORM_WARPS) * d * sizeof(float) : 0;
+#define GM_BWD(C)                                                                                                              \
+    if (x_fp32) {                                                                                                              \
+        auto k = rmsnorm_bwd_kernel<float, C>;                                                                                 \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));    \
+        k<<<blocks, NORM_WARPS * 32, smem, s>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const float*>(x), w, rstd,  \
+                                                static_cast<const float*>(dres), static_cast<float*>(dx), dw_partial, rows, d); \
+    } else {                                                                                                                   \
+        auto k = rmsnorm_bwd_kernel<__nv_bfloat16, C>;                                                                         \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));    \
+        k<<<blocks, NORM_WARPS * 32, smem, s>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), w, rstd, \
+                                                static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx), dw_partial, rows, d); \
+    }
+    GM_DISPATCH_CHUNKS(d, GM_BWD)
+#undef GM_BWD
+    if (dw_partial) column_sum_kernel<<<(d + 255) / 256, 256, 0, s>>>(dw_partial, dw, blocks, d, dw_accumulate);
+    return true;
+}
+
+void launch_column_sum(const float* partial, float* out, int rows, int cols, int accumulate, cudaStream_t s) {
+    column_sum_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, out, rows, cols, accumulate);
+}
+
+// ---- RoPE + QK-norm ---------------------------------------------------------------------------------------
+// Rows are (token, head) vectors of D elements inside a [tokens, row_stride] matrix (the packed QKV GEMM output):
+// element (t, h, i) sits at t*row_stride + h*D + i.  The first `q_heads` heads use q_scale, the next `k_heads`
+// heads use k_scale.  pos = t % seq_len indexes the cos/sin tables [seq_len, D/2].
+// forward:  r = rope(x);  g = rsqrt(mean|sum(r^2) + eps);  y = r * g * clamp(scale[h])
+// backward: dr = g*s*(dy - r * g^2 * mean|sum(dy*r));  dx = rope^T(dr);  dscale[h] += sum(dy * r * g) inside the clamp range
+template <int D, bool BWD>
+__global__ void __launch_bounds__(256)
+rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ out,
+                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, const float* __restrict__ q_scale,
+                   const float* __restrict__ k_scale, float* __restrict__ dscale_partial, long long tokens, int seq_len,
+                   int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin, float smax) {
+    constexpr int PAIRS = D / 2;
+    constexpr int PER_LANE = (PAIRS + 31) / 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int heads = q_heads + k_heads;
+    const long long total = tokens * heads;
+    __shared__ float ds_smem[8][64];
+    if (BWD) {
+        for (int i = threadIdx.x; i < 8 * 64; i += blockDim.x) (&ds_smem[0][0])[i] = 0.f;
+        __syncthreads();
+    }
+    for (long long idx = static_cast<long long>(blockIdx.x) * 8 + warp; idx < total; idx += static_cast<long long>(gridDim.x) * 8) {
+        const long long t = idx / heads;
+        const int h = static_cast<int>(idx - t * heads);
+        const int pos = static_cast<int>(t % seq_len);
+        const float raw = h < q_heads ? (q_scale ? q_scale[h] : 1.f) : (k_scale ? k_scale[h - q_heads] : 1.f);
+        const bool has_norm = q_scale != nullptr;
+        const float sc = fminf(fmaxf(raw, smin), smax);
+        float r1[PER_LANE], r2[PER_LANE], c[PER_LANE], sn[PER_LANE], g1[PER_LANE], g2[PER_LANE];
+        float ss = 0.f, dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+            const int pr = lane + 32 * i;
+            r1[i] = r2[i] = g1[i] = g2[i] = 0.f; c[i] = 1.f; sn[i] = 0.f;
+            if (pr < PAIRS) {
+                const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(x + t * x_stride + h * D + 2 * pr);
+                const float2 xf = __bfloat1622float2(xv);
+                if (cos_t) { c[i] = cos_t[pos * PAIRS + pr]; sn[i] = sin_t[pos * PAIRS + pr]; }
+                r1[i] = xf.x * c[i] - xf.y * sn[i];
+                r2[i] = xf.x * sn[i] + xf.y * c[i];
+                ss += r1[i] * r1[i] + r2[i] * r2[i];
+                if (BWD) {
+                    const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dy + t * o_stride + h * D + 2 * pr));
+                    g1[i] = gf.x; g2[i] = gf.y;
+                    dot += g1[i] * r1[i] + g2[i] * r2[i];
+                }
+            }
+        }
+        float gain = 1.f, mult = 1.f;
+        if (has_norm) {
+            ss = warp_sum(ss);
+            gain = rsqrtf((rms ? ss / D : ss) + eps);
+            mult = gain * sc;
+        }
+        if (BWD) {
+            dot = warp_sum(dot);
+            if (has_norm && lane == 0 && raw >= smin && raw <= smax) ds_smem[warp][h] += dot * gain;
+            const float coef = has_norm ? gain * gain * (rms ? dot / D : dot) : 0.f;
+#pragma unroll
+            for (int i = 0; i < PER_LANE; ++i) {
+                const int pr = lane + 32 * i;
+                if (pr < PAIRS) {
+                    const float d1 = mult * (g1[i] - r1[i] * coef), d2 = mult * (g2[i] - r2[i] * coef);
+                    const float o1 = d1 * c[i] + d2 * sn[i], o2 = -d1 * sn[i] + d2 * c[i];
+                    *reinterpret_cast<__nv_bfloat162*>(out + t * x_stride + h * D + 2 * pr) = __floats2bfloat162_rn(o1, o2);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < PER_LANE; ++i) {
+                const int pr = lane + 32 * i;
+                if (pr < PAIRS)
+                    *reinterpret_cast<__nv_bfloat162*>(out + t * o_stride + h * D + 2 * pr) = __floats2bfloat162_rn(r1[i] * mult, r2[i] * mult);
+            }
+        }
+    }
+    if (BWD && dscale_partial) {
+        __syncthreads();
+        for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+            float s = 0.f;
+#pragma unroll
+            for (int wi = 0; wi < 8; ++wi) s += ds_smem[wi][h];
+            dscale_partial[static_cast<long long>(blockIdx.x) * heads + h] = s;
+        }
+    }
+}
+
+int rope_blocks(long long tokens, int heads) {
+    const long long want = (tokens * heads + 7) / 8;
+    return static_cast<int>(want < 2368 ? want : 2368);
+}
+
+bool launch_rope_qknorm(bool bwd, int D, const void* x, const void* dy, void* out, const float* cos_t, const float* sin_t,
+                        const float* q_scale, const float* k_scale, float* dscale_partial, long long tokens, int seq_len,
+                        int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin,
+                        float smax, cudaStream_t s) {
+    if (q_heads + k_heads > 64) return false;
+    const int blocks = rope_blocks(tokens, q_heads + k_heads);
+#define GM_ROPE(DD)                                                                                                            \
+    if (bwd)                                                                                                                   \
+        rope_qknorm_kernel<DD, true><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), \
+            static_cast<__nv_bfloat16*>(out), cos_t, sin_t, q_scale, k_scale, dscale_partial, tokens, seq_len, q_heads, k_heads,  \
+            x_stride, o_stride, eps, rms, smin, smax);                                                                         \
+    else                                                                                                                       \
+        rope_qknorm_kernel<DD, false><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), nullptr,                     \
+            static_cast<__nv_bfloat16*>(out), cos_t, sin_t, q_scale, k_scale, nullptr, tokens, seq_len, q_heads, k_heads,        \
+            x_stride, o_stride, eps, rms, smin, smax);
+    switch (D) {
+        case 32: GM_ROPE(32); break;
+        case 64: GM_ROPE(64); break;
+        case 128: GM_ROPE(128); break;
+        default: return false;
+    }
+#undef GM_ROPE
+    return true;
+}
+
+}  // namespace gm

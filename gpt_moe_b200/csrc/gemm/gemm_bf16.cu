@@ -1,0 +1,292 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: D = alpha * A * B^T (+ beta * C) (+ D).
+//
+// One CTA per SM walks a list of 128 x 256 output tiles.  Roles:
+//   warp 0  : TMA producer   - fills a 4-stage ring of {A 128x64, B 256x64} bf16 tiles (128B swizzle)
+//   warp 1  : MMA issuer     - one thread issues tcgen05.mma (M128 N256 K16) into one of two TMEM
+//                              accumulators (2 x 256 columns), commits to free the smem stage
+//   warps 2-5: epilogue      - tcgen05.ld the finished accumulator (thread = row), scale / add C /
+//                              accumulate, convert, store; overlaps the next tile's main loop
+// Operands may be K-major ([rows, K] with K contiguous) or MN-major ([K, rows] with rows
+// contiguous); both are read straight from row-major tensors by TMA, so forward (X W^T), input
+// gradient (dY W) and weight gradient (dY^T X) all run without a transposed copy.
+//
+// Three tile enumerations share the kernel:
+//   DENSE     (optionally batched over z)                      - projections, LM head, Polar Express
+//   GROUPED_M rows of A belong to experts; tile -> expert table on the device picks B's z slice
+//             (expert segments are padded to 128 rows, so a tile never straddles two experts)
+//   GROUPED_K one output matrix per expert, contraction over that expert's (padded) row segment
+//             - the expert weight gradient; empty experts get exact zeros
+// Reference counterparts: Triton `_grouped_mm_kernel` (model/linear/default/grouped.py:12-70) and the
+// cuBLAS calls behind every F.linear (model/linear/linear.py:23).
+#include "../common/ptx.cuh"
+#include "gemm.h"
+
+#include <cuda.h>
+
+namespace gm {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int GROUP_M = 8;
+constexpr uint32_t TMEM_COLS = 512;
+
+struct TileCoord {
+    int m0, n0;        // element offsets of the tile in the output
+    int az, bz, dz;    // z (batch / expert) coordinates for A, B, D
+    int k_begin, k_blocks;
+    int m_limit, n_limit;
+};
+
+__device__ __forceinline__ int total_tiles(const GemmParams& p, int& m_tiles, int& n_tiles) {
+    n_tiles = (p.N + BN - 1) / BN;
+    if (p.mode == GEMM_GROUPED_M) {
+        m_tiles = *p.num_m_tiles;
+        return m_tiles * n_tiles;
+    }
+    m_tiles = (p.M + BM - 1) / BM;
+    return m_tiles * n_tiles * p.batch;
+}
+
+__device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, int m_tiles, int n_tiles) {
+    TileCoord t;
+    const int per_batch = m_tiles * n_tiles;
+    const int z = (p.mode == GEMM_GROUPED_M) ? 0 : tile / per_batch;
+    int r = tile - z * per_batch;
+    // grouped raster: GROUP_M row-tiles share their column sweep so A tiles stay in L2
+    const int group = r / (GROUP_M * n_tiles);
+    const int first_m = group * GROUP_M;
+    const int rows_in_group = min(GROUP_M, m_tiles - first_m);
+    r -= group * GROUP_M * n_tiles;
+    const int mt = first_m + r % rows_in_group;
+    const int nt = r / rows_in_group;
+    t.m0 = mt * BM;
+    t.n0 = nt * BN;
+    t.m_limit = p.M;
+    t.n_limit = p.N;
+    t.k_begin = 0;
+    t.k_blocks = (p.K + BK - 1) / BK;
+    t.az = t.bz = t.dz = z;
+    if (p.mode == GEMM_GROUPED_M) {
+        t.az = 0;
+        t.dz = 0;
+        t.bz = p.tile_expert[mt];
+        t.m_limit = m_tiles * BM;
+    } else if (p.mode == GEMM_GROUPED_K) {
+        const int begin = z == 0 ? 0 : p.seg_ends[z - 1];
+        t.az = t.bz = 0;
+        t.k_begin = begin;
+        t.k_blocks = (p.seg_ends[z] - begin) / BK;
+    }
+    return t;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 128); }
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    int m_tiles, n_tiles;
+    const int tiles = total_tiles(p, m_tiles, n_tiles);
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const TileCoord t = tile_coord(p, tile, m_tiles, n_tiles);
+                for (int kb = 0; kb < t.k_blocks; ++kb) {
+                    if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(p.status, 101); ok = false; break; }
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    uint8_t* a_dst = smem + s * STAGE_BYTES;
+                    uint8_t* b_dst = a_dst + A_BYTES;
+                    const int k = t.k_begin + kb * BK;
+                    if (A_MN) {
+                        for (int i = 0; i < BM / 64; ++i) tma_load_3d(a_dst + i * (64 * BK * 2), &tmap_a, &full[s], t.m0 + 64 * i, k, t.az);
+                    } else {
+                        tma_load_3d(a_dst, &tmap_a, &full[s], k, t.m0, t.az);
+                    }
+                    if (B_MN) {
+                        for (int i = 0; i < BN / 64; ++i) tma_load_3d(b_dst + i * (64 * BK * 2), &tmap_b, &full[s], t.n0 + 64 * i, k, t.bz);
+                    } else {
+                        tma_load_3d(b_dst, &tmap_b, &full[s], k, t.n0, t.bz);
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+            // K-major: 8-row groups are 1024 B apart, 16 K-elements = 32 B.  MN-major: 64-element column slabs are
+            // BK*128 B apart (leading offset), 8-K-row groups 1024 B apart, 16 K-rows = 2048 B.
+            constexpr uint32_t a_lbo = A_MN ? BK * 128 : 16, b_lbo = B_MN ? BK * 128 : 16;
+            constexpr uint32_t a_kstep = A_MN ? 2048 : 32, b_kstep = B_MN ? 2048 : 32;
+            int s = 0; uint32_t ph = 0; int acc = 0; uint32_t acc_ph = 0;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const TileCoord t = tile_coord(p, tile, m_tiles, n_tiles);
+                if (t.k_blocks == 0) continue;
+                if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1)) { atomicExch(p.status, 102); ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < t.k_blocks; ++kb) {
+                    if (!mbar_wait(&full[s], ph)) { atomicExch(p.status, 103); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                    for (int k4 = 0; k4 < BK / 16; ++k4) {
+                        const uint64_t adesc = make_smem_desc(a_addr + k4 * a_kstep, a_lbo, 1024);
+                        const uint64_t bdesc = make_smem_desc(b_addr + k4 * b_kstep, b_lbo, 1024);
+                        umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k4) != 0);
+                    }
+                    umma_commit(&empty[s]);
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[acc]);
+                if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            }
+        }
+    } else {
+        const int quad = warp & 3;                  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+        int acc = 0; uint32_t acc_ph = 0;
+        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            const TileCoord t = tile_coord(p, tile, m_tiles, n_tiles);
+            const int row = t.m0 + quad * 32 + lane;
+            const bool row_ok = row < t.m_limit;
+            const long long row_off = static_cast<long long>(t.dz) * p.d_batch_stride + static_cast<long long>(row) * p.ldd;
+            const bool have_acc = t.k_blocks != 0;
+            if (have_acc) {
+                if (!mbar_wait(&acc_full[acc], acc_ph)) { atomicExch(p.status, 104); ok = false; break; }
+                tc_fence_after();
+            }
+            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                const int col0 = t.n0 + chunk * 32;
+                if (col0 >= t.n_limit) break;      // uniform across the CTA
+                uint32_t r[32];
+                if (have_acc) {
+                    tmem_ld_32x32b_x32(tmem_base + acc * BN + chunk * 32 + (static_cast<uint32_t>(quad * 32) << 16), r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = 0u;
+                }
+                if (!row_ok) continue;
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+                const bool full_chunk = col0 + 32 <= t.n_limit;
+                if (p.C != nullptr) {
+                    const __nv_bfloat16* c = reinterpret_cast<const __nv_bfloat16*>(p.C) +
+                        static_cast<long long>(t.dz) * p.c_batch_stride + static_cast<long long>(row) * p.ldc + col0;
+                    if (full_chunk) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            const uint4 q = *reinterpret_cast<const uint4*>(c + j);
+                            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 f = __bfloat1622float2(h[e]);
+                                v[j + 2 * e] += p.beta * f.x;
+                                v[j + 2 * e + 1] += p.beta * f.y;
+                            }
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < t.n_limit; ++j) v[j] += p.beta * __bfloat162float(c[j]);
+                    }
+                }
+                if (p.out_fp32) {
+                    float* d = reinterpret_cast<float*>(p.D) + row_off + col0;
+                    if (full_chunk) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            if (p.accumulate) {
+                                const float4 old = *reinterpret_cast<const float4*>(d + j);
+                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            }
+                            *reinterpret_cast<float4*>(d + j) = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < t.n_limit; ++j) d[j] = p.accumulate ? d[j] + v[j] : v[j];
+                    }
+                } else {
+                    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + row_off + col0;
+                    if (full_chunk) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 o;
+                            o.x = pack_bf16x2(v[j], v[j + 1]);
+                            o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                            o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+                            o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                            *reinterpret_cast<uint4*>(d + j) = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < t.n_limit; ++j) d[j] = __float2bfloat16(v[j]);
+                    }
+                }
+            }
+            if (have_acc) {
+                tc_fence_before();
+                mbar_arrive(&acc_empty[acc]);
+                if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            }
+        }
+    }
+
+    // common teardown: every path (including a timed-out wait) reaches it, so TMEM is always released
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*reinterpret_cast<volatile int*>(p.status) != 0) {
+            // a wait gave up: give any TMA copy still in flight time to land before the CTA's smem is recycled
+            const long long start = clock64();
+            while (clock64() - start < 200000) {}
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+template <bool A_MN, bool B_MN>
+static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms, cudaStream_t stream) {
+    auto kernel = gemm_bf16_kernel<A_MN, B_MN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    kernel<<<sms, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gemm_bf16(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, bool a_mn, bool b_mn,
+                             int sms, cudaStream_t stream) {
+    if (a_mn) return b_mn ? launch_variant<true, true>(ta, tb, p, sms, stream) : launch_variant<true, false>(ta, tb, p, sms, stream);
+    return b_mn ? launch_variant<false, true>(ta, tb, p, sms, stream) : launch_variant<false, false>(ta, tb, p, sms, stream);
+}
+
+}  // namespace gm
