@@ -1,14 +1,259 @@
-// Bindings of the non-GEMM kernels.
+// Bindings of the non-GEMM kernels: tensors in, raw pointers out.  Shape/dtype checks live here so the
+// kernels can assume aligned, contiguous data.
 #include <torch/extension.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
 #include "kernels.h"
+#include "kernels_decl.h"
 
 namespace gm {
+namespace {
+
+#define GM_CHECK(cond, msg) TORCH_CHECK(cond, "gpt_moe_b200: ", msg)
+using torch::Tensor;
+using OptTensor = c10::optional<Tensor>;
+
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+const float* fptr(const OptTensor& t) { return t.has_value() ? t->data_ptr<float>() : nullptr; }
+void check_bf16(const Tensor& t, const char* name) {
+    GM_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.is_contiguous(), std::string(name) + " must be a contiguous CUDA bf16 tensor");
+}
+
+// y = rmsnorm(x_new) * w with x_new = alpha*x + beta*branch when a branch is given.  Returns (y, rstd, x_new).
+std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const OptTensor& w, double eps, const OptTensor& branch, const OptTensor& alpha,
+                                const OptTensor& beta) {
+    c10::cuda::CUDAGuard guard(x.device());
+    GM_CHECK(x.is_cuda() && x.is_contiguous(), "rmsnorm input must be contiguous");
+    GM_CHECK(x.scalar_type() == torch::kFloat32 || x.scalar_type() == torch::kBFloat16, "rmsnorm input must be fp32 or bf16");
+    const int d = x.size(-1);
+    const int rows = x.numel() / d;
+    GM_CHECK(norm_dim_supported(d), "rmsnorm width must be 128*{1,2,4,6,8,12,16}");
+    Tensor y = torch::empty(x.sizes(), x.options().dtype(torch::kBFloat16));
+    Tensor rstd = torch::empty({rows}, x.options().dtype(torch::kFloat32));
+    Tensor x_new = x;
+    if (branch.has_value()) {
+        check_bf16(*branch, "branch");
+        x_new = torch::empty_like(x);
+    }
+    launch_rmsnorm_fwd(x.data_ptr(), x.scalar_type() == torch::kFloat32, branch.has_value() ? branch->data_ptr() : nullptr,
+                       fptr(alpha), fptr(beta), x_new.data_ptr(), fptr(w), y.data_ptr(), rstd.data_ptr<float>(), rows, d,
+                       static_cast<float>(eps), stream());
+    return {y, rstd, x_new};
+}
+
+// Returns (dx, dw).  dx = norm backward (+ dres when given), same dtype as x.
+std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const OptTensor& w, const Tensor& rstd, const OptTensor& dres) {
+    c10::cuda::CUDAGuard guard(x.device());
+    check_bf16(dy, "dy");
+    const int d = x.size(-1);
+    const int rows = x.numel() / d;
+    Tensor dx = torch::empty_like(x);
+    Tensor dw, partial;
+    if (w.has_value()) {
+        dw = torch::empty({d}, x.options().dtype(torch::kFloat32));
+        partial = torch::empty({rmsnorm_bwd_blocks(rows), d}, x.options().dtype(torch::kFloat32));
+    }
+    GM_CHECK(launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), x.scalar_type() == torch::kFloat32, fptr(w), rstd.data_ptr<float>(),
+                                dres.has_value() ? dres->data_ptr() : nullptr, dx.data_ptr(),
+                                w.has_value() ? partial.data_ptr<float>() : nullptr, w.has_value() ? dw.data_ptr<float>() : nullptr, 0,
+                                rows, d, stream()), "unsupported rmsnorm width");
+    return {dx, dw};
+}
+
+// qkv: [tokens, row_stride] bf16 holding q heads then k heads (then anything else) of width D each.
+// forward writes rotated+normalised q,k into `out` (same layout; may alias a separate buffer)
+void rope_qknorm_fwd(const Tensor& x, Tensor& out, const OptTensor& cos_t, const OptTensor& sin_t, const OptTensor& q_scale,
+                     const OptTensor& k_scale, int64_t seq_len, int64_t q_heads, int64_t k_heads, int64_t head_dim, double eps,
+                     bool rms, double smin, double smax) {
+    c10::cuda::CUDAGuard guard(x.device());
+    GM_CHECK(x.scalar_type() == torch::kBFloat16 && x.stride(-1) == 1 && out.stride(-1) == 1, "rope_qknorm needs bf16 rows");
+    const long long tokens = x.size(0);
+    GM_CHECK(launch_rope_qknorm(false, head_dim, x.data_ptr(), nullptr, out.data_ptr(), fptr(cos_t), fptr(sin_t), fptr(q_scale),
+                                fptr(k_scale), nullptr, tokens, seq_len, q_heads, k_heads, x.stride(0), out.stride(0),
+                                static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), stream()),
+             "unsupported head size for rope_qknorm");
+}
+
+// backward: dx written into `dx` (layout of x) for the q and k heads; returns dscale [q_heads + k_heads] (fp32)
+Tensor rope_qknorm_bwd(const Tensor& x, const Tensor& dy, Tensor& dx, const OptTensor& cos_t, const OptTensor& sin_t,
+                       const OptTensor& q_scale, const OptTensor& k_scale, int64_t seq_len, int64_t q_heads, int64_t k_heads,
+                       int64_t head_dim, double eps, bool rms, double smin, double smax) {
+    c10::cuda::CUDAGuard guard(x.device());
+    const long long tokens = x.size(0);
+    const int heads = q_heads + k_heads;
+    const int blocks = rope_blocks(tokens, heads);
+    Tensor partial = torch::empty({blocks, heads}, x.options().dtype(torch::kFloat32));
+    GM_CHECK(x.stride(0) == dx.stride(0), "dx must share x's row stride");
+    GM_CHECK(launch_rope_qknorm(true, head_dim, x.data_ptr(), dy.data_ptr(), dx.data_ptr(), fptr(cos_t), fptr(sin_t), fptr(q_scale),
+                                fptr(k_scale), partial.data_ptr<float>(), tokens, seq_len, q_heads, k_heads, x.stride(0),
+                                dy.stride(0), static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), stream()),
+             "unsupported head size for rope_qknorm");
+    Tensor dscale = torch::empty({heads}, partial.options());
+    launch_column_sum(partial.data_ptr<float>(), dscale.data_ptr<float>(), blocks, heads, 0, stream());
+    return dscale;
+}
+
+// Counted routing.  Returns (dest[S], src_of_row[cap], seg_ends[E], counts[E], tile_expert[cap/128], meta[2]).
+std::vector<Tensor> route(const Tensor& top_idx, int64_t experts) {
+    c10::cuda::CUDAGuard guard(top_idx.device());
+    GM_CHECK(top_idx.is_cuda() && top_idx.scalar_type() == torch::kInt64 && top_idx.is_contiguous(), "top_idx must be contiguous int64");
+    const int slots = top_idx.numel();
+    const int cap = (slots + 127) / 128 * 128 + experts * 128;
+    const int chunks = (slots + 1023) / 1024;
+    auto opt = top_idx.options().dtype(torch::kInt32);
+    Tensor hist = torch::empty({2, chunks, experts}, opt);
+    Tensor dest = torch::empty({slots}, opt), src = torch::empty({cap}, opt);
+    Tensor seg = torch::empty({experts}, opt), counts = torch::empty({experts}, opt);
+    Tensor tiles = torch::zeros({cap / 128}, opt), meta = torch::empty({2}, opt);
+    GM_CHECK(launch_route(top_idx.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(top_idx.data_ptr<int64_t>()) : nullptr, slots,
+                          experts, hist[0].data_ptr<int>(), hist[1].data_ptr<int>(), counts.data_ptr<int>(), seg.data_ptr<int>(),
+                          tiles.data_ptr<int>(), meta.data_ptr<int>(), dest.data_ptr<int>(), src.data_ptr<int>(), stream()),
+             "routing supports at most 128 experts");
+    return {dest, src, seg, counts, tiles, meta};
+}
+
+Tensor gather_rows(const Tensor& hidden, const Tensor& src_of_row, const Tensor& meta, int64_t top_k) {
+    c10::cuda::CUDAGuard guard(hidden.device());
+    check_bf16(hidden, "hidden");
+    const int d = hidden.size(-1);
+    GM_CHECK(d % 8 == 0, "row width must be a multiple of 8");
+    const int cap = src_of_row.numel();
+    Tensor packed = torch::empty({cap, d}, hidden.options());
+    launch_gather_rows(hidden.data_ptr(), src_of_row.data_ptr<int>(), meta.data_ptr<int>(), packed.data_ptr(), d, top_k, cap, stream());
+    return packed;
+}
+
+Tensor combine_fwd(const Tensor& y, const Tensor& dest, const Tensor& gates) {
+    c10::cuda::CUDAGuard guard(y.device());
+    check_bf16(y, "y");
+    GM_CHECK(gates.scalar_type() == torch::kFloat32 && gates.is_contiguous(), "gates must be contiguous fp32");
+    const int tokens = gates.size(0), top_k = gates.size(1), d = y.size(-1);
+    Tensor out = torch::empty({tokens, d}, y.options());
+    launch_combine_fwd(y.data_ptr(), dest.data_ptr<int>(), gates.data_ptr<float>(), out.data_ptr(), tokens, d, top_k, stream());
+    return out;
+}
+
+std::vector<Tensor> combine_bwd(const Tensor& dout, const Tensor& y, const Tensor& src_of_row, const Tensor& gates, const Tensor& meta) {
+    c10::cuda::CUDAGuard guard(y.device());
+    check_bf16(dout, "dout");
+    check_bf16(y, "y");
+    const int top_k = gates.size(1), d = y.size(-1), cap = src_of_row.numel();
+    Tensor dy = torch::empty_like(y);
+    Tensor dgates = torch::zeros_like(gates);
+    launch_combine_bwd(dout.data_ptr(), y.data_ptr(), src_of_row.data_ptr<int>(), gates.data_ptr<float>(), meta.data_ptr<int>(),
+                       dy.data_ptr(), dgates.data_ptr<float>(), d, top_k, cap, stream());
+    return {dy, dgates};
+}
+
+int act_kind(const std::string& name) {
+    if (name == "gelu") return 0;
+    if (name == "relu") return 1;
+    if (name == "relu2") return 2;
+    if (name == "silu") return 3;
+    if (name == "swiglu") return 4;
+    GM_CHECK(false, "unsupported activation function: " + name);
+    return -1;
+}
+
+Tensor activation_fwd(const Tensor& pre, const std::string& name, const OptTensor& meta) {
+    c10::cuda::CUDAGuard guard(pre.device());
+    check_bf16(pre, "pre");
+    const int kind = act_kind(name);
+    const int in_w = pre.size(-1), h = kind == 4 ? in_w / 2 : in_w;
+    const int rows = pre.numel() / in_w;
+    GM_CHECK(h % 2 == 0, "activation width must be even");
+    auto sizes = pre.sizes().vec();
+    sizes.back() = h;
+    Tensor act = torch::empty(sizes, pre.options());
+    launch_activation_fwd(pre.data_ptr(), act.data_ptr(), meta.has_value() ? meta->data_ptr<int>() : nullptr, rows, h, kind, stream());
+    return act;
+}
+
+Tensor activation_bwd(const Tensor& dact, const Tensor& pre, const std::string& name, const OptTensor& meta) {
+    c10::cuda::CUDAGuard guard(pre.device());
+    check_bf16(dact, "dact");
+    const int kind = act_kind(name);
+    const int in_w = pre.size(-1), h = kind == 4 ? in_w / 2 : in_w;
+    const int rows = pre.numel() / in_w;
+    Tensor dpre = torch::empty_like(pre);
+    launch_activation_bwd(dact.data_ptr(), pre.data_ptr(), dpre.data_ptr(), meta.has_value() ? meta->data_ptr<int>() : nullptr, rows, h, kind, stream());
+    return dpre;
+}
+
+// loss per row; logits overwritten with (softmax - onehot) * grad_scale when write_grad
+Tensor ce_fwd_bwd(Tensor& logits, const Tensor& targets, const Tensor& grad_scale, int64_t ignore_index, bool write_grad) {
+    c10::cuda::CUDAGuard guard(logits.device());
+    GM_CHECK(logits.scalar_type() == torch::kBFloat16 && logits.dim() == 2 && logits.stride(1) == 1 && logits.stride(0) % 8 == 0,
+             "logits must be [rows, vocab] bf16 with a row pitch that is a multiple of 8");
+    GM_CHECK(targets.scalar_type() == torch::kInt64 && targets.is_contiguous(), "targets must be contiguous int64");
+    const int rows = logits.size(0);
+    Tensor loss = torch::empty({rows}, logits.options().dtype(torch::kFloat32));
+    launch_ce_fwd_bwd(logits.data_ptr(), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), loss.data_ptr<float>(),
+                      grad_scale.data_ptr<float>(), rows, logits.size(1), logits.stride(0), ignore_index, write_grad, stream());
+    return loss;
+}
+
+void adamw(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptTensor& p_bf16, double lr, double beta1, double beta2,
+           double eps, double wd, int64_t step, double grad_scale) {
+    c10::cuda::CUDAGuard guard(p.device());
+    GM_CHECK(p.scalar_type() == torch::kFloat32 && g.scalar_type() == torch::kFloat32 && p.is_contiguous() && g.is_contiguous(),
+             "AdamW expects contiguous fp32 parameters and gradients");
+    GM_CHECK(m.scalar_type() == v.scalar_type() && m.is_contiguous() && v.is_contiguous(), "AdamW moments must share a dtype");
+    const double bc1 = 1.0 - std::pow(beta1, static_cast<double>(step));
+    const double bc2 = std::sqrt(1.0 - std::pow(beta2, static_cast<double>(step)));
+    launch_adamw(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr(), v.data_ptr(), m.scalar_type() == torch::kBFloat16,
+                 p_bf16.has_value() ? p_bf16->data_ptr() : nullptr, p.numel(), lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale, stream());
+}
+
+// pointer tables are int64 CUDA tensors holding device addresses (built once per bucket by the caller)
+void muon_prepare(const Tensor& grad_ptrs, const Tensor& buf_ptrs, Tensor& packed, Tensor& sumsq, int64_t rows, int64_t cols,
+                  int64_t g_stride, int64_t b_stride, double momentum, bool nesterov, bool transpose, double grad_scale) {
+    c10::cuda::CUDAGuard guard(packed.device());
+    check_bf16(packed, "packed");
+    const int n = grad_ptrs.numel();
+    GM_CHECK(packed.numel() == n * rows * cols && (rows * cols) % 2 == 0, "packed buffer shape");
+    launch_muon_prepare(reinterpret_cast<const float* const*>(grad_ptrs.data_ptr<int64_t>()),
+                        reinterpret_cast<float* const*>(buf_ptrs.data_ptr<int64_t>()), packed.data_ptr(), sumsq.data_ptr<float>(), n,
+                        rows, cols, g_stride, b_stride, momentum, nesterov, transpose, grad_scale, stream());
+}
+
+void muon_apply(const Tensor& weight_ptrs, const OptTensor& bf16_ptrs, const Tensor& update, int64_t rows, int64_t cols,
+                int64_t w_stride, double alpha, bool transpose) {
+    c10::cuda::CUDAGuard guard(update.device());
+    check_bf16(update, "update");
+    launch_muon_apply(reinterpret_cast<float* const*>(weight_ptrs.data_ptr<int64_t>()),
+                      bf16_ptrs.has_value() ? reinterpret_cast<void* const*>(bf16_ptrs->data_ptr<int64_t>()) : nullptr,
+                      update.data_ptr(), weight_ptrs.numel(), rows, cols, w_stride, alpha, transpose, stream());
+}
+
+void cast_bf16(const Tensor& src, Tensor& dst) {
+    c10::cuda::CUDAGuard guard(src.device());
+    GM_CHECK(src.scalar_type() == torch::kFloat32 && dst.scalar_type() == torch::kBFloat16 && src.is_contiguous() && dst.is_contiguous() &&
+             src.numel() == dst.numel(), "cast_bf16 expects contiguous fp32 -> bf16 of equal size");
+    launch_cast_bf16(src.data_ptr<float>(), dst.data_ptr(), src.numel(), stream());
+}
+
+}  // namespace
 
 void register_kernels(pybind11::module_& m) {
-    (void)m;
+    namespace py = pybind11;
+    m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("eps"), py::arg("branch") = py::none(),
+          py::arg("alpha") = py::none(), py::arg("beta") = py::none());
+    m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("dres") = py::none());
+    m.def("rope_qknorm_fwd", &rope_qknorm_fwd);
+    m.def("rope_qknorm_bwd", &rope_qknorm_bwd);
+    m.def("route", &route);
+    m.def("gather_rows", &gather_rows);
+    m.def("combine_fwd", &combine_fwd);
+    m.def("combine_bwd", &combine_bwd);
+    m.def("activation_fwd", &activation_fwd, py::arg("pre"), py::arg("name"), py::arg("meta") = py::none());
+    m.def("activation_bwd", &activation_bwd, py::arg("dact"), py::arg("pre"), py::arg("name"), py::arg("meta") = py::none());
+    m.def("ce_fwd_bwd", &ce_fwd_bwd);
+    m.def("adamw", &adamw);
+    m.def("muon_prepare", &muon_prepare);
+    m.def("muon_apply", &muon_apply);
+    m.def("cast_bf16", &cast_bf16);
 }
 
 }  // namespace gm

@@ -1,0 +1,284 @@
+// Mixture-of-experts data movement: counted top-k routing into a padded expert-major layout, row gather,
+// gated combine (forward / backward) and the expert activation (forward / backward).
+//
+// Layout produced by routing: the S = M*k (token, slot) pairs are bucketed by expert, order inside a bucket
+// is the original slot order (stable, no atomics decide placement), and every bucket is padded to a multiple
+// of 128 rows.  Consequences: a 128-row GEMM tile never straddles two experts, the weight-gradient GEMM can
+// contract over whole padded segments, and pad rows are written as zeros so they contribute nothing.
+//   dest[slot]        row of the packed buffer that holds this (token, slot)
+//   src_of_row[row]   slot stored in that row, -1 for pad rows
+//   seg_ends[e]       cumulative padded end of expert e;  counts[e] the true row count
+//   tile_expert[t]    expert of the t-th 128-row tile;  meta[0] = number of tiles, meta[1] = padded rows
+// Reference counterparts: `model/feedforward/routing.py:12-96` (histogram -> prefix -> stable permutation),
+// `model/linear/fp8/custom/grouped.py:57-72` (per-expert padding to 128), `experiments/053-fused-expert-output-combine.patch`.
+#include "../common/ptx.cuh"
+#include "../kernels_decl.h"
+
+namespace gm {
+
+constexpr int ROUTE_CHUNK = 1024;
+constexpr int MAX_EXPERTS = 128;
+
+__global__ void __launch_bounds__(ROUTE_CHUNK)
+route_count_kernel(const long long* __restrict__ idx, int* __restrict__ chunk_hist, int slots, int experts) {
+    __shared__ int hist[MAX_EXPERTS];
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    const int slot = blockIdx.x * ROUTE_CHUNK + threadIdx.x;
+    if (slot < slots) atomicAdd(&hist[static_cast<int>(idx[slot])], 1);
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) chunk_hist[blockIdx.x * experts + e] = hist[e];
+}
+
+// single block: per-expert prefix over chunks, padded segment plan, tile table, pad rows marked -1
+__global__ void __launch_bounds__(128)
+route_plan_kernel(const int* __restrict__ chunk_hist, int* __restrict__ chunk_start, int* __restrict__ counts,
+                  int* __restrict__ seg_ends, int* __restrict__ tile_expert, int* __restrict__ meta,
+                  int* __restrict__ src_of_row, int chunks, int experts) {
+    __shared__ int cnt[MAX_EXPERTS], pstart[MAX_EXPERTS + 1];
+    const int e = threadIdx.x;
+    if (e < experts) {
+        int c = 0;
+        for (int ch = 0; ch < chunks; ++ch) c += chunk_hist[ch * experts + e];
+        cnt[e] = c;
+        counts[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int i = 0; i < experts; ++i) {
+            pstart[i] = acc;
+            acc += (cnt[i] + 127) / 128 * 128;
+            seg_ends[i] = acc;
+        }
+        pstart[experts] = acc;
+        meta[0] = acc / 128;
+        meta[1] = acc;
+    }
+    __syncthreads();
+    if (e < experts) {
+        int run = pstart[e];
+        for (int ch = 0; ch < chunks; ++ch) {
+            chunk_start[ch * experts + e] = run;
+            run += chunk_hist[ch * experts + e];
+        }
+        for (int r = pstart[e] + cnt[e]; r < pstart[e + 1]; ++r) src_of_row[r] = -1;
+        for (int t = pstart[e] / 128; t < pstart[e + 1] / 128; ++t) tile_expert[t] = e;
+    }
+}
+
+__global__ void __launch_bounds__(ROUTE_CHUNK)
+route_place_kernel(const long long* __restrict__ idx, const int* __restrict__ chunk_start, int* __restrict__ dest,
+                   int* __restrict__ src_of_row, int slots, int experts) {
+    __shared__ int warp_count[32][MAX_EXPERTS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < 32 * MAX_EXPERTS; i += blockDim.x) (&warp_count[0][0])[i] = 0;
+    __syncthreads();
+    const int slot = blockIdx.x * ROUTE_CHUNK + threadIdx.x;
+    const int e = slot < slots ? static_cast<int>(idx[slot]) : experts;     // `experts` = sentinel for idle lanes
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(same & ((1u << lane) - 1u));
+    if (e < experts && rank == 0) warp_count[warp][e] = __popc(same);
+    __syncthreads();
+    if (threadIdx.x < experts) {           // exclusive prefix over the 32 warps, per expert
+        int run = 0;
+        for (int w = 0; w < 32; ++w) {
+            const int c = warp_count[w][threadIdx.x];
+            warp_count[w][threadIdx.x] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    if (e < experts) {
+        const int row = chunk_start[blockIdx.x * experts + e] + warp_count[warp][e] + rank;
+        dest[slot] = row;
+        src_of_row[row] = slot;
+    }
+}
+
+bool launch_route(const long long* idx, int slots, int experts, int* chunk_hist, int* chunk_start, int* counts, int* seg_ends,
+                  int* tile_expert, int* meta, int* dest, int* src_of_row, cudaStream_t s) {
+    if (experts > MAX_EXPERTS || slots <= 0) return false;
+    const int chunks = (slots + ROUTE_CHUNK - 1) / ROUTE_CHUNK;
+    route_count_kernel<<<chunks, ROUTE_CHUNK, 0, s>>>(idx, chunk_hist, slots, experts);
+    route_plan_kernel<<<1, 128, 0, s>>>(chunk_hist, chunk_start, counts, seg_ends, tile_expert, meta, src_of_row, chunks, experts);
+    route_place_kernel<<<chunks, ROUTE_CHUNK, 0, s>>>(idx, chunk_start, dest, src_of_row, slots, experts);
+    return true;
+}
+
+// packed[row] = hidden[src_of_row[row] / k] (zeros for pad rows); one warp per row, 16-byte vectors
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const __nv_bfloat16* __restrict__ hidden, const int* __restrict__ src_of_row, const int* __restrict__ meta,
+                   __nv_bfloat16* __restrict__ packed, int d, int top_k, int cap_rows) {
+    const int lane = threadIdx.x & 31;
+    const int total = min(meta[1], cap_rows);
+    for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total; row += gridDim.x * 8) {
+        const int src = src_of_row[row];
+        uint4* out = reinterpret_cast<uint4*>(packed + static_cast<long long>(row) * d);
+        if (src < 0) {
+            for (int i = lane; i < d / 8; i += 32) out[i] = make_uint4(0, 0, 0, 0);
+        } else {
+            const uint4* in = reinterpret_cast<const uint4*>(hidden + static_cast<long long>(src / top_k) * d);
+            for (int i = lane; i < d / 8; i += 32) out[i] = in[i];
+        }
+    }
+}
+
+void launch_gather_rows(const void* hidden, const int* src_of_row, const int* meta, void* packed, int d, int top_k, int cap_rows,
+                        cudaStream_t s) {
+    gather_rows_kernel<<<1184, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(hidden), src_of_row, meta,
+                                            static_cast<__nv_bfloat16*>(packed), d, top_k, cap_rows);
+}
+
+// out[t] = sum_k gates[t,k] * y[dest[t*k+k']]   (fp32 accumulation, bf16 result); one warp per token
+__global__ void __launch_bounds__(256)
+combine_fwd_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ dest, const float* __restrict__ gates,
+                   __nv_bfloat16* __restrict__ out, int tokens, int d, int top_k) {
+    const int lane = threadIdx.x & 31;
+    for (int t = blockIdx.x * 8 + (threadIdx.x >> 5); t < tokens; t += gridDim.x * 8) {
+        for (int i = lane; i < d / 8; i += 32) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int k = 0; k < top_k; ++k) {
+                const float g = gates[t * top_k + k];
+                const uint4 raw = *reinterpret_cast<const uint4*>(y + static_cast<long long>(dest[t * top_k + k]) * d + i * 8);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(h[e]);
+                    acc[2 * e] += g * f.x;
+                    acc[2 * e + 1] += g * f.y;
+                }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+            o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+            *reinterpret_cast<uint4*>(out + static_cast<long long>(t) * d + i * 8) = o;
+        }
+    }
+}
+
+// per packed row: dy[row] = gate * dout[token] (zeros for pad rows), dgate[slot] = <dout[token], y[row]>
+__global__ void __launch_bounds__(256)
+combine_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ y, const int* __restrict__ src_of_row,
+                   const float* __restrict__ gates, const int* __restrict__ meta, __nv_bfloat16* __restrict__ dy,
+                   float* __restrict__ dgates, int d, int top_k, int cap_rows) {
+    const int lane = threadIdx.x & 31;
+    const int total = min(meta[1], cap_rows);
+    for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total; row += gridDim.x * 8) {
+        const int src = src_of_row[row];
+        uint4* o = reinterpret_cast<uint4*>(dy + static_cast<long long>(row) * d);
+        if (src < 0) {
+            for (int i = lane; i < d / 8; i += 32) o[i] = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        const float g = gates[src];
+        const uint4* gin = reinterpret_cast<const uint4*>(dout + static_cast<long long>(src / top_k) * d);
+        const uint4* yin = reinterpret_cast<const uint4*>(y + static_cast<long long>(row) * d);
+        float dot = 0.f;
+        for (int i = lane; i < d / 8; i += 32) {
+            const uint4 a = gin[i], b = yin[i];
+            const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+            const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+            uint4 w;
+            uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 fa = __bfloat1622float2(ha[e]), fb = __bfloat1622float2(hb[e]);
+                dot += fa.x * fb.x + fa.y * fb.y;
+                wp[e] = pack_bf16x2(g * fa.x, g * fa.y);
+            }
+            o[i] = w;
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
+        if (lane == 0) dgates[src] = dot;
+    }
+}
+
+void launch_combine_fwd(const void* y, const int* dest, const float* gates, void* out, int tokens, int d, int top_k, cudaStream_t s) {
+    combine_fwd_kernel<<<1184, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(y), dest, gates, static_cast<__nv_bfloat16*>(out), tokens, d, top_k);
+}
+void launch_combine_bwd(const void* dout, const void* y, const int* src_of_row, const float* gates, const int* meta, void* dy,
+                        float* dgates, int d, int top_k, int cap_rows, cudaStream_t s) {
+    combine_bwd_kernel<<<1184, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(y), src_of_row,
+                                            gates, meta, static_cast<__nv_bfloat16*>(dy), dgates, d, top_k, cap_rows);
+}
+
+// ---- activations ---------------------------------------------------------------------------------------
+// kind: 0 gelu (erf), 1 relu, 2 relu^2, 3 silu, 4 swiglu (pre = [gate | up], gate first).
+__device__ __forceinline__ float act_fwd(int kind, float x) {
+    switch (kind) {
+        case 0: return 0.5f * x * (1.f + erff(x * 0.70710678118f));
+        case 1: return fmaxf(x, 0.f);
+        case 2: { const float r = fmaxf(x, 0.f); return r * r; }
+        default: return x / (1.f + __expf(-x));
+    }
+}
+__device__ __forceinline__ float act_grad(int kind, float x) {
+    switch (kind) {
+        case 0: return 0.5f * (1.f + erff(x * 0.70710678118f)) + x * 0.3989422804f * __expf(-0.5f * x * x);
+        case 1: return x > 0.f ? 1.f : 0.f;
+        case 2: return 2.f * fmaxf(x, 0.f);
+        default: { const float s = 1.f / (1.f + __expf(-x)); return s * (1.f + x * (1.f - s)); }
+    }
+}
+
+// rows limited by meta[1] when meta != nullptr (padded expert rows), else by `rows`
+__global__ void __launch_bounds__(256)
+activation_fwd_kernel(const __nv_bfloat16* __restrict__ pre, __nv_bfloat16* __restrict__ act, const int* __restrict__ meta,
+                      int rows, int h, int kind) {
+    const int total = meta ? min(meta[1], rows) : rows;
+    const int per_row = h / 2;
+    const long long n = static_cast<long long>(total) * per_row;
+    const int in_w = kind == 4 ? 2 * h : h;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = i / per_row;
+        const int c = static_cast<int>(i - r * per_row) * 2;
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pre + r * in_w + c));
+        float2 o;
+        if (kind == 4) {
+            const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pre + r * in_w + h + c));
+            o.x = act_fwd(3, a.x) * u.x;
+            o.y = act_fwd(3, a.y) * u.y;
+        } else {
+            o.x = act_fwd(kind, a.x);
+            o.y = act_fwd(kind, a.y);
+        }
+        *reinterpret_cast<__nv_bfloat162*>(act + r * h + c) = __floats2bfloat162_rn(o.x, o.y);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+activation_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ pre, __nv_bfloat16* __restrict__ dpre,
+                      const int* __restrict__ meta, int rows, int h, int kind) {
+    const int total = meta ? min(meta[1], rows) : rows;
+    const int per_row = h / 2;
+    const long long n = static_cast<long long>(total) * per_row;
+    const int in_w = kind == 4 ? 2 * h : h;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = i / per_row;
+        const int c = static_cast<int>(i - r * per_row) * 2;
+        const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dact + r * h + c));
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pre + r * in_w + c));
+        if (kind == 4) {
+            const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pre + r * in_w + h + c));
+            *reinterpret_cast<__nv_bfloat162*>(dpre + r * in_w + c) =
+                __floats2bfloat162_rn(g.x * u.x * act_grad(3, a.x), g.y * u.y * act_grad(3, a.y));
+            *reinterpret_cast<__nv_bfloat162*>(dpre + r * in_w + h + c) =
+                __floats2bfloat162_rn(g.x * act_fwd(3, a.x), g.y * act_fwd(3, a.y));
+        } else {
+            *reinterpret_cast<__nv_bfloat162*>(dpre + r * in_w + c) =
+                __floats2bfloat162_rn(g.x * act_grad(kind, a.x), g.y * act_grad(kind, a.y));
+        }
+    }
+}
+
+void launch_activation_fwd(const void* pre, void* act, const int* meta, int rows, int h, int kind, cudaStream_t s) {
+    activation_fwd_kernel<<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(act), meta, rows, h, kind);
+}
+void launch_activation_bwd(const void* dact, const void* pre, void* dpre, const int* meta, int rows, int h, int kind, cudaStream_t s) {
+    activation_bwd_kernel<<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dact), static_cast<const __nv_bfloat16*>(pre),
+                                               static_cast<__nv_bfloat16*>(dpre), meta, rows, h, kind);
+}
+
+}  // namespace gm

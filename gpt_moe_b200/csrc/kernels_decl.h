@@ -19,4 +19,27 @@ bool launch_rope_qknorm(bool bwd, int D, const void* x, const void* dy, void* ou
                         int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin,
                         float smax, cudaStream_t s);
 
+// fused/moe.cu
+bool launch_route(const long long* idx, int slots, int experts, int* chunk_hist, int* chunk_start, int* counts, int* seg_ends,
+                  int* tile_expert, int* meta, int* dest, int* src_of_row, cudaStream_t s);
+void launch_gather_rows(const void* hidden, const int* src_of_row, const int* meta, void* packed, int d, int top_k, int cap_rows,
+                        cudaStream_t s);
+void launch_combine_fwd(const void* y, const int* dest, const float* gates, void* out, int tokens, int d, int top_k, cudaStream_t s);
+void launch_combine_bwd(const void* dout, const void* y, const int* src_of_row, const float* gates, const int* meta, void* dy,
+                        float* dgates, int d, int top_k, int cap_rows, cudaStream_t s);
+void launch_activation_fwd(const void* pre, void* act, const int* meta, int rows, int h, int kind, cudaStream_t s);
+void launch_activation_bwd(const void* dact, const void* pre, void* dpre, const int* meta, int rows, int h, int kind, cudaStream_t s);
+
+// fused/loss_optim.cu
+void launch_ce_fwd_bwd(void* logits, const long long* targets, float* loss, const float* grad_scale, int rows, int vocab,
+                       long long row_stride, long long ignore_index, int write_grad, cudaStream_t s);
+void launch_adamw(float* p, const float* g, void* m, void* v, bool moments_bf16, void* p_bf16, long long n, float lr, float beta1,
+                  float beta2, float eps, float wd, float bc1, float bc2_sqrt, float grad_scale, cudaStream_t s);
+void launch_muon_prepare(const float* const* grads, float* const* bufs, void* packed, float* sumsq, int n_mats, int rows, int cols,
+                         long long g_stride, long long b_stride, float momentum, int nesterov, int transpose, float grad_scale,
+                         cudaStream_t s);
+void launch_muon_apply(float* const* weights, void* const* weights_bf16, const void* update, int n_mats, int rows, int cols,
+                       long long w_stride, float alpha, int transpose, cudaStream_t s);
+void launch_cast_bf16(const float* src, void* dst, long long n, cudaStream_t s);
+
 }  // namespace gm

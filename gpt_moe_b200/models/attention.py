@@ -84,6 +84,22 @@ class SelfAttention(nn.Module):
 
     def project_qkv(self, x: Tensor):
         b, t, _ = x.shape
+        d, hq, hk = self.head_size, self.n_heads, self.n_kv_heads
+        if x.is_cuda and self.q_proj.bias is None and d in (32, 64, 128) and hq + hk <= 64:
+            # one GEMM over the concatenated q/k/v weights, then RoPE + QK-norm in place on the packed rows
+            from ..ops import cuda_ops
+            qkv = cuda_ops.linear_multi(x, (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight), self.q_proj.precision)
+            cos = sin = None
+            if self.rotary is not None:
+                cos, sin = self.rotary.cos_cached[:t], self.rotary.sin_cached[:t]
+            qkv = cuda_ops.rope_qk_norm_packed(
+                qkv.view(b * t, -1), cos, sin, self.q_scale if self.use_qk_norm else None,
+                self.k_scale if self.use_qk_norm else None, t, hq, hk, d, self.qk_eps, self.qk_norm_type == "rms",
+                self.qk_scale_min, self.qk_scale_max).view(b, t, -1)
+            q = qkv[..., : hq * d].unflatten(-1, (hq, d))
+            k = qkv[..., hq * d: (hq + hk) * d].unflatten(-1, (hk, d))
+            v = qkv[..., (hq + hk) * d:].unflatten(-1, (hk, d))
+            return q, k, v
         q = self.q_proj(x).view(b, t, self.n_heads, self.head_size)
         k = self.k_proj(x).view(b, t, self.n_kv_heads, self.head_size)
         v = self.v_proj(x).view(b, t, self.n_kv_heads, self.head_size)

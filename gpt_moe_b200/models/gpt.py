@@ -131,6 +131,12 @@ class GPT(nn.Module):
         self.set_precision_phase("training")
         self.engine = None      # set by parallel.ddp_engine when the model is placed on a GPU
 
+    def set_sliding_window(self, window: int) -> None:
+        """Update the device-resident window and remember the host value (ops that need a host integer read
+        it from the buffer's `host_value` attribute instead of synchronising)."""
+        self.sliding_window_size.fill_(int(window))
+        self.sliding_window_size.host_value = int(window)
+
     # ---- precision phases ---------------------------------------------------------------------
     def set_precision_phase(self, phase: str) -> None:
         if phase == self.precision_phase:

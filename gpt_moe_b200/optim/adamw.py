@@ -22,6 +22,18 @@ class AdamW(torch.optim.Optimizer):
         super().__init__(params, defaults)
         self.moment_dtype = moment_dtype
 
+    def state_dict(self):
+        """torch layout; the device-side `step` tensors are synchronised with the host counters first."""
+        for group in self.param_groups:
+            for p in group["params"]:
+                state = self.state.get(p)
+                if state and "_host_step" in state:
+                    state["step"].fill_(float(state["_host_step"]))
+        sd = super().state_dict()
+        for state in sd["state"].values():
+            state.pop("_host_step", None)
+        return sd
+
     def _init_state(self, p: torch.Tensor) -> dict:
         state = self.state[p]
         if not state:

@@ -214,7 +214,7 @@ class Trainer:
         if state is not None:
             for key, value in state.items():
                 setattr(self, key, value)
-        self.raw_gpt_model.sliding_window_size.fill_(self.current_window_size)
+        self.raw_gpt_model.set_sliding_window(self.current_window_size)
 
     def schedule_state(self) -> Dict[str, int]:
         keys = ("swa_schedule_idx", "current_window_size", "next_swa_update_tokens", "batch_schedule_idx",
@@ -227,7 +227,7 @@ class Trainer:
         return model(indices, targets, attn_mask=attn_mask, ignore_doc_mask=ignore_doc_mask, document_ids=document_ids)
 
     def _to_device(self, t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
-        if t is None or self.device_type != "cuda":
+        if t is None or self.device_type != "cuda" or t.is_cuda:
             return t
         if not t.is_pinned():
             t = t.pin_memory()
@@ -280,7 +280,7 @@ class Trainer:
             self.swa_schedule_idx += 1
             self.current_window_size = cfg.swa_schedule_values[self.swa_schedule_idx]
             self.next_swa_update_tokens = get_next_update_tokens(cfg.swa_schedule_keys, self.swa_schedule_idx, cfg.max_tokens)
-        raw.sliding_window_size.fill_(self.current_window_size)
+        raw.set_sliding_window(self.current_window_size)
         for group in self.optimizers["adamw"].param_groups:
             group["lr"] = adamw_lr
         if "muon" in self.optimizers:

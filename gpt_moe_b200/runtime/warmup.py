@@ -52,7 +52,7 @@ def kernel_warmup(run, num_train_steps: int = 2) -> float:
     trainer.train_tokens_processed = saved[0]
     for key, value in saved[1].items():
         setattr(trainer, key, value)
-    run.raw_gpt_model.sliding_window_size.fill_(trainer.current_window_size)
+    run.raw_gpt_model.set_sliding_window(trainer.current_window_size)
     du.barrier()
     elapsed = du.max_over_ranks(time.time() - t0, run.device)
     if run.master_process:

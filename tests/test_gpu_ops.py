@@ -1,0 +1,201 @@
+"""GPU kernels against the plain-PyTorch fp32 definitions in `ops.reference`.
+
+Tolerances follow the reference's check scripts (`experiments/check_grouped.py:73-82`): relative L2 of
+6e-3 for bf16 results, 1e-5 for fp32 statistics.
+"""
+import pytest
+import torch
+
+from gpt_moe_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+BF16_TOL = 6e-3
+
+
+def rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from gpt_moe_b200.ops import cuda_ops
+    cuda_ops.ext().reset_status()
+    yield cuda_ops
+    cuda_ops.check_status()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (1000, 776, 200), (4096, 2304, 768), (300, 8, 768), (64, 512, 128)])
+def test_gemm_all_majors(ops, m, n, k):
+    torch.manual_seed(0)
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = torch.randn(n, k, device="cuda").bfloat16()
+    want = a.float() @ b.float().t()
+    for a_mn in (False, True):
+        for b_mn in (False, True):
+            if (a_mn and m % 8) or (b_mn and n % 8):
+                continue
+            d = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+            ops.ext().gemm_bf16(a.t().contiguous() if a_mn else a, b.t().contiguous() if b_mn else b, d, a_mn, b_mn)
+            assert rel(d, want) < BF16_TOL, (a_mn, b_mn)
+
+
+def test_gemm_epilogue_batched_grouped(ops):
+    torch.manual_seed(1)
+    c = ops.ext()
+    a = torch.randn(3, 256, 128, device="cuda").bfloat16()
+    b = torch.randn(3, 512, 128, device="cuda").bfloat16()
+    add = torch.randn(3, 256, 512, device="cuda").bfloat16()
+    d = torch.empty(3, 256, 512, device="cuda", dtype=torch.bfloat16)
+    c.gemm_bf16(a, b, d, False, False, 0.5, 2.0, add)
+    assert rel(d, 0.5 * torch.bmm(a.float(), b.float().transpose(1, 2)) + 2.0 * add.float()) < BF16_TOL
+    acc = torch.ones(256, 512, device="cuda")
+    c.gemm_bf16(a[0], b[0], acc, False, False, 1.0, 0.0, None, True)
+    assert rel(acc, 1 + a[0].float() @ b[0].float().t()) < 1e-5
+    # ragged expert segments with an empty expert (counts padded to 128 by construction)
+    counts, e, n, k = [0, 128, 384, 256], 4, 512, 256
+    rows = sum(counts)
+    x = torch.randn(rows, k, device="cuda").bfloat16()
+    w = torch.randn(e, n, k, device="cuda").bfloat16()
+    tiles = torch.tensor(sum([[i] * (cnt // 128) for i, cnt in enumerate(counts)], []), dtype=torch.int32, device="cuda")
+    meta = torch.tensor([rows // 128, rows], dtype=torch.int32, device="cuda")
+    y = torch.zeros(rows, n, device="cuda", dtype=torch.bfloat16)
+    c.gemm_bf16(x, w, y, False, False, 1.0, 0.0, None, False, 1, tiles, meta, None)
+    starts = [0, 0, 128, 512]
+    want = torch.cat([x[s:s + cnt].float() @ w[i].float().t() for i, (s, cnt) in enumerate(zip(starts, counts))])
+    assert rel(y, want) < BF16_TOL
+    dy = torch.randn(rows, n, device="cuda").bfloat16()
+    ends = torch.tensor([0, 128, 512, 768], dtype=torch.int32, device="cuda")
+    dw = torch.full((e, n, k), 7.0, device="cuda")
+    c.gemm_bf16(dy, x, dw, True, True, 1.0, 0.0, None, False, 2, None, None, ends)
+    want = torch.stack([dy[s:s + cnt].float().t() @ x[s:s + cnt].float() for s, cnt in zip(starts, counts)])
+    assert rel(dw, want) < 1e-5
+    assert dw[0].abs().max().item() == 0.0       # empty expert: exact zeros
+
+
+@pytest.mark.parametrize("d,dtype", [(768, torch.float32), (1024, torch.bfloat16), (128, torch.float32)])
+def test_rmsnorm(ops, d, dtype):
+    torch.manual_seed(2)
+    x = torch.randn(4, 100, d, device="cuda").to(dtype).requires_grad_()
+    w = (1 + 0.1 * torch.randn(d, device="cuda")).requires_grad_()
+    y = ops.rms_norm(x, w, 1e-6)
+    g = torch.randn_like(y)
+    y.backward(g)
+    x2, w2 = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    y2 = ref.rms_norm(x2, w2, 1e-6)
+    y2.backward(g.float())
+    assert rel(y, y2) < BF16_TOL and rel(x.grad, x2.grad) < BF16_TOL and rel(w.grad, w2.grad) < BF16_TOL
+
+
+@pytest.mark.parametrize("d,rms", [(64, True), (32, False), (128, True)])
+def test_rope_qknorm(ops, d, rms):
+    torch.manual_seed(3)
+    b, t, hq, hk = 2, 96, 4, 2
+    q = torch.randn(b, t, hq, d, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(b, t, hk, d, device="cuda").bfloat16().requires_grad_()
+    qs = torch.tensor([1.0, 0.5, 6.0, 2.0], device="cuda").view(1, hq, 1, 1).requires_grad_()   # 6.0 is clamped at 5
+    ks = torch.tensor([1.5, 0.7], device="cuda").view(1, hk, 1, 1).requires_grad_()
+    cos, sin = ref.rope_tables(d, 10000.0, t, device="cuda")
+    oq, ok = ops.rope_qk_norm(q, k, cos, sin, qs, ks, 1e-6, rms, float("-inf"), 5.0)
+    gq, gk = torch.randn_like(oq), torch.randn_like(ok)
+    (oq.float() * gq.float()).sum().add((ok.float() * gk.float()).sum()).backward()
+    q2, k2 = q.detach().float().requires_grad_(), k.detach().float().requires_grad_()
+    qs2, ks2 = qs.detach().clone().requires_grad_(), ks.detach().clone().requires_grad_()
+    rq, rk = ref.rope_qk_norm(q2, k2, cos, sin, qs2, ks2, 1e-6, rms, float("-inf"), 5.0)
+    ((rq * gq.float()).sum() + (rk * gk.float()).sum()).backward()
+    assert rel(oq, rq) < BF16_TOL and rel(ok, rk) < BF16_TOL
+    assert rel(q.grad, q2.grad) < 1.5e-2 and rel(k.grad, k2.grad) < 1.5e-2
+    assert rel(qs.grad, qs2.grad) < 1.5e-2 and rel(ks.grad, ks2.grad) < 1.5e-2
+    assert qs.grad.view(-1)[2].item() == 0.0       # clamped scale receives no gradient
+
+
+@pytest.mark.parametrize("top_k,experts,act", [(1, 8, "swiglu"), (2, 4, "relu2"), (2, 16, "swiglu")])
+def test_moe_experts(ops, top_k, experts, act):
+    torch.manual_seed(4)
+    m, d, h = 1000, 128, 256
+    up_w = 2 * h if act == "swiglu" else h
+    hidden = torch.randn(m, d, device="cuda").bfloat16().requires_grad_()
+    logits = torch.randn(m, experts, device="cuda")
+    logits[:, 1] = -1e4                                   # expert 1 stays empty
+    top_idx, gates, _ = ref.router_gates(logits, top_k, False)
+    gates = gates.detach().requires_grad_()
+    ups = [torch.randn(up_w, d, device="cuda").mul_(0.05).requires_grad_() for _ in range(experts)]
+    downs = [torch.randn(d, h, device="cuda").mul_(0.05).requires_grad_() for _ in range(experts)]
+    out = ops.moe_experts(hidden, top_idx, gates, ups, downs, None, None, act, "default", "default")
+    g = torch.randn_like(out)
+    out.backward(g)
+    from gpt_moe_b200.ops import api
+    hid2 = hidden.detach().float().cpu().requires_grad_()
+    gates2 = gates.detach().cpu().requires_grad_()
+    ups2 = [w.detach().bfloat16().float().cpu().requires_grad_() for w in ups]
+    downs2 = [w.detach().bfloat16().float().cpu().requires_grad_() for w in downs]
+    want = api.moe_experts(hid2, top_idx.cpu(), gates2, ups2, downs2, None, None, act, "default", "default")
+    want.backward(g.float().cpu())
+    assert rel(out.cpu(), want) < 1e-2
+    assert rel(hidden.grad.cpu(), hid2.grad) < 2e-2 and rel(gates.grad.cpu(), gates2.grad) < 2e-2
+    for a, b in zip(ups + downs, ups2 + downs2):
+        assert rel(a.grad.cpu(), b.grad) < 2e-2
+    assert ups[1].grad.abs().max().item() == 0.0          # empty expert: exact zero gradient
+
+
+def test_linear_cross_entropy(ops):
+    torch.manual_seed(5)
+    rows, d, vocab = 300, 128, 50304
+    x = torch.randn(rows, d, device="cuda").bfloat16().requires_grad_()
+    w = torch.randn(vocab, d, device="cuda").mul_(0.02).requires_grad_()
+    targets = torch.randint(0, vocab, (rows,), device="cuda")
+    targets[::7] = -100
+    loss = ops.linear_cross_entropy(x, w, targets, -100)
+    loss.backward()
+    x2 = x.detach().float().requires_grad_()
+    w2 = w.detach().bfloat16().float().requires_grad_()
+    want = ref.linear_cross_entropy(x2, w2, targets, -100)
+    want.backward()
+    assert abs(loss.item() - want.item()) < 2e-3
+    assert rel(x.grad, x2.grad) < 2e-2 and rel(w.grad, w2.grad) < 2e-2
+
+
+def test_polar_express_gemms(ops):
+    """The tcgen05 Polar Express against the same iteration in torch bf16 (same rounding regime) and fp32."""
+    torch.manual_seed(6)
+    for shape in [(3, 256, 256), (2, 256, 1024), (1, 768, 3072)]:
+        g = torch.randn(shape, device="cuda")
+        x = (g / (g.norm(dim=(-2, -1), keepdim=True) * 1.02 + 1e-6)).bfloat16()
+        got = ops.polar_express_bf16(x.clone())
+        same_regime = ref.polar_express(g, dtype=torch.bfloat16)
+        exact = ref.polar_express(g, dtype=torch.float32)
+        assert rel(got, same_regime) < 5e-2, shape
+        assert rel(got, exact) < 1.5e-1, shape
+        sv = torch.linalg.svdvals(got.float())
+        inside = ((sv > 0.5) & (sv < 1.3)).float().mean().item()      # the smallest few singular values converge last
+        assert sv.max().item() < 1.3 and inside > 0.95, (shape, inside, sv.max().item())
+
+
+def test_adamw_and_muon_steps(ops):
+    from gpt_moe_b200.optim import AdamW, Muon
+    torch.manual_seed(7)
+    shapes = [(256, 256), (512, 256), (256, 1024), (8, 256), (768, 256)]
+    ps = [torch.randn(s).mul_(0.02) for s in shapes]
+    gs = [torch.randn(s) for s in shapes]
+    gpu = [p.clone().cuda().requires_grad_() for p in ps]
+    for p, g in zip(gpu, gs):
+        p.grad = g.clone().cuda()
+    opt = Muon(gpu, lr=0.02, momentum=0.95, nesterov=True, backend="polarexpress")
+    opt.step()
+    for p, p0, g in zip(gpu, ps, gs):
+        # first step: buf = g, u = g + 0.95 g; the update is -lr*sqrt(max(shape)) * polar(u); (768,256) is split into 3 squares
+        u = (g * 1.95).cuda()
+        parts = u.split(u.shape[1]) if u.shape[0] == 3 * u.shape[1] else [u]
+        want = torch.cat([ref.polar_express(q, dtype=torch.bfloat16).float() * (-0.02 * max(q.shape) ** 0.5) for q in parts])
+        assert rel(p.detach() - p0.cuda(), want) < 6e-2, tuple(p.shape)
+        assert rel(opt.state[p]["momentum_buffer"], g.cuda()) < 1e-6
+    cpu = [p.clone().requires_grad_() for p in ps]
+    gpu = [p.clone().cuda().requires_grad_() for p in ps]
+    ac, ag = AdamW(cpu, lr=1e-2, weight_decay=0.1), AdamW(gpu, lr=1e-2, weight_decay=0.1)
+    for _ in range(3):
+        for c, g_, gr in zip(cpu, gpu, gs):
+            c.grad, g_.grad = gr.clone(), gr.clone().cuda()
+        ac.step(); ag.step()
+    for c, g_, p0 in zip(cpu, gpu, ps):
+        assert rel(g_.detach().cpu() - p0, c.detach() - p0) < 1e-4
+    assert float(ag.state_dict()["state"][0]["step"]) == 3.0
