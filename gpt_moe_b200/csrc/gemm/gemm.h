@@ -18,6 +18,7 @@ struct GemmParams {
     long long ldc, c_batch_stride;
     float alpha, beta;
     int out_fp32, accumulate;    // accumulate: D += result (fp32 output only)
+    int split_k;                 // >1: the K loop is shared by this many CTAs per tile, partials meet in a TMA reduce-add (fp32 output)
     const int* tile_expert;      // GROUPED_M: expert of each 128-row tile
     const int* num_m_tiles;      // GROUPED_M: number of 128-row tiles (device scalar)
     const int* seg_ends;         // GROUPED_K: cumulative padded row ends per expert
@@ -33,7 +34,7 @@ bool make_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, uint64_
                      uint64_t row_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_cols, uint32_t box_rows,
                      int swizzle_bytes);
 
-cudaError_t launch_gemm_bf16(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, bool a_mn, bool b_mn,
-                             int sms, cudaStream_t stream);
+cudaError_t launch_gemm_bf16(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmParams& p, bool a_mn,
+                             bool b_mn, int sms, cudaStream_t stream);
 
 }  // namespace gm

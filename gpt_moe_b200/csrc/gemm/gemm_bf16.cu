@@ -4,8 +4,10 @@
 //   warp 0  : TMA producer   - fills a 4-stage ring of {A 128x64, B 256x64} bf16 tiles (128B swizzle)
 //   warp 1  : MMA issuer     - one thread issues tcgen05.mma (M128 N256 K16) into one of two TMEM
 //                              accumulators (2 x 256 columns), commits to free the smem stage
-//   warps 2-5: epilogue      - tcgen05.ld the finished accumulator (thread = row), scale / add C /
-//                              accumulate, convert, store; overlaps the next tile's main loop
+//   warps 2-5: epilogue      - tcgen05.ld the finished accumulator (thread = row), scale / add C, convert,
+//                              stage 128-byte-swizzled slabs in shared memory and hand them to TMA
+//                              (store, or reduce-add for fp32 accumulation and split-K); overlaps the
+//                              next tile's main loop.  TMA clips rows/columns outside the tensor.
 // Operands may be K-major ([rows, K] with K contiguous) or MN-major ([K, rows] with rows
 // contiguous); both are read straight from row-major tensors by TMA, so forward (X W^T), input
 // gradient (dY W) and weight gradient (dY^T X) all run without a transposed copy.
@@ -30,12 +32,14 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int GEMM_THREADS = 192;
 constexpr int GROUP_M = 8;
 constexpr uint32_t TMEM_COLS = 512;
+constexpr int STAGING_BYTES = 2 * BM * 128;      // two slabs of [128 rows][128 bytes]
 
 struct TileCoord {
     int m0, n0;        // element offsets of the tile in the output
     int az, bz, dz;    // z (batch / expert) coordinates for A, B, D
     int k_begin, k_blocks;
     int m_limit, n_limit;
+    bool store_zeros;  // no contraction work at all for this output tile: write zeros unless accumulating
 };
 
 __device__ __forceinline__ int total_tiles(const GemmParams& p, int& m_tiles, int& n_tiles) {
@@ -45,11 +49,16 @@ __device__ __forceinline__ int total_tiles(const GemmParams& p, int& m_tiles, in
         return m_tiles * n_tiles;
     }
     m_tiles = (p.M + BM - 1) / BM;
-    return m_tiles * n_tiles * p.batch;
+    return m_tiles * n_tiles * p.batch * p.split_k;
 }
 
 __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, int m_tiles, int n_tiles) {
     TileCoord t;
+    int split = 0;
+    if (p.mode != GEMM_GROUPED_M && p.split_k > 1) {
+        split = tile % p.split_k;
+        tile /= p.split_k;
+    }
     const int per_batch = m_tiles * n_tiles;
     const int z = (p.mode == GEMM_GROUPED_M) ? 0 : tile / per_batch;
     int r = tile - z * per_batch;
@@ -78,15 +87,26 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, i
         t.k_begin = begin;
         t.k_blocks = (p.seg_ends[z] - begin) / BK;
     }
+    t.store_zeros = t.k_blocks == 0;
+    if (p.split_k > 1) {          // contiguous share of the K blocks; partial results meet in a TMA reduce-add
+        const int per = (t.k_blocks + p.split_k - 1) / p.split_k;
+        const int first = min(split * per, t.k_blocks);
+        const int count = min(per, t.k_blocks - first);
+        t.k_begin += first * BK;
+        t.k_blocks = count;
+        t.store_zeros = false;
+    }
     return t;
 }
 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_d, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint8_t* staging = smem + STAGES * STAGE_BYTES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(staging + STAGING_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;
     uint64_t* acc_empty = acc_full + 2;
@@ -99,6 +119,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_d);
     }
     if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
@@ -168,90 +189,115 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
     } else {
         const int quad = warp & 3;                  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+        const int row_in_tile = quad * 32 + lane;
+        const bool leader = threadIdx.x == 64;      // first epilogue thread issues the TMA stores
+        const int elem = p.out_fp32 ? 4 : 2;
+        const int chunks_per_round = p.out_fp32 ? 2 : 4;          // 32-column accumulator chunks staged per round
+        const int rounds = (BN / 32) / chunks_per_round;
+        const int cols_per_slab = 128 / elem;
+        const bool reduce = p.accumulate || p.split_k > 1;
+        uint8_t* my_row = staging + row_in_tile * 128;
+        const int sw = row_in_tile & 7;
         int acc = 0; uint32_t acc_ph = 0;
         for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
             const TileCoord t = tile_coord(p, tile, m_tiles, n_tiles);
-            const int row = t.m0 + quad * 32 + lane;
-            const bool row_ok = row < t.m_limit;
-            const long long row_off = static_cast<long long>(t.dz) * p.d_batch_stride + static_cast<long long>(row) * p.ldd;
             const bool have_acc = t.k_blocks != 0;
+            if (!have_acc && !(t.store_zeros && !p.accumulate)) continue;      // nothing to add, nothing to clear
+            const int row = t.m0 + row_in_tile;
+            const bool row_ok = row < t.m_limit;
             if (have_acc) {
                 if (!mbar_wait(&acc_full[acc], acc_ph)) { atomicExch(p.status, 104); ok = false; break; }
                 tc_fence_after();
             }
-            for (int chunk = 0; chunk < BN / 32; ++chunk) {
-                const int col0 = t.n0 + chunk * 32;
-                if (col0 >= t.n_limit) break;      // uniform across the CTA
-                uint32_t r[32];
-                if (have_acc) {
-                    tmem_ld_32x32b_x32(tmem_base + acc * BN + chunk * 32 + (static_cast<uint32_t>(quad * 32) << 16), r);
-                    tmem_ld_wait();
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = 0u;
-                }
-                if (!row_ok) continue;
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-                const bool full_chunk = col0 + 32 <= t.n_limit;
-                if (p.C != nullptr) {
-                    const __nv_bfloat16* c = reinterpret_cast<const __nv_bfloat16*>(p.C) +
-                        static_cast<long long>(t.dz) * p.c_batch_stride + static_cast<long long>(row) * p.ldc + col0;
-                    if (full_chunk) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            const uint4 q = *reinterpret_cast<const uint4*>(c + j);
-                            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float2 f = __bfloat1622float2(h[e]);
-                                v[j + 2 * e] += p.beta * f.x;
-                                v[j + 2 * e + 1] += p.beta * f.y;
-                            }
-                        }
+            for (int round = 0; round < rounds; ++round) {
+                const int round_col0 = t.n0 + round * chunks_per_round * 32;
+                if (round_col0 >= t.n_limit) break;                           // uniform across the CTA
+                if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                asm volatile("bar.sync 1, 128;" ::: "memory");                 // staging buffer is free again
+                for (int cc = 0; cc < chunks_per_round; ++cc) {
+                    const int chunk = round * chunks_per_round + cc;
+                    const int col0 = t.n0 + chunk * 32;
+                    uint32_t r[32];
+                    if (have_acc) {
+                        tmem_ld_32x32b_x32(tmem_base + acc * BN + chunk * 32 + (static_cast<uint32_t>(quad * 32) << 16), r);
+                        tmem_ld_wait();
                     } else {
-                        for (int j = 0; j < 32 && col0 + j < t.n_limit; ++j) v[j] += p.beta * __bfloat162float(c[j]);
-                    }
-                }
-                if (p.out_fp32) {
-                    float* d = reinterpret_cast<float*>(p.D) + row_off + col0;
-                    if (full_chunk) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                            if (p.accumulate) {
-                                const float4 old = *reinterpret_cast<const float4*>(d + j);
-                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                        for (int j = 0; j < 32; ++j) r[j] = 0u;
+                    }
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+                    if (p.C != nullptr && row_ok && col0 < t.n_limit) {
+                        const __nv_bfloat16* c = reinterpret_cast<const __nv_bfloat16*>(p.C) +
+                            static_cast<long long>(t.dz) * p.c_batch_stride + static_cast<long long>(row) * p.ldc + col0;
+                        if (col0 + 32 <= t.n_limit) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                const uint4 q = *reinterpret_cast<const uint4*>(c + j);
+                                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float2 f = __bfloat1622float2(h[e]);
+                                    v[j + 2 * e] += p.beta * f.x;
+                                    v[j + 2 * e + 1] += p.beta * f.y;
+                                }
                             }
-                            *reinterpret_cast<float4*>(d + j) = o;
-                        }
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < t.n_limit; ++j) d[j] = p.accumulate ? d[j] + v[j] : v[j];
-                    }
-                } else {
-                    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + row_off + col0;
-                    if (full_chunk) {
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < t.n_limit) v[j] += p.beta * __bfloat162float(c[j]);
+                        }
+                    }
+                    // 16-byte pieces of this thread's row go to piece index (i ^ row%8) of the 128-byte slab row
+                    if (p.out_fp32) {
+                        uint8_t* slab = my_row + cc * (BM * 128);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            *reinterpret_cast<float4*>(slab + ((q ^ sw) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    } else {
+                        uint8_t* slab = my_row + (cc >> 1) * (BM * 128);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
                             uint4 o;
-                            o.x = pack_bf16x2(v[j], v[j + 1]);
-                            o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                            o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-                            o.w = pack_bf16x2(v[j + 6], v[j + 7]);
-                            *reinterpret_cast<uint4*>(d + j) = o;
+                            o.x = pack_bf16x2(v[8 * q], v[8 * q + 1]);
+                            o.y = pack_bf16x2(v[8 * q + 2], v[8 * q + 3]);
+                            o.z = pack_bf16x2(v[8 * q + 4], v[8 * q + 5]);
+                            o.w = pack_bf16x2(v[8 * q + 6], v[8 * q + 7]);
+                            *reinterpret_cast<uint4*>(slab + ((((cc & 1) * 4 + q) ^ sw) << 4)) = o;
                         }
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < t.n_limit; ++j) d[j] = __float2bfloat16(v[j]);
                     }
+                }
+                if (have_acc && round == rounds - 1) {                        // accumulator fully read: release it early
+                    tc_fence_before();
+                    mbar_arrive(&acc_empty[acc]);
+                }
+                fence_proxy_async();
+                asm volatile("bar.sync 1, 128;" ::: "memory");                 // slabs complete and visible to the async proxy
+                if (leader) {
+                    for (int sl = 0; sl < 2; ++sl) {
+                        const int col = round_col0 + sl * cols_per_slab;
+                        if (col >= t.n_limit) break;
+                        const uint32_t src = smem_u32(staging + sl * (BM * 128));
+                        if (reduce) {
+                            asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4}], [%1];"
+                                         ::"l"(&tmap_d), "r"(src), "r"(col), "r"(t.m0), "r"(t.dz) : "memory");
+                        } else {
+                            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                                         ::"l"(&tmap_d), "r"(src), "r"(col), "r"(t.m0), "r"(t.dz) : "memory");
+                        }
+                    }
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
             if (have_acc) {
-                tc_fence_before();
-                mbar_arrive(&acc_empty[acc]);
+                // tiles narrower than BN leave the round loop early: the accumulator is released here in that case
+                const int rounds_done = min(rounds, (t.n_limit - t.n0 + chunks_per_round * 32 - 1) / (chunks_per_round * 32));
+                if (rounds_done < rounds) { tc_fence_before(); mbar_arrive(&acc_empty[acc]); }
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
         }
+        if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     // common teardown: every path (including a timed-out wait) reaches it, so TMEM is always released
@@ -268,10 +314,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
 }
 
-constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 template <bool A_MN, bool B_MN>
-static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms, cudaStream_t stream) {
+static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmParams& p, int sms,
+                                  cudaStream_t stream) {
     auto kernel = gemm_bf16_kernel<A_MN, B_MN>;
     static bool configured = false;
     if (!configured) {
@@ -279,14 +326,14 @@ static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, 
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    kernel<<<sms, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
+    kernel<<<sms, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, td, p);
     return cudaGetLastError();
 }
 
-cudaError_t launch_gemm_bf16(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, bool a_mn, bool b_mn,
-                             int sms, cudaStream_t stream) {
-    if (a_mn) return b_mn ? launch_variant<true, true>(ta, tb, p, sms, stream) : launch_variant<true, false>(ta, tb, p, sms, stream);
-    return b_mn ? launch_variant<false, true>(ta, tb, p, sms, stream) : launch_variant<false, false>(ta, tb, p, sms, stream);
+cudaError_t launch_gemm_bf16(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmParams& p, bool a_mn,
+                             bool b_mn, int sms, cudaStream_t stream) {
+    if (a_mn) return b_mn ? launch_variant<true, true>(ta, tb, td, p, sms, stream) : launch_variant<true, false>(ta, tb, td, p, sms, stream);
+    return b_mn ? launch_variant<false, true>(ta, tb, td, p, sms, stream) : launch_variant<false, false>(ta, tb, td, p, sms, stream);
 }
 
 }  // namespace gm

@@ -73,6 +73,20 @@ def test_gemm_epilogue_batched_grouped(ops):
     assert dw[0].abs().max().item() == 0.0       # empty expert: exact zeros
 
 
+def test_gemm_split_k_weight_gradient(ops):
+    """Few output tiles and a long contraction: the K loop is shared by several CTAs and reduced by TMA."""
+    torch.manual_seed(8)
+    tokens, n, k = 8192, 256, 384
+    dy = torch.randn(tokens, n, device="cuda").bfloat16()
+    x = torch.randn(tokens, k, device="cuda").bfloat16()
+    want = dy.float().t() @ x.float()
+    dw = torch.full((n, k), 3.0, device="cuda")
+    ops.ext().gemm_bf16(dy, x, dw, True, True)
+    assert rel(dw, want) < 1e-5
+    ops.ext().gemm_bf16(dy, x, dw, True, True, 1.0, 0.0, None, True)
+    assert rel(dw, 2 * want) < 1e-5
+
+
 @pytest.mark.parametrize("d,dtype", [(768, torch.float32), (1024, torch.bfloat16), (128, torch.float32)])
 def test_rmsnorm(ops, d, dtype):
     torch.manual_seed(2)
