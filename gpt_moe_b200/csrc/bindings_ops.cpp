@@ -61,6 +61,20 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const OptTens
     return {dx, dw};
 }
 
+// backward of x_new = x + beta*branch: returns (dbranch bf16, dbeta fp32[1])
+std::vector<Tensor> residual_bwd(const Tensor& dxn, const Tensor& branch, const Tensor& beta) {
+    c10::cuda::CUDAGuard guard(dxn.device());
+    GM_CHECK(dxn.scalar_type() == torch::kFloat32 && dxn.is_contiguous() && dxn.numel() % 4 == 0, "dxn must be contiguous fp32");
+    check_bf16(branch, "branch");
+    GM_CHECK(beta.scalar_type() == torch::kFloat32 && beta.numel() == 1, "beta must be one fp32 value");
+    Tensor dbranch = torch::empty_like(branch);
+    Tensor partial = torch::empty({residual_bwd_blocks(dxn.numel())}, dxn.options());
+    Tensor dbeta = torch::empty({1}, dxn.options());
+    launch_residual_bwd(dxn.data_ptr<float>(), branch.data_ptr(), beta.data_ptr<float>(), dbranch.data_ptr(), partial.data_ptr<float>(),
+                        dbeta.data_ptr<float>(), dxn.numel(), stream());
+    return {dbranch, dbeta};
+}
+
 // qkv: [tokens, row_stride] bf16 holding q heads then k heads (then anything else) of width D each.
 // forward writes rotated+normalised q,k into `out` (same layout; may alias a separate buffer)
 void rope_qknorm_fwd(const Tensor& x, Tensor& out, const OptTensor& cos_t, const OptTensor& sin_t, const OptTensor& q_scale,
@@ -212,7 +226,7 @@ void muon_prepare(const Tensor& grad_ptrs, const Tensor& buf_ptrs, Tensor& packe
     c10::cuda::CUDAGuard guard(packed.device());
     check_bf16(packed, "packed");
     const int n = grad_ptrs.numel();
-    GM_CHECK(packed.numel() == n * rows * cols && (rows * cols) % 2 == 0, "packed buffer shape");
+    GM_CHECK(packed.numel() == n * rows * cols && (rows * cols) % 8 == 0, "packed buffer shape");
     launch_muon_prepare(reinterpret_cast<const float* const*>(grad_ptrs.data_ptr<int64_t>()),
                         reinterpret_cast<float* const*>(buf_ptrs.data_ptr<int64_t>()), packed.data_ptr(), sumsq.data_ptr<float>(), n,
                         rows, cols, g_stride, b_stride, momentum, nesterov, transpose, grad_scale, stream());
@@ -241,6 +255,7 @@ void register_kernels(pybind11::module_& m) {
     m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("eps"), py::arg("branch") = py::none(),
           py::arg("alpha") = py::none(), py::arg("beta") = py::none());
     m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("dres") = py::none());
+    m.def("residual_bwd", &residual_bwd);
     m.def("rope_qknorm_fwd", &rope_qknorm_fwd);
     m.def("rope_qknorm_bwd", &rope_qknorm_bwd);
     m.def("route", &route);

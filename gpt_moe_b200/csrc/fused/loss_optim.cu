@@ -122,32 +122,46 @@ void launch_adamw(float* p, const float* g, void* m, void* v, bool moments_bf16,
 // For matrix i of a same-shape bucket (pointer tables on the device):
 //   buf = momentum*buf + g ;  u = nesterov ? g + momentum*buf : buf ;  packed[i] = bf16(u), transposed if tall
 // and per-matrix sum of squares of bf16(u) (for the Frobenius normalisation) accumulated into sumsq[i].
+// 32x32 tiles through shared memory keep both the row-major reads and the (possibly transposed) writes coalesced.
 __global__ void __launch_bounds__(256)
 muon_prepare_kernel(const float* const* __restrict__ grads, float* const* __restrict__ bufs, __nv_bfloat16* __restrict__ packed,
                     float* __restrict__ sumsq, int rows, int cols, long long g_stride, long long b_stride, float momentum,
                     int nesterov, int transpose, float grad_scale) {
-    const int mat = blockIdx.y;
+    __shared__ float tile[32][33];
+    __shared__ float part[8];
+    const int mat = blockIdx.z;
     const float* g = grads[mat];
     float* buf = bufs[mat];
-    const long long n = static_cast<long long>(rows) * cols;
-    __nv_bfloat16* out = packed + mat * n;
+    __nv_bfloat16* out = packed + static_cast<long long>(mat) * rows * cols;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
     float local = 0.f;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int r = static_cast<int>(i / cols), c = static_cast<int>(i - static_cast<long long>(r) * cols);
-        const float grad = g[r * g_stride + c] * grad_scale;
-        float b = buf[r * b_stride + c] * momentum;
-        b = b + grad;
-        buf[r * b_stride + c] = b;
-        const float u = nesterov ? fmaf(momentum, b, grad) : b;
-        const __nv_bfloat16 q = __float2bfloat16(u);
-        out[transpose ? static_cast<long long>(c) * rows + r : i] = q;
-        const float qf = __bfloat162float(q);
-        local += qf * qf;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = r0 + ty + 8 * i, c = c0 + tx;
+        float u = 0.f;
+        if (r < rows && c < cols) {
+            const float grad = g[r * g_stride + c] * grad_scale;
+            float b = buf[r * b_stride + c] * momentum;
+            b = b + grad;
+            buf[r * b_stride + c] = b;
+            u = __bfloat162float(__float2bfloat16(nesterov ? fmaf(momentum, b, grad) : b));
+            if (!transpose) out[static_cast<long long>(r) * cols + c] = __float2bfloat16(u);
+        }
+        tile[ty + 8 * i][tx] = u;
+        local += u * u;
+    }
+    if (transpose) {
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = c0 + ty + 8 * i, r = r0 + tx;          // out is [cols][rows]
+            if (r < rows && c < cols) out[static_cast<long long>(c) * rows + r] = __float2bfloat16(tile[tx][ty + 8 * i]);
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-    __shared__ float part[8];
-    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = local;
+    if (tx == 0) part[ty] = local;
     __syncthreads();
     if (threadIdx.x == 0) {
         float t = 0.f;
@@ -161,10 +175,16 @@ __global__ void __launch_bounds__(256)
 muon_normalize_kernel(__nv_bfloat16* __restrict__ packed, const float* __restrict__ sumsq, long long per_matrix) {
     const int mat = blockIdx.y;
     const float inv = 1.f / (sqrtf(sumsq[mat]) * 1.02f + 1e-6f);
-    __nv_bfloat162* x = reinterpret_cast<__nv_bfloat162*>(packed + mat * per_matrix);
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < per_matrix / 2; i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const float2 f = __bfloat1622float2(x[i]);
-        x[i] = __floats2bfloat162_rn(f.x * inv, f.y * inv);
+    uint4* x = reinterpret_cast<uint4*>(packed + mat * per_matrix);
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < per_matrix / 8; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        uint4 raw = x[i];
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            h[e] = __floats2bfloat162_rn(f.x * inv, f.y * inv);
+        }
+        x[i] = raw;
     }
 }
 
@@ -172,17 +192,30 @@ muon_normalize_kernel(__nv_bfloat16* __restrict__ packed, const float* __restric
 __global__ void __launch_bounds__(256)
 muon_apply_kernel(float* const* __restrict__ weights, __nv_bfloat16* const* __restrict__ weights_bf16,
                   const __nv_bfloat16* __restrict__ update, int rows, int cols, long long w_stride, float alpha, int transpose) {
-    const int mat = blockIdx.y;
+    __shared__ float tile[32][33];
+    const int mat = blockIdx.z;
     float* w = weights[mat];
     __nv_bfloat16* wb = weights_bf16 ? weights_bf16[mat] : nullptr;
-    const long long n = static_cast<long long>(rows) * cols;
-    const __nv_bfloat16* o = update + mat * n;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int r = static_cast<int>(i / cols), c = static_cast<int>(i - static_cast<long long>(r) * cols);
-        const float upd = __bfloat162float(o[transpose ? static_cast<long long>(c) * rows + r : i]);
-        const float nw = w[r * w_stride + c] + alpha * upd;
-        w[r * w_stride + c] = nw;
-        if (wb) wb[r * w_stride + c] = __float2bfloat16(nw);
+    const __nv_bfloat16* o = update + static_cast<long long>(mat) * rows * cols;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    if (transpose) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = c0 + ty + 8 * i, r = r0 + tx;          // update is [cols][rows]
+            tile[ty + 8 * i][tx] = (r < rows && c < cols) ? __bfloat162float(o[static_cast<long long>(c) * rows + r]) : 0.f;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = r0 + ty + 8 * i, c = c0 + tx;
+        if (r < rows && c < cols) {
+            const float upd = transpose ? tile[tx][ty + 8 * i] : __bfloat162float(o[static_cast<long long>(r) * cols + c]);
+            const float nw = w[r * w_stride + c] + alpha * upd;
+            w[r * w_stride + c] = nw;
+            if (wb) wb[r * w_stride + c] = __float2bfloat16(nw);
+        }
     }
 }
 
@@ -190,16 +223,16 @@ void launch_muon_prepare(const float* const* grads, float* const* bufs, void* pa
                          long long g_stride, long long b_stride, float momentum, int nesterov, int transpose, float grad_scale,
                          cudaStream_t s) {
     const long long n = static_cast<long long>(rows) * cols;
-    dim3 grid(static_cast<unsigned>(std::min<long long>((n + 255) / 256, 592LL)), n_mats);
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32, n_mats);
     muon_prepare_kernel<<<grid, 256, 0, s>>>(grads, bufs, static_cast<__nv_bfloat16*>(packed), sumsq, rows, cols, g_stride, b_stride,
                                              momentum, nesterov, transpose, grad_scale);
-    muon_normalize_kernel<<<grid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(packed), sumsq, n);
+    dim3 grid2(static_cast<unsigned>(std::min<long long>((n / 8 + 255) / 256, 592LL)), n_mats);
+    muon_normalize_kernel<<<grid2, 256, 0, s>>>(static_cast<__nv_bfloat16*>(packed), sumsq, n);
 }
 
 void launch_muon_apply(float* const* weights, void* const* weights_bf16, const void* update, int n_mats, int rows, int cols,
                        long long w_stride, float alpha, int transpose, cudaStream_t s) {
-    const long long n = static_cast<long long>(rows) * cols;
-    dim3 grid(static_cast<unsigned>(std::min<long long>((n + 255) / 256, 592LL)), n_mats);
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32, n_mats);
     muon_apply_kernel<<<grid, 256, 0, s>>>(weights, reinterpret_cast<__nv_bfloat16* const*>(weights_bf16),
                                            static_cast<const __nv_bfloat16*>(update), rows, cols, w_stride, alpha, transpose);
 }

@@ -136,13 +136,58 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const TX* __restrict__ 
     }
 }
 
-// out[col] = sum over rows of partial[row][col]  (second pass of the deterministic column reductions)
-__global__ void column_sum_kernel(const float* __restrict__ partial, float* __restrict__ out, int rows, int cols, int accumulate) {
-    const int col = blockIdx.x * blockDim.x + threadIdx.x;
-    if (col >= cols) return;
+// out[col] = sum over rows of partial[row][col]  (second pass of the deterministic column reductions).
+// Each block owns 32 columns; 8 warps stride over the rows and combine through shared memory in a fixed order.
+__global__ void __launch_bounds__(256)
+column_sum_kernel(const float* __restrict__ partial, float* __restrict__ out, int rows, int cols, int accumulate) {
+    __shared__ float red[8][32];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int col = blockIdx.x * 32 + tx;
     float s = 0.f;
-    for (int r = 0; r < rows; ++r) s += partial[static_cast<long long>(r) * cols + col];
-    out[col] = accumulate ? out[col] + s : s;
+    if (col < cols)
+        for (int r = ty; r < rows; r += 8) s += partial[static_cast<long long>(r) * cols + col];
+    red[ty][tx] = s;
+    __syncthreads();
+    if (ty == 0 && col < cols) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += red[w][tx];
+        out[col] = accumulate ? out[col] + t : t;
+    }
+}
+
+// Backward of x_new = x + beta * branch with respect to the branch and beta:
+//   dbranch = bf16(beta * dxn),  partial[block] = sum(dxn * branch)   (fixed-order block partials)
+__global__ void __launch_bounds__(256)
+residual_bwd_kernel(const float* __restrict__ dxn, const __nv_bfloat16* __restrict__ branch, const float* __restrict__ beta,
+                    __nv_bfloat16* __restrict__ dbranch, float* __restrict__ partial, long long n) {
+    __shared__ float red[8];
+    const float b = *beta;
+    float dot = 0.f;
+    for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 4; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
+        const float4 g = *reinterpret_cast<const float4*>(dxn + i);
+        const float4 r = load4<__nv_bfloat16>(branch + i);
+        dot += g.x * r.x + g.y * r.y + g.z * r.z + g.w * r.w;
+        store4<__nv_bfloat16>(dbranch + i, make_float4(b * g.x, b * g.y, b * g.z, b * g.w));
+    }
+    dot = warp_sum(dot);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = dot;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += red[w];
+        partial[blockIdx.x] = t;
+    }
+}
+
+int residual_bwd_blocks(long long n) { return static_cast<int>(n / 4 / 256 + 1 < 1184 ? n / 4 / 256 + 1 : 1184); }
+
+void launch_residual_bwd(const float* dxn, const void* branch, const float* beta, void* dbranch, float* partial, float* dbeta,
+                         long long n, cudaStream_t s) {
+    const int blocks = residual_bwd_blocks(n);
+    residual_bwd_kernel<<<blocks, 256, 0, s>>>(dxn, static_cast<const __nv_bfloat16*>(branch), beta, static_cast<__nv_bfloat16*>(dbranch), partial, n);
+    column_sum_kernel<<<1, 256, 0, s>>>(partial, dbeta, blocks, 1, 0);
 }
 
 bool norm_dim_supported(int d) {
@@ -201,12 +246,12 @@ bool launch_rmsnorm_bwd(const void* dy, const void* x, bool x_fp32, const float*
     }
     GM_DISPATCH_CHUNKS(d, GM_BWD)
 #undef GM_BWD
-    if (dw_partial) column_sum_kernel<<<(d + 255) / 256, 256, 0, s>>>(dw_partial, dw, blocks, d, dw_accumulate);
+    if (dw_partial) column_sum_kernel<<<(d + 31) / 32, 256, 0, s>>>(dw_partial, dw, blocks, d, dw_accumulate);
     return true;
 }
 
 void launch_column_sum(const float* partial, float* out, int rows, int cols, int accumulate, cudaStream_t s) {
-    column_sum_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, out, rows, cols, accumulate);
+    column_sum_kernel<<<(cols + 31) / 32, 256, 0, s>>>(partial, out, rows, cols, accumulate);
 }
 
 // ---- RoPE + QK-norm ---------------------------------------------------------------------------------------

@@ -12,6 +12,9 @@ bool launch_rmsnorm_fwd(const void* x, bool x_fp32, const void* branch, const fl
 int rmsnorm_bwd_blocks(int rows);
 bool launch_rmsnorm_bwd(const void* dy, const void* x, bool x_fp32, const float* w, const float* rstd, const void* dres, void* dx,
                         float* dw_partial, float* dw, int dw_accumulate, int rows, int d, cudaStream_t s);
+int residual_bwd_blocks(long long n);
+void launch_residual_bwd(const float* dxn, const void* branch, const float* beta, void* dbranch, float* partial, float* dbeta,
+                         long long n, cudaStream_t s);
 void launch_column_sum(const float* partial, float* out, int rows, int cols, int accumulate, cudaStream_t s);
 int rope_blocks(long long tokens, int heads);
 bool launch_rope_qknorm(bool bwd, int D, const void* x, const void* dy, void* out, const float* cos_t, const float* sin_t,

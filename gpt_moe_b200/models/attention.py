@@ -96,10 +96,7 @@ class SelfAttention(nn.Module):
                 qkv.view(b * t, -1), cos, sin, self.q_scale if self.use_qk_norm else None,
                 self.k_scale if self.use_qk_norm else None, t, hq, hk, d, self.qk_eps, self.qk_norm_type == "rms",
                 self.qk_scale_min, self.qk_scale_max).view(b, t, -1)
-            q = qkv[..., : hq * d].unflatten(-1, (hq, d))
-            k = qkv[..., hq * d: (hq + hk) * d].unflatten(-1, (hk, d))
-            v = qkv[..., (hq + hk) * d:].unflatten(-1, (hk, d))
-            return q, k, v
+            return cuda_ops.split_qkv(qkv, hq, hk, d)
         q = self.q_proj(x).view(b, t, self.n_heads, self.head_size)
         k = self.k_proj(x).view(b, t, self.n_kv_heads, self.head_size)
         v = self.v_proj(x).view(b, t, self.n_kv_heads, self.head_size)

@@ -99,6 +99,10 @@ class GPT(nn.Module):
         if self.use_tied_embeddings:
             self.transformer.wte.weight = self.lm_head.weight
         self.apply(self._init_weights)
+        if ep_size > 1:
+            for block in self.transformer.h:
+                if block.use_moe:
+                    block.mlp.keep_local_experts()
 
         if stage_index is not None:
             assert not self.use_tied_embeddings, "pipeline parallelism requires untied embeddings"
@@ -235,7 +239,19 @@ class GPT(nn.Module):
 
         balance_loss = None
         grad_mode = self.training and torch.is_grad_enabled()
-        if self.activation_offloader is not None and grad_mode:
+        blocks = self.transformer.h
+        chain = (self.stage_index is None and isinstance(self.transformer.ln_f, nn.RMSNorm) and len(blocks) > 0
+                 and not (grad_mode and (self.use_activation_checkpointing or self.activation_offloader is not None)))
+        if chain:
+            # residual update + following RMSNorm as one op per link (see Block.forward_prenormed)
+            h = apply_norm(blocks[0].ln_1, x)
+            for i, block in enumerate(blocks):
+                next_norm = blocks[i + 1].ln_1 if i + 1 < len(blocks) else self.transformer.ln_f
+                x, h, block_balance = block.forward_prenormed(x, h, ctx, next_norm)
+                if block_balance is not None:
+                    balance_loss = block_balance if balance_loss is None else balance_loss + block_balance
+            x = h
+        elif self.activation_offloader is not None and grad_mode:
             x, balance_loss = self.activation_offloader.run(self.transformer.h, x, ctx)
         else:
             for block in self.transformer.h:
@@ -248,7 +264,8 @@ class GPT(nn.Module):
         if self.stage_index == 0:
             return (x, balance_loss) if balance_loss is not None else x
 
-        x = apply_norm(self.transformer.ln_f, x)
+        if not chain:
+            x = apply_norm(self.transformer.ln_f, x)
         ignore_index = self.pad_token_id if self.data_uses_padding else -100
         logits = None
         if targets is not None and (self.use_liger_loss or (x.is_cuda and self.training)):

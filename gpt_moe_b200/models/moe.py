@@ -36,13 +36,17 @@ class MoE(nn.Module):
         self.full_softmax_gating = gpt_config.moe_full_softmax_gating
         self.load_balance_weight = training_config.moe_load_balance_weight
         self.router = Linear(gpt_config.hidden_size, num_experts, role="router", bias=False)
-        # keys are global expert indices: experts.{e}.up_proj.weight
-        self.experts = nn.ModuleDict({
-            str(e): MLP(gpt_config, training_config)
-            for e in range(self.first_expert, self.first_expert + self.experts_per_rank)})
+        # keys are global expert indices: experts.{e}.up_proj.weight.  All experts are constructed so that the
+        # initial weights do not depend on the sharding; `keep_local_experts()` drops the others after init.
+        self.experts = nn.ModuleDict({str(e): MLP(gpt_config, training_config) for e in range(num_experts)})
         self.shared_expert = (MLP(gpt_config, training_config, hidden_dim=gpt_config.moe_shared_expert_hidden_dim)
                               if gpt_config.moe_shared_expert_hidden_dim > 0 else None)
         self.ep_group = None            # set by parallel.ep.attach_expert_parallel
+
+    def keep_local_experts(self) -> None:
+        for e in range(self.num_experts):
+            if not self.first_expert <= e < self.first_expert + self.experts_per_rank:
+                del self.experts[str(e)]
 
     def local_experts(self):
         return [self.experts[str(e)] for e in range(self.first_expert, self.first_expert + self.experts_per_rank)]

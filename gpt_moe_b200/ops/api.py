@@ -78,6 +78,15 @@ def rms_norm(x: Tensor, weight: Optional[Tensor], eps: float) -> Tensor:
     return ref.rms_norm(x, weight, eps)
 
 
+def residual_rms_norm(x: Tensor, branch: Tensor, alpha: Optional[Tensor], beta: Optional[Tensor], weight: Optional[Tensor],
+                      eps: float) -> Tuple[Tensor, Tensor]:
+    """x_new = alpha*x + beta*branch (alpha/beta None = 1) and rmsnorm(x_new); returns (x_new, normed)."""
+    if x.is_cuda:
+        return _cuda().residual_rms_norm(x, branch, alpha, beta, weight, eps)
+    x_new = (x if alpha is None else alpha * x) + (branch if beta is None else beta * branch).to(x.dtype)
+    return x_new, ref.rms_norm(x_new, weight, eps)
+
+
 def rope_qk_norm(q, k, cos, sin, q_scale, k_scale, eps, rms, scale_min, scale_max):
     if q.is_cuda:
         return _cuda().rope_qk_norm(q, k, cos, sin, q_scale, k_scale, eps, rms, scale_min, scale_max)

@@ -241,6 +241,76 @@ def rms_norm(x: Tensor, weight: Optional[Tensor], eps: float) -> Tensor:
     return _RMSNormFn.apply(x, weight, eps)
 
 
+class _ResidualRMSNormFn(torch.autograd.Function):
+    """x_new = x + beta * branch;  h = rmsnorm(x_new) * w.  One kernel forward; backward adds the norm's input
+    gradient onto the residual gradient in the norm-backward kernel and derives d(branch), d(beta) in one more pass."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, branch: Tensor, beta: Tensor, weight: Tensor, eps: float):
+        xc = x if x.is_contiguous() else x.contiguous()
+        br = branch if (branch.dtype == BF16 and branch.is_contiguous()) else branch.to(BF16).contiguous()
+        w = weight.detach().float()
+        b = beta.detach().float().reshape(1)
+        h, rstd, x_new = ext().rmsnorm_fwd(xc, w, eps, br, None, b)
+        ctx.save_for_backward(x_new, w, rstd, br, b)
+        ctx.meta = (beta.shape, beta.dtype, weight.dtype, beta.requires_grad)
+        return x_new, h
+
+    @staticmethod
+    def backward(ctx, dx_new: Optional[Tensor], dh: Optional[Tensor]):
+        x_new, w, rstd, br, b = ctx.saved_tensors
+        beta_shape, beta_dtype, w_dtype, beta_grad = ctx.meta
+        dw = None
+        if dh is not None:
+            dh = dh if (dh.dtype == BF16 and dh.is_contiguous()) else dh.to(BF16).contiguous()
+            res = None if dx_new is None else (dx_new if dx_new.is_contiguous() else dx_new.contiguous())
+            dxn, dw = ext().rmsnorm_bwd(dh, x_new, w, rstd, res)
+            dw = dw.to(w_dtype)
+        else:
+            dxn = dx_new.contiguous()
+        dbranch, dbeta = ext().residual_bwd(dxn, br, b)
+        return dxn, dbranch, (dbeta.reshape(beta_shape).to(beta_dtype) if beta_grad else None), dw, None
+
+
+def residual_rms_norm(x: Tensor, branch: Tensor, alpha: Optional[Tensor], beta: Optional[Tensor], weight: Tensor, eps: float):
+    """(x_new, rmsnorm(x_new)) with x_new = alpha*x + beta*branch.  The fused kernel covers the common case
+    (fp32 residual stream, no alpha); other cases compose the unfused ops."""
+    d = x.shape[-1]
+    fused = (alpha is None and x.dtype == torch.float32 and weight is not None and d % 128 == 0
+             and (d // 128) in (1, 2, 4, 6, 8, 12, 16) and x.numel() % 4 == 0)
+    if not fused:
+        x_new = (x if alpha is None else alpha * x) + (branch if beta is None else beta * branch)
+        return x_new, rms_norm(x_new, weight, eps)
+    if beta is None:
+        beta = torch.ones(1, device=x.device)
+    return _ResidualRMSNormFn.apply(x, branch, beta, weight, eps)
+
+
+class _SplitQKVFn(torch.autograd.Function):
+    """Views of the packed projection output as q, k, v; the backward assembles one packed gradient instead of
+    three zero-filled slice gradients."""
+
+    @staticmethod
+    def forward(ctx, qkv: Tensor, hq: int, hk: int, d: int):
+        ctx.cfg = (hq, hk, d, qkv.shape)
+        q = qkv[..., : hq * d].unflatten(-1, (hq, d))
+        k = qkv[..., hq * d: (hq + hk) * d].unflatten(-1, (hk, d))
+        v = qkv[..., (hq + hk) * d:].unflatten(-1, (hk, d))
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        hq, hk, d, shape = ctx.cfg
+        parts = []
+        for g, h in ((dq, hq), (dk, hk), (dv, hk)):
+            parts.append(g.flatten(-2) if g is not None else torch.zeros(shape[:-1] + (h * d,), dtype=BF16, device="cuda"))
+        return torch.cat(parts, dim=-1), None, None, None
+
+
+def split_qkv(qkv: Tensor, hq: int, hk: int, d: int):
+    return _SplitQKVFn.apply(qkv, hq, hk, d)
+
+
 # ---- RoPE + QK-norm ---------------------------------------------------------------------------------------------------
 class _RopeQKNormFn(torch.autograd.Function):
     """Operates on the packed projection output qkv[tokens, (Hq + Hk + Hv) * D]; q and k heads are rotated and
@@ -515,7 +585,7 @@ def polar_express_bf16(x: Tensor) -> Tensor:
 
 
 def muon_polar_step(work: List[Tuple[Tensor, Tensor, Tensor]], lr: float, momentum: float, nesterov: bool,
-                    max_batch: int = 16) -> None:
+                    max_batch: int = 128) -> None:
     """work: (weight fp32, gradient fp32, momentum buffer fp32) triples, all 2-D.  Same-shape matrices are
     processed together: momentum/Nesterov/bf16 pack (transposed when tall) -> normalise -> Polar Express ->
     W += -lr * sqrt(max(rows, cols)) * O."""
@@ -525,7 +595,7 @@ def muon_polar_step(work: List[Tuple[Tensor, Tensor, Tensor]], lr: float, moment
         buckets.setdefault((tuple(w.shape), w.stride(0), g.stride(0), buf.stride(0)), []).append((w, g, buf))
     for (shape, ws, gs, bs), items in buckets.items():
         rows, cols = shape
-        small = min(rows, cols) < 128 or rows % 8 or cols % 8 or (rows * cols) % 2
+        small = min(rows, cols) < 128 or rows % 8 or cols % 8
         for start in range(0, len(items), max_batch):
             batch = items[start: start + max_batch]
             n = len(batch)

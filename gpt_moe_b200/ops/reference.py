@@ -90,16 +90,17 @@ def rope_qk_norm(q: Tensor, k: Tensor, cos: Optional[Tensor], sin: Optional[Tens
 def softcap(scores: Tensor, cap: float, backend: str = "exact") -> Tensor:
     """cap * tanh(scores / cap) with the four tanh variants of the reference
     (`model/attention/logit_softcapping.py`): "exact"/"ptx" use tanh ("ptx" is `tanh.approx.f32`
-    on the GPU, exact here), "clamp" is a hard clip, "rational" is the Pade(3,2) approximant
-    x(27+x^2)/(27+9x^2) clipped to [-1, 1]."""
+    on the GPU, exact here), "clamp" is a hard clip, "rational" is z(27+z^2)/(27+9z^2)
+    with z clipped to [-3, 3], where the expression reaches exactly +-1."""
     if cap <= 0:
         return scores
     z = scores / cap
     if backend == "clamp":
         t = z.clamp(-1.0, 1.0)
     elif backend == "rational":
+        z = z.clamp(-3.0, 3.0)
         z2 = z * z
-        t = (z * (27.0 + z2) / (27.0 + 9.0 * z2)).clamp(-1.0, 1.0)
+        t = z * (27.0 + z2) / (27.0 + 9.0 * z2)
     else:
         t = torch.tanh(z)
     return cap * t
