@@ -1,0 +1,35 @@
+// Host-visible interface of the tcgen05 attention kernels (head size 64).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gm {
+
+struct AttnParams {
+    int batch, heads, seq_len;      // q heads
+    int group;                      // q heads per kv head
+    int q_col0, k_col0, v_col0;     // first column of head 0 inside each tensor map
+    int window;                     // inclusive look-back W (a query sees keys q-W..q); >= seq_len means plain causal
+    const int* window_ptr;          // optional device-resident window (overrides `window`)
+    float scale_log2e;              // softmax scale * log2(e)
+    float scale;                    // softmax scale
+    void* out;                      // forward: O [tokens, heads*64] bf16
+    long long out_stride;
+    float* lse;                     // [batch, heads, seq] natural-log LSE of the scaled scores
+    // backward
+    const float* delta;             // [batch, heads, seq] rowsum(dO * O)
+    float* dq_accum;                // [tokens, heads*64] fp32, zero-initialised; reduced into by TMA
+    void* dk;                       // [tokens, kv_heads*64] bf16
+    void* dv;
+    long long dkv_stride;
+    int* status;
+};
+
+cudaError_t launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t stream);
+
+cudaError_t launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                            const CUtensorMap& tdq, const AttnParams& p, const void* d_out, const void* out, long long do_stride,
+                            long long o_stride, float* delta, cudaStream_t stream);
+
+}  // namespace gm

@@ -1,0 +1,295 @@
+// Causal sliding-window attention forward for sm_100a, head size 64, bf16 in / bf16 out + fp32 log-sum-exp.
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the key tiles its rows can see:
+// keys kv with  q - W <= kv <= q  (window inclusive, W + 1 keys), tiles of 128 keys.
+//   S  = Q K^T          tcgen05.mma M128 N128 K64, accumulator in TMEM (128 columns)
+//   P  = exp2(S*c - m)  softmax warps read S from TMEM (thread = query row), mask token-exactly, keep running
+//                       max / sum in registers, write P back to TMEM as packed bf16 pairs (64 columns)
+//   PV = P V            tcgen05.mma M128 N64 K128 with A = P read from TMEM and V read MN-major straight from its
+//                       row-major shared-memory tile; accumulator in TMEM (64 columns)
+//   O  = O*alpha + PV   rescale-and-accumulate in registers (64 fp32 per row), normalise at the end
+// Q, K and V are read by TMA directly out of the packed projection output [tokens, (Hq+2Hkv)*64]; nothing is transposed.
+// Warp 8 is the control warp (TMA loads + MMA issue, one thread); warps 0-7 are the softmax warps: warps w and w+4
+// share the 32 query rows of TMEM quadrant w and split the key columns (and the output columns) between them; the two
+// halves of a row exchange only their running maximum, through shared memory, once per key tile.  K and V each use a
+// two-deep ring of shared-memory tiles refilled as soon as the MMA reading a tile has committed; two CTAs fit per SM
+// (80 KB shared memory, 256 TMEM columns each), so one CTA's softmax overlaps the other's MMAs.
+// Reference counterpart: FlexAttention with the causal + sliding-window BlockMask (model/gpt.py:311-687,
+// model/attention/self_attention.py:250-255); here the window test is exact per token in every tile.
+#include "../common/ptx.cuh"
+#include "attn.h"
+
+namespace gm {
+
+constexpr int AT_BM = 128, AT_BN = 128, AT_D = 64;
+constexpr int AT_THREADS = 288;
+constexpr int Q_BYTES = AT_BM * AT_D * 2, K_BYTES = AT_BN * AT_D * 2, V_BYTES = K_BYTES, P_BYTES = AT_BM * AT_BN * 2;
+constexpr uint32_t AT_TMEM_COLS = 256;
+constexpr int POLY_PER_8 = 3;     // of every 8 exponentials, how many run on the FMA pipe instead of MUFU
+constexpr int KV_STAGES = 2;      // key/value tiles in flight: the global->shared latency of a strided tile spans more than one tile of work
+
+// 2^x for x <= 0 on the FMA pipe: split x into integer and fraction, cubic minimax polynomial for 2^frac (max relative
+// error about 1e-4, below bf16 resolution), exponent added through the float's bit pattern.  The MUFU unit evaluates
+// only 16 exponentials per clock per SM, which for head size 64 is slower than the tensor cores; evaluating part of
+// every row here lets both pipes work at once.
+__device__ __forceinline__ float exp2_poly(float x) {
+    x = fmaxf(x, -125.f);
+    const float shifted = x + 12582912.f;                       // 1.5 * 2^23: the integer part lands in the low mantissa bits
+    const float xi = shifted - 12582912.f;
+    const float f = x - xi;                                     // f in [-0.5, 0.5]
+    float pl = fmaf(f, 0.0555041086f, 0.2402265069f);
+    pl = fmaf(pl, f, 0.6931471806f);
+    pl = fmaf(pl, f, 1.0f);
+    return __int_as_float(__float_as_int(pl) + (__float_as_int(shifted) << 23));
+}
+
+__device__ __forceinline__ void tma_load_2d_as3d(void* dst, const void* tmap, uint64_t* bar, int col, int row) {
+    tma_load_3d(dst, tmap, bar, col, row, 0);
+}
+
+// Softmax of one thread's 64 scores of the current key tile (two 32-column TMEM reads per pass).
+// Pass 1 finds the row maximum (combined with the other half of the row through shared memory); pass 2 forms the
+// exponentials, packs them to bf16 pairs and writes them to the P columns of TMEM.  MASK selects the token-exact
+// causal/window test; it is a template parameter so interior tiles carry no per-element compare or branch.
+template <bool MASK>
+__device__ __forceinline__ void softmax_tile(uint32_t s_addr, uint32_t p_addr, int kv0, int qpos, int window, float c, float m,
+                                             float* row_stat, int half, int r, int bar_id, float& tile_max, float& alpha,
+                                             float& base, float& row_sum) {
+    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+        uint32_t sreg[32];
+        tmem_ld_32x32b_x32(s_addr + cc * 32, sreg);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            float v = __uint_as_float(sreg[i]);
+            if (MASK) {
+                const int kpos = kv0 + cc * 32 + i;
+                v = (kpos > qpos || qpos - kpos > window) ? -INFINITY : v;
+            }
+            mx[i & 3] = fmaxf(mx[i & 3], v);
+        }
+    }
+    tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+    row_stat[half * AT_BM + r] = tile_max;
+    asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+    tile_max = fmaxf(tile_max, row_stat[(half ^ 1) * AT_BM + r]);
+    const float m_new = fmaxf(m, tile_max * c);
+    base = m_new == -INFINITY ? 0.f : m_new;                 // a row may have no visible key in this tile
+    alpha = exp2f(m - base);
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+        uint32_t sreg[32];
+        tmem_ld_32x32b_x32(s_addr + cc * 32, sreg);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            float e2[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                float v = __uint_as_float(sreg[i + u]);
+                if (MASK) {
+                    const int kpos = kv0 + cc * 32 + i + u;
+                    v = (kpos > qpos || qpos - kpos > window) ? -INFINITY : v;
+                }
+                const float arg = fmaf(v, c, -base);
+                e2[u] = ((i + u) % 8 < POLY_PER_8) ? exp2_poly(arg) : exp2f(arg);
+                sum[(i + u) & 3] += e2[u];
+            }
+            packed[i >> 1] = pack_bf16x2(e2[0], e2[1]);
+        }
+        tmem_st_32x32b_x16(p_addr + cc * 16, packed);
+    }
+    row_sum = (sum[0] + sum[1]) + (sum[2] + sum[3]);
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sq = smem;
+    uint8_t* sk = sq + Q_BYTES;                     // KV_STAGES key tiles
+    uint8_t* sv = sk + KV_STAGES * K_BYTES;         // KV_STAGES value tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sv + KV_STAGES * V_BYTES);
+    uint64_t* bar_q = bars + 0;
+    uint64_t* bar_s = bars + 1;
+    uint64_t* bar_p = bars + 2;
+    uint64_t* bar_o = bars + 3;
+    uint64_t* bar_k = bars + 4;                     // [KV_STAGES]
+    uint64_t* bar_v = bar_k + KV_STAGES;            // [KV_STAGES]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_v + KV_STAGES);
+    float* row_stat = reinterpret_cast<float*>(bars + 16);     // [2 halves][128 rows]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q_tile = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+    const int q0 = q_tile * AT_BM;
+    const int window = p.window_ptr ? *p.window_ptr : p.window;
+    int kv_lo = q0 - window;
+    if (kv_lo < 0) kv_lo = 0;
+    kv_lo &= ~(AT_BN - 1);
+    const int n_tiles = (q0 + AT_BM - kv_lo) / AT_BN;
+    const int kv_head = head / p.group;                       // grouped-query attention: several q heads share a kv head
+    const int row0 = batch * p.seq_len;
+    const int q_col = p.q_col0 + head * AT_D, k_col = p.k_col0 + kv_head * AT_D, v_col = p.v_col0 + kv_head * AT_D;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_q, 1); mbar_init(bar_s, 1); mbar_init(bar_p, 256); mbar_init(bar_o, 1);
+        for (int st = 0; st < KV_STAGES; ++st) { mbar_init(&bar_k[st], 1); mbar_init(&bar_v[st], 1); }
+        fence_barrier_init();
+    }
+    if (warp == 8) { tmem_alloc(tmem_slot, AT_TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base, tmem_p = tmem_base + AT_BN, tmem_pv = tmem_base + AT_BN + AT_BN / 2;
+    bool ok = true;
+
+    if (warp == 8) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc_bf16(AT_BM, AT_BN, false, false);
+            constexpr uint32_t idesc_pv = make_idesc_bf16(AT_BM, AT_D, false, true);
+            const uint32_t q_addr = smem_u32(sq), k_addr = smem_u32(sk), v_addr = smem_u32(sv);
+            auto issue_s = [&](int st) {
+#pragma unroll
+                for (int k4 = 0; k4 < AT_D / 16; ++k4)
+                    umma_f16(tmem_s, make_smem_desc(q_addr + k4 * 32, 16, 1024),
+                             make_smem_desc(k_addr + st * K_BYTES + k4 * 32, 16, 1024), idesc_s, k4 != 0);
+                umma_commit(bar_s);
+            };
+            auto load_k = [&](int tile) {
+                const int st = tile % KV_STAGES;
+                mbar_expect_tx(&bar_k[st], K_BYTES);
+                tma_load_2d_as3d(sk + st * K_BYTES, &tmap_k, &bar_k[st], k_col, row0 + kv_lo + tile * AT_BN);
+            };
+            auto load_v = [&](int tile) {
+                const int st = tile % KV_STAGES;
+                mbar_expect_tx(&bar_v[st], V_BYTES);
+                tma_load_2d_as3d(sv + st * V_BYTES, &tmap_v, &bar_v[st], v_col, row0 + kv_lo + tile * AT_BN);
+            };
+            mbar_expect_tx(bar_q, Q_BYTES);
+            tma_load_2d_as3d(sq, &tmap_q, bar_q, q_col, row0 + q0);
+            for (int t = 0; t < KV_STAGES && t < n_tiles; ++t) { load_k(t); load_v(t); }
+            if (!mbar_wait(bar_q, 0) || !mbar_wait(&bar_k[0], 0)) { atomicExch(p.status, 201); ok = false; }
+            if (ok) { tc_fence_after(); issue_s(0); }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const uint32_t ph = j & 1;
+                const int st = j % KV_STAGES;
+                const uint32_t st_ph = (j / KV_STAGES) & 1;
+                const bool more = j + 1 < n_tiles;
+                if (!mbar_wait(bar_s, ph)) { atomicExch(p.status, 202); ok = false; break; }
+                if (j + KV_STAGES < n_tiles) load_k(j + KV_STAGES);           // S_j has consumed its key tile: refill the stage
+                if (!mbar_wait(bar_p, ph) || !mbar_wait(&bar_v[st], st_ph)) { atomicExch(p.status, 203); ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int k8 = 0; k8 < AT_BN / 16; ++k8) {
+                    const uint64_t bdesc = make_smem_desc(v_addr + st * V_BYTES + k8 * 2048, AT_BN * 128, 1024);
+                    umma_f16_ta(tmem_pv, tmem_p + k8 * 8, bdesc, idesc_pv, k8 != 0);      // 16 keys = 8 packed columns
+                }
+                umma_commit(bar_o);
+                if (more) {
+                    const int nst = (j + 1) % KV_STAGES;
+                    if (!mbar_wait(&bar_k[nst], ((j + 1) / KV_STAGES) & 1)) { atomicExch(p.status, 204); ok = false; break; }
+                    tc_fence_after();
+                    issue_s(nst);
+                }
+                if (!mbar_wait(bar_o, ph)) { atomicExch(p.status, 205); ok = false; break; }
+                if (j + KV_STAGES < n_tiles) load_v(j + KV_STAGES);           // PV_j has consumed its value tile
+            }
+        }
+    } else {
+        const int quad = warp & 3, half = warp >> 2;         // TMEM lanes 32*quad..+31; key / output columns of this half
+        const int r = quad * 32 + lane;
+        const int qpos = q0 + r;
+        const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+        const float c = p.scale_log2e;
+        float m = -INFINITY, l = 0.f;
+        float o[AT_D / 2];
+#pragma unroll
+        for (int i = 0; i < AT_D / 2; ++i) o[i] = 0.f;
+        const int bar_id = 1 + quad;                             // pairs (w, w+4) meet on their own named barrier
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const uint32_t ph = j & 1;
+            const int kv0 = kv_lo + j * AT_BN + half * 64;
+            if (!mbar_wait(bar_s, ph)) { atomicExch(p.status, 206); ok = false; break; }
+            tc_fence_after();
+            // tiles strictly inside the band need no mask; the diagonal tile and the tile(s) at the window edge do
+            const int tile0 = kv_lo + j * AT_BN;
+            const bool need_mask = (tile0 + AT_BN - 1 > q0) || (q0 + AT_BM - 1 - tile0 > window);
+            float tile_max, alpha, base, row_sum;
+            if (need_mask) softmax_tile<true>(tmem_s + lane_off + half * 64, tmem_p + lane_off + half * 32, kv0, qpos, window, c, m,
+                                              row_stat, half, r, bar_id, tile_max, alpha, base, row_sum);
+            else softmax_tile<false>(tmem_s + lane_off + half * 64, tmem_p + lane_off + half * 32, kv0, qpos, window, c, m,
+                                     row_stat, half, r, bar_id, tile_max, alpha, base, row_sum);
+            const float m_new = fmaxf(m, tile_max * c);
+            tmem_st_wait();
+            l = l * alpha + row_sum;
+            m = m_new;
+            tc_fence_before();
+            mbar_arrive(bar_p);
+            if (!mbar_wait(bar_o, ph)) { atomicExch(p.status, 207); ok = false; break; }
+            tc_fence_after();
+            {
+                uint32_t oreg[32];
+                tmem_ld_32x32b_x32(tmem_pv + lane_off + half * 32, oreg);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = o[i] * alpha + __uint_as_float(oreg[i]);
+            }
+            tc_fence_before();
+            asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");     // partner has read this tile's maximum
+        }
+        if (ok) {
+            row_stat[half * AT_BM + r] = l;
+            asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+            l += row_stat[(half ^ 1) * AT_BM + r];
+            const float inv = 1.f / l;
+            const long long token = static_cast<long long>(row0) + qpos;
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + token * p.out_stride + head * AT_D + half * 32;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 w;
+                w.x = pack_bf16x2(o[8 * q] * inv, o[8 * q + 1] * inv);
+                w.y = pack_bf16x2(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
+                w.z = pack_bf16x2(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
+                w.w = pack_bf16x2(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
+                *reinterpret_cast<uint4*>(out + 8 * q) = w;
+            }
+            // natural-log LSE of the scaled scores, layout [batch, head, seq]
+            if (half == 0) p.lse[(static_cast<long long>(batch) * p.heads + head) * p.seq_len + qpos] = m * 0.69314718056f + __logf(l);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        if (*reinterpret_cast<volatile int*>(p.status) != 0) {
+            const long long start = clock64();
+            while (clock64() - start < 200000) {}
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem_base, AT_TMEM_COLS);
+    }
+}
+
+constexpr int AT_FWD_SMEM = Q_BYTES + KV_STAGES * (K_BYTES + V_BYTES) + 1024 + 128 + 2 * AT_BM * 4;
+
+cudaError_t launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_FWD_SMEM);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    dim3 grid(p.seq_len / AT_BM, p.heads, p.batch);
+    attn_fwd_kernel<<<grid, AT_THREADS, AT_FWD_SMEM, stream>>>(tq, tk, tv, p);
+    return cudaGetLastError();
+}
+
+}  // namespace gm

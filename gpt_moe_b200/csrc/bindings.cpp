@@ -9,6 +9,7 @@
 #include <unordered_map>
 
 #include "gemm/gemm.h"
+#include "attention/attn.h"
 #include "kernels.h"
 
 namespace {
@@ -151,6 +152,67 @@ void gemm_bf16(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& d,
     GM_CHECK(e == cudaSuccess, cudaGetErrorString(e));
 }
 
+// map over a [B, T, H, 64] bf16 view whose tokens are rows of a wider matrix (e.g. the packed QKV projection output)
+const CUtensorMap& head_map(const torch::Tensor& t, int box_rows) {
+    GM_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 4, "attention operands must be [B, T, H, D] bf16 CUDA tensors");
+    GM_CHECK(t.stride(3) == 1 && t.stride(2) == t.size(3) && t.stride(0) == t.size(1) * t.stride(1),
+             "attention operands must be token-major with contiguous heads");
+    return cached_map(t.data_ptr(), 2, t.size(2) * t.size(3), t.size(0) * t.size(1), 1, t.stride(1) * 2, 0, 64, box_rows, 128);
+}
+
+// Returns (out [B,T,H,64] bf16, lse [B,H,T] fp32).
+std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, int64_t window, double scale) {
+    c10::cuda::CUDAGuard guard(q.device());
+    const int B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
+    GM_CHECK(D == 64 && v.size(3) == 64 && T % 128 == 0 && H % Hkv == 0, "attention kernel: head size 64, sequence length multiple of 128");
+    gm::AttnParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.batch = B; p.heads = H; p.seq_len = T; p.group = H / Hkv;
+    p.window = static_cast<int>(std::min<int64_t>(window, T));
+    p.scale = static_cast<float>(scale);
+    p.scale_log2e = static_cast<float>(scale * 1.4426950408889634);
+    auto out = torch::empty({B, T, H, D}, q.options());
+    auto lse = torch::empty({B, H, T}, q.options().dtype(torch::kFloat32));
+    p.out = out.data_ptr(); p.out_stride = H * D; p.lse = lse.data_ptr<float>();
+    p.status = status_tensor(q.device().index()).data_ptr<int>();
+    cudaError_t e = gm::launch_attn_fwd(head_map(q, 128), head_map(k, 128), head_map(v, 128), p, current_stream());
+    GM_CHECK(e == cudaSuccess, cudaGetErrorString(e));
+    return {out, lse};
+}
+
+// Backward.  q, k, v, out, d_out: [B,T,H(kv),64] bf16 views; lse [B,H,T].  dk, dv: [B,T,Hkv,64] bf16 views that are written
+// (they may be column slices of a packed gradient buffer).  Returns dq as fp32 [B,T,H,64].
+torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, const torch::Tensor& out,
+                       const torch::Tensor& d_out, const torch::Tensor& lse, torch::Tensor& dk, torch::Tensor& dv, int64_t window,
+                       double scale) {
+    c10::cuda::CUDAGuard guard(q.device());
+    const int B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
+    GM_CHECK(D == 64 && T % 128 == 0 && H % Hkv == 0, "attention kernel: head size 64, sequence length multiple of 128");
+    GM_CHECK(dk.stride(3) == 1 && dk.stride(2) == 64 && dv.stride(3) == 1 && dv.stride(2) == 64 && dk.stride(1) == dv.stride(1),
+             "dk/dv must be token-major views with contiguous heads and equal row pitch");
+    GM_CHECK(out.stride(3) == 1 && out.stride(2) == 64 && d_out.stride(3) == 1 && d_out.stride(2) == 64, "out/d_out layout");
+    gm::AttnParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.batch = B; p.heads = H; p.seq_len = T; p.group = H / Hkv;
+    p.window = static_cast<int>(std::min<int64_t>(window, T));
+    p.scale = static_cast<float>(scale);
+    p.scale_log2e = static_cast<float>(scale * 1.4426950408889634);
+    p.lse = const_cast<float*>(lse.data_ptr<float>());
+    auto delta = torch::empty({B, H, T}, lse.options());
+    auto dq = torch::zeros({B, T, H, D}, lse.options());
+    p.delta = delta.data_ptr<float>();
+    p.dq_accum = dq.data_ptr<float>();
+    p.dk = dk.data_ptr(); p.dv = dv.data_ptr(); p.dkv_stride = dk.stride(1);
+    p.status = status_tensor(q.device().index()).data_ptr<int>();
+    const CUtensorMap& tdq = cached_map(dq.data_ptr(), 4, static_cast<uint64_t>(H) * D, static_cast<uint64_t>(B) * T, 1,
+                                        static_cast<uint64_t>(H) * D * 4, 0, 32, 128, 128);
+    cudaError_t e = gm::launch_attn_bwd(head_map(q, 128), head_map(k, 128), head_map(v, 128), head_map(d_out, 128), tdq, p,
+                                        d_out.data_ptr(), out.data_ptr(), d_out.stride(1), out.stride(1), delta.data_ptr<float>(),
+                                        current_stream());
+    GM_CHECK(e == cudaSuccess, cudaGetErrorString(e));
+    return dq;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -160,5 +222,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("alpha") = 1.0, py::arg("beta") = 0.0, py::arg("c") = py::none(), py::arg("accumulate") = false,
           py::arg("mode") = 0, py::arg("tile_expert") = py::none(), py::arg("num_m_tiles") = py::none(),
           py::arg("seg_ends") = py::none());
+    m.def("attn_fwd", &attn_fwd);
+    m.def("attn_bwd", &attn_bwd);
     gm::register_kernels(m);
 }

@@ -301,6 +301,10 @@ class _SplitQKVFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dq, dk, dv):
         hq, hk, d, shape = ctx.cfg
+        # the attention kernel's backward hands over three views of one packed buffer: return that buffer as is
+        if dq is not None and dk is not None and dv is not None and dq._base is not None and dq._base is dk._base and \
+                dq._base is dv._base and dq._base.shape == shape and dq.storage_offset() == 0:
+            return dq._base, None, None, None
         parts = []
         for g, h in ((dq, hq), (dk, hk), (dv, hk)):
             parts.append(g.flatten(-2) if g is not None else torch.zeros(shape[:-1] + (h * d,), dtype=BF16, device="cuda"))

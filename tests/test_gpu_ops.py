@@ -82,9 +82,9 @@ def test_gemm_split_k_weight_gradient(ops):
     want = dy.float().t() @ x.float()
     dw = torch.full((n, k), 3.0, device="cuda")
     ops.ext().gemm_bf16(dy, x, dw, True, True)
-    assert rel(dw, want) < 1e-5
+    assert rel(dw, want) < 5e-5          # fp32 partial sums meet in arbitrary order
     ops.ext().gemm_bf16(dy, x, dw, True, True, 1.0, 0.0, None, True)
-    assert rel(dw, 2 * want) < 1e-5
+    assert rel(dw, 2 * want) < 5e-5
 
 
 @pytest.mark.parametrize("d,dtype", [(768, torch.float32), (1024, torch.bfloat16), (128, torch.float32)])
@@ -213,3 +213,47 @@ def test_adamw_and_muon_steps(ops):
     for c, g_, p0 in zip(cpu, gpu, ps):
         assert rel(g_.detach().cpu() - p0, c.detach() - p0) < 1e-4
     assert float(ag.state_dict()["state"][0]["step"]) == 3.0
+
+
+@pytest.mark.parametrize("t,window,hq,hk", [(256, 1000, 2, 2), (512, 128, 4, 2), (1024, 300, 2, 1), (384, 0, 2, 2)])
+def test_attention_forward_kernel(ops, t, window, hq, hk):
+    torch.manual_seed(9)
+    b, d = 2, 64
+    packed = torch.randn(b, t, (hq + 2 * hk) * d, device="cuda").bfloat16()      # q | k | v columns of one projection output
+    q = packed[..., : hq * d].unflatten(-1, (hq, d))
+    k = packed[..., hq * d: (hq + hk) * d].unflatten(-1, (hk, d))
+    v = packed[..., (hq + hk) * d:].unflatten(-1, (hk, d))
+    out, lse = ops.ext().attn_fwd(q, k, v, window, d ** -0.5)
+    want = ref.attention(q.float(), k.float(), v.float(), causal=True, window=window)
+    assert rel(out, want) < 1e-2
+    # log-sum-exp of the scaled, masked scores
+    rep = hq // hk
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float().repeat_interleave(rep, dim=2)) * d ** -0.5
+    keep = ref.attention_mask(t, "cuda", True, window)
+    assert torch.allclose(lse, torch.logsumexp(s.masked_fill(~keep, float("-inf")), dim=-1), atol=2e-2)
+
+
+@pytest.mark.parametrize("t,window,hq,hk", [(256, 1000, 2, 2), (512, 128, 4, 2), (1024, 300, 2, 1), (384, 0, 2, 2)])
+def test_attention_backward_kernel(ops, t, window, hq, hk):
+    from gpt_moe_b200.ops import attention_tc
+    torch.manual_seed(10)
+    b, d = 2, 64
+    packed = torch.randn(b, t, (hq + 2 * hk) * d, device="cuda").bfloat16().requires_grad_()
+    q, k, v = ops.split_qkv(packed, hq, hk, d)
+    assert attention_tc.supported(q, k, v, 0.0)
+    out = attention_tc.attention(q, k, v, window=window, scale=None)
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref_in = packed.detach().float().requires_grad_()
+    rq = ref_in[..., : hq * d].unflatten(-1, (hq, d))
+    rk = ref_in[..., hq * d: (hq + hk) * d].unflatten(-1, (hk, d))
+    rv = ref_in[..., (hq + hk) * d:].unflatten(-1, (hk, d))
+    want = ref.attention(rq, rk, rv, causal=True, window=window)
+    want.backward(g.float())
+    assert rel(out, want) < 1e-2
+    got, exp = packed.grad.float(), ref_in.grad
+    for name, sl in (("dq", slice(0, hq * d)), ("dk", slice(hq * d, (hq + hk) * d)), ("dv", slice((hq + hk) * d, None))):
+        if exp[..., sl].norm().item() < 1e-6:          # window 0: a single visible key makes dq and dk vanish exactly
+            assert got[..., sl].abs().max().item() < 1e-4, name
+        else:
+            assert rel(got[..., sl], exp[..., sl]) < 2e-2, name
