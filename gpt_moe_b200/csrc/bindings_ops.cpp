@@ -241,6 +241,54 @@ void muon_apply(const Tensor& weight_ptrs, const OptTensor& bf16_ptrs, const Ten
                       update.data_ptr(), weight_ptrs.numel(), rows, cols, w_stride, alpha, transpose, stream());
 }
 
+std::vector<long long> to_deltas(const std::vector<int64_t>& deltas) { return std::vector<long long>(deltas.begin(), deltas.end()); }
+
+// Owner-side gradient reduction over peer memory fused with Muon's momentum / Nesterov / bf16 pack / Frobenius normalisation.
+// grad_ptrs point into THIS rank's symmetric gradient buffer; peer_deltas[r] = (rank r's buffer base) - (this rank's base).
+void rs_muon_prepare(const Tensor& grad_ptrs, const Tensor& buf_ptrs, Tensor& packed, Tensor& sumsq, int64_t rows, int64_t cols,
+                     int64_t g_stride, int64_t b_stride, double momentum, bool nesterov, bool transpose,
+                     const std::vector<int64_t>& peer_deltas) {
+    c10::cuda::CUDAGuard guard(packed.device());
+    check_bf16(packed, "packed");
+    const int n = grad_ptrs.numel();
+    GM_CHECK(packed.numel() == n * rows * cols && (rows * cols) % 8 == 0, "packed buffer shape");
+    auto d = to_deltas(peer_deltas);
+    GM_CHECK(launch_rs_muon_prepare(reinterpret_cast<const float* const*>(grad_ptrs.data_ptr<int64_t>()),
+                                    reinterpret_cast<float* const*>(buf_ptrs.data_ptr<int64_t>()), packed.data_ptr(), sumsq.data_ptr<float>(), n,
+                                    rows, cols, g_stride, b_stride, momentum, nesterov, transpose, d.data(), d.size(), stream()),
+             "rs_muon_prepare: at most 16 ranks, column count a multiple of 4");
+    launch_muon_normalize(packed.data_ptr(), sumsq.data_ptr<float>(), n, rows * cols, stream());
+}
+
+// W_master += alpha * O on the owner; the refreshed bf16 copy is stored into every rank's weight buffer.
+void muon_apply_push(const Tensor& weight_ptrs, const Tensor& bf16_ptrs, const Tensor& update, int64_t rows, int64_t cols,
+                     int64_t w_stride, int64_t wb_stride, double alpha, bool transpose, const std::vector<int64_t>& peer_deltas) {
+    c10::cuda::CUDAGuard guard(update.device());
+    check_bf16(update, "update");
+    auto d = to_deltas(peer_deltas);
+    GM_CHECK(launch_muon_apply_push(reinterpret_cast<float* const*>(weight_ptrs.data_ptr<int64_t>()),
+                                    reinterpret_cast<void* const*>(bf16_ptrs.data_ptr<int64_t>()), update.data_ptr(), weight_ptrs.numel(),
+                                    rows, cols, w_stride, wb_stride, alpha, transpose, d.data(), d.size(), stream()),
+             "muon_apply_push: at most 16 ranks, column count a multiple of 4");
+}
+
+// AdamW on this rank's slice [lo, lo+n) of the flat parameter buffer: gradient summed from all ranks, result stored to all ranks.
+void adamw_sharded(Tensor& params, const Tensor& grads, Tensor& m, Tensor& v, const Tensor& decay, int64_t lo, int64_t n, double lr,
+                   double beta1, double beta2, double eps, int64_t step, const std::vector<int64_t>& grad_deltas,
+                   const std::vector<int64_t>& param_deltas) {
+    c10::cuda::CUDAGuard guard(params.device());
+    GM_CHECK(params.scalar_type() == torch::kFloat32 && grads.scalar_type() == torch::kFloat32 && decay.scalar_type() == torch::kFloat32,
+             "adamw_sharded expects fp32 flat buffers");
+    GM_CHECK(m.numel() >= n && v.numel() >= n && m.scalar_type() == v.scalar_type(), "moment buffers must cover the slice");
+    const double bc1 = 1.0 - std::pow(beta1, static_cast<double>(step));
+    const double bc2 = std::sqrt(1.0 - std::pow(beta2, static_cast<double>(step)));
+    auto gd = to_deltas(grad_deltas), pd = to_deltas(param_deltas);
+    GM_CHECK(launch_adamw_sharded(params.data_ptr<float>(), grads.data_ptr<float>(), m.data_ptr(), v.data_ptr(),
+                                  m.scalar_type() == torch::kBFloat16, decay.data_ptr<float>(), lo, n, lr, beta1, beta2, eps, bc1, bc2,
+                                  gd.data(), pd.data(), gd.size(), stream()),
+             "adamw_sharded: at most 16 ranks, slice bounds multiples of 4");
+}
+
 void cast_bf16(const Tensor& src, Tensor& dst) {
     c10::cuda::CUDAGuard guard(src.device());
     GM_CHECK(src.scalar_type() == torch::kFloat32 && dst.scalar_type() == torch::kBFloat16 && src.is_contiguous() && dst.is_contiguous() &&
@@ -269,6 +317,9 @@ void register_kernels(pybind11::module_& m) {
     m.def("muon_prepare", &muon_prepare);
     m.def("muon_apply", &muon_apply);
     m.def("cast_bf16", &cast_bf16);
+    m.def("rs_muon_prepare", &rs_muon_prepare);
+    m.def("muon_apply_push", &muon_apply_push);
+    m.def("adamw_sharded", &adamw_sharded);
 }
 
 }  // namespace gm

@@ -1,0 +1,214 @@
+// Optimizer kernels fused with their collectives over NVLink peer memory.
+//
+// Every rank maps every other rank's gradient / weight buffers (symmetric allocation: the same offset means the same
+// tensor on every GPU), so a kernel reaches a peer's copy as `local pointer + delta[rank]`.  Three kernels replace
+// "reduce-scatter, optimizer, all-gather":
+//   rs_muon_prepare   the owner of a matrix SUMS that matrix's gradient straight out of all ranks' buffers (plain P2P
+//                     loads = the reduce-scatter), averages, applies momentum / Nesterov, packs bf16 (transposed when
+//                     tall) and accumulates the Frobenius norm — the input of Polar Express
+//   muon_apply_push   W_master += alpha * O on the owner, and the refreshed bf16 GEMM copy is STORED into every rank's
+//                     weight buffer (P2P stores = the all-gather); nothing is staged
+//   adamw_sharded     each rank owns a slice of the flat AdamW parameters: sum of all ranks' gradients for the slice,
+//                     AdamW on the slice, new fp32 values stored into every rank's parameter buffer
+// Cross-rank ordering (gradients complete before they are read, pushes complete before the next forward) is provided by
+// barriers between the kernels, issued by the engine.  No multicast / cluster loads are used on peer memory.
+// The reference has no counterpart: its DDP all-reduces every gradient and then repeats the full optimizer on every
+// rank (train.py:213-215, optimizers/muon.py:147-224).
+#include "../common/ptx.cuh"
+#include "../kernels_decl.h"
+
+namespace gm {
+
+constexpr int MAX_RANKS = 16;
+struct PeerDeltas { long long d[MAX_RANKS]; };
+
+__device__ __forceinline__ float4 ld_peer4(const float* p, long long delta) {
+    return *reinterpret_cast<const float4*>(reinterpret_cast<const char*>(p) + delta);
+}
+
+// tile: 32 rows x 128 columns, 256 threads; thread (tx, ty) owns columns 4*tx..4*tx+3 of rows ty, ty+8, ty+16, ty+24
+__global__ void __launch_bounds__(256)
+rs_muon_prepare_kernel(const float* const* __restrict__ grads, float* const* __restrict__ bufs, __nv_bfloat16* __restrict__ packed,
+                       float* __restrict__ sumsq, int rows, int cols, long long g_stride, long long b_stride, float momentum,
+                       int nesterov, int transpose, PeerDeltas peers, int world, float inv_world) {
+    __shared__ float tile[32][132];
+    __shared__ float part[8];
+    const int mat = blockIdx.z;
+    const float* g = grads[mat];
+    float* buf = bufs[mat];
+    __nv_bfloat16* out = packed + static_cast<long long>(mat) * rows * cols;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int c0 = blockIdx.x * 128, r0 = blockIdx.y * 32;
+    float local = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = r0 + ty + 8 * i, c = c0 + 4 * tx;
+        float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < rows && c < cols) {
+            const float* gp = g + r * g_stride + c;
+            float4 s = ld_peer4(gp, peers.d[0]);
+            for (int k = 1; k < world; ++k) {
+                const float4 t = ld_peer4(gp, peers.d[k]);
+                s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+            }
+            s.x *= inv_world; s.y *= inv_world; s.z *= inv_world; s.w *= inv_world;
+            float4 b = *reinterpret_cast<const float4*>(buf + r * b_stride + c);
+            b.x = b.x * momentum + s.x; b.y = b.y * momentum + s.y; b.z = b.z * momentum + s.z; b.w = b.w * momentum + s.w;
+            *reinterpret_cast<float4*>(buf + r * b_stride + c) = b;
+            if (nesterov) { u.x = fmaf(momentum, b.x, s.x); u.y = fmaf(momentum, b.y, s.y); u.z = fmaf(momentum, b.z, s.z); u.w = fmaf(momentum, b.w, s.w); }
+            else u = b;
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(u.x, u.y), hi = __floats2bfloat162_rn(u.z, u.w);
+            const float2 flo = __bfloat1622float2(lo), fhi = __bfloat1622float2(hi);
+            u = make_float4(flo.x, flo.y, fhi.x, fhi.y);               // the rounded values are what Polar Express sees
+            if (!transpose) {
+                uint2 w;
+                w.x = *reinterpret_cast<const uint32_t*>(&lo);
+                w.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(out + static_cast<long long>(r) * cols + c) = w;
+            }
+        }
+        tile[ty + 8 * i][4 * tx] = u.x; tile[ty + 8 * i][4 * tx + 1] = u.y; tile[ty + 8 * i][4 * tx + 2] = u.z; tile[ty + 8 * i][4 * tx + 3] = u.w;
+        local += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
+    }
+    if (transpose) {
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int c = c0 + ty + 8 * i, r = r0 + tx;              // out is [cols][rows]
+            if (r < rows && c < cols) out[static_cast<long long>(c) * rows + r] = __float2bfloat16(tile[tx][ty + 8 * i]);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+    if (tx == 0) part[ty] = local;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < 8; ++w) t += part[w];
+        atomicAdd(&sumsq[mat], t);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+muon_apply_push_kernel(float* const* __restrict__ weights, __nv_bfloat16* const* __restrict__ weights_bf16,
+                       const __nv_bfloat16* __restrict__ update, int rows, int cols, long long w_stride, long long wb_stride,
+                       float alpha, int transpose, PeerDeltas peers, int world) {
+    __shared__ float tile[128][33];
+    const int mat = blockIdx.z;
+    float* w = weights[mat];
+    __nv_bfloat16* wb = weights_bf16[mat];
+    const __nv_bfloat16* o = update + static_cast<long long>(mat) * rows * cols;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int c0 = blockIdx.x * 128, r0 = blockIdx.y * 32;
+    if (transpose) {                                                 // update is [cols][rows]: stage the 128 x 32 block
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int c = c0 + ty + 8 * i, r = r0 + tx;
+            tile[ty + 8 * i][tx] = (r < rows && c < cols) ? __bfloat162float(o[static_cast<long long>(c) * rows + r]) : 0.f;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int rl = ty + 8 * i, r = r0 + rl, c = c0 + 4 * tx;
+        if (r < rows && c < cols) {
+            float4 upd;
+            if (transpose) {
+                upd = make_float4(tile[4 * tx][rl], tile[4 * tx + 1][rl], tile[4 * tx + 2][rl], tile[4 * tx + 3][rl]);
+            } else {
+                const uint2 raw = *reinterpret_cast<const uint2*>(o + static_cast<long long>(r) * cols + c);
+                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                upd = make_float4(a.x, a.y, b.x, b.y);
+            }
+            float4 cur = *reinterpret_cast<const float4*>(w + r * w_stride + c);
+            cur.x += alpha * upd.x; cur.y += alpha * upd.y; cur.z += alpha * upd.z; cur.w += alpha * upd.w;
+            *reinterpret_cast<float4*>(w + r * w_stride + c) = cur;
+            uint2 q;
+            q.x = pack_bf16x2(cur.x, cur.y);
+            q.y = pack_bf16x2(cur.z, cur.w);
+            char* dst = reinterpret_cast<char*>(wb + r * wb_stride + c);
+            for (int k = 0; k < world; ++k) *reinterpret_cast<uint2*>(dst + peers.d[k]) = q;      // local copy and every peer's copy
+        }
+    }
+}
+
+// slice [lo, lo + n) of the flat AdamW parameter / gradient buffers (n and lo multiples of 4)
+template <typename TM>
+__global__ void __launch_bounds__(256)
+adamw_sharded_kernel(float* __restrict__ params, const float* __restrict__ grads, TM* __restrict__ m, TM* __restrict__ v,
+                     const float* __restrict__ decay, long long lo, long long n, float lr, float beta1, float beta2, float eps,
+                     float bc1, float bc2_sqrt, PeerDeltas gpeers, PeerDeltas ppeers, int world, float inv_world) {
+    for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 4; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
+        const float* gp = grads + lo + i;
+        float4 g = ld_peer4(gp, gpeers.d[0]);
+        for (int k = 1; k < world; ++k) {
+            const float4 t = ld_peer4(gp, gpeers.d[k]);
+            g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+        }
+        const float gg[4] = {g.x * inv_world, g.y * inv_world, g.z * inv_world, g.w * inv_world};
+        float4 pw = *reinterpret_cast<const float4*>(params + lo + i);
+        float pp[4] = {pw.x, pw.y, pw.z, pw.w};
+        const float4 wd4 = *reinterpret_cast<const float4*>(decay + lo + i);      // per-element weight decay (0 for no-decay groups)
+        const float wd[4] = {wd4.x, wd4.y, wd4.z, wd4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float mi, vi;
+            if constexpr (sizeof(TM) == 4) { mi = m[i + e]; vi = v[i + e]; } else { mi = __bfloat162float(m[i + e]); vi = __bfloat162float(v[i + e]); }
+            mi = beta1 * mi + (1.f - beta1) * gg[e];
+            vi = beta2 * vi + (1.f - beta2) * gg[e] * gg[e];
+            if constexpr (sizeof(TM) == 4) { m[i + e] = mi; v[i + e] = vi; } else { m[i + e] = __float2bfloat16(mi); v[i + e] = __float2bfloat16(vi); }
+            float x = pp[e] * (1.f - lr * wd[e]);
+            x -= lr / bc1 * mi / (sqrtf(vi) / bc2_sqrt + eps);
+            pp[e] = x;
+        }
+        const float4 nw = make_float4(pp[0], pp[1], pp[2], pp[3]);
+        char* dst = reinterpret_cast<char*>(params + lo + i);
+        for (int k = 0; k < world; ++k) *reinterpret_cast<float4*>(dst + ppeers.d[k]) = nw;
+    }
+}
+
+static PeerDeltas make_deltas(const long long* deltas, int world) {
+    PeerDeltas p;
+    for (int i = 0; i < MAX_RANKS; ++i) p.d[i] = i < world ? deltas[i] : 0;
+    return p;
+}
+
+bool launch_rs_muon_prepare(const float* const* grads, float* const* bufs, void* packed, float* sumsq, int n_mats, int rows, int cols,
+                            long long g_stride, long long b_stride, float momentum, int nesterov, int transpose,
+                            const long long* peer_deltas, int world, cudaStream_t s) {
+    if (world > MAX_RANKS || cols % 4) return false;
+    dim3 grid((cols + 127) / 128, (rows + 31) / 32, n_mats);
+    rs_muon_prepare_kernel<<<grid, 256, 0, s>>>(grads, bufs, static_cast<__nv_bfloat16*>(packed), sumsq, rows, cols, g_stride, b_stride,
+                                                momentum, nesterov, transpose, make_deltas(peer_deltas, world), world, 1.f / world);
+    return true;
+}
+
+bool launch_muon_apply_push(float* const* weights, void* const* weights_bf16, const void* update, int n_mats, int rows, int cols,
+                            long long w_stride, long long wb_stride, float alpha, int transpose, const long long* peer_deltas, int world,
+                            cudaStream_t s) {
+    if (world > MAX_RANKS || cols % 4) return false;
+    dim3 grid((cols + 127) / 128, (rows + 31) / 32, n_mats);
+    muon_apply_push_kernel<<<grid, 256, 0, s>>>(weights, reinterpret_cast<__nv_bfloat16* const*>(weights_bf16),
+                                                static_cast<const __nv_bfloat16*>(update), rows, cols, w_stride, wb_stride, alpha, transpose,
+                                                make_deltas(peer_deltas, world), world);
+    return true;
+}
+
+bool launch_adamw_sharded(float* params, const float* grads, void* m, void* v, bool moments_bf16, const float* decay, long long lo,
+                          long long n, float lr, float beta1, float beta2, float eps, float bc1, float bc2_sqrt,
+                          const long long* grad_deltas, const long long* param_deltas, int world, cudaStream_t s) {
+    if (world > MAX_RANKS || (n % 4) || (lo % 4)) return false;
+    if (n == 0) return true;
+    const int blocks = static_cast<int>((n / 4 + 255) / 256 < 1184 ? (n / 4 + 255) / 256 : 1184);
+    const PeerDeltas gp = make_deltas(grad_deltas, world), pp = make_deltas(param_deltas, world);
+    if (moments_bf16)
+        adamw_sharded_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(params, grads, static_cast<__nv_bfloat16*>(m), static_cast<__nv_bfloat16*>(v),
+                                                                   decay, lo, n, lr, beta1, beta2, eps, bc1, bc2_sqrt, gp, pp, world, 1.f / world);
+    else
+        adamw_sharded_kernel<float><<<blocks, 256, 0, s>>>(params, grads, static_cast<float*>(m), static_cast<float*>(v), decay, lo, n, lr,
+                                                           beta1, beta2, eps, bc1, bc2_sqrt, gp, pp, world, 1.f / world);
+    return true;
+}
+
+}  // namespace gm

@@ -230,6 +230,11 @@ void launch_muon_prepare(const float* const* grads, float* const* bufs, void* pa
     muon_normalize_kernel<<<grid2, 256, 0, s>>>(static_cast<__nv_bfloat16*>(packed), sumsq, n);
 }
 
+void launch_muon_normalize(void* packed, const float* sumsq, int n_mats, long long per_matrix, cudaStream_t s) {
+    dim3 grid(static_cast<unsigned>(std::min<long long>((per_matrix / 8 + 255) / 256, 592LL)), n_mats);
+    muon_normalize_kernel<<<grid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(packed), sumsq, per_matrix);
+}
+
 void launch_muon_apply(float* const* weights, void* const* weights_bf16, const void* update, int n_mats, int rows, int cols,
                        long long w_stride, float alpha, int transpose, cudaStream_t s) {
     dim3 grid((cols + 31) / 32, (rows + 31) / 32, n_mats);

@@ -45,4 +45,17 @@ void launch_muon_apply(float* const* weights, void* const* weights_bf16, const v
                        long long w_stride, float alpha, int transpose, cudaStream_t s);
 void launch_cast_bf16(const float* src, void* dst, long long n, cudaStream_t s);
 
+void launch_muon_normalize(void* packed, const float* sumsq, int n_mats, long long per_matrix, cudaStream_t s);
+
+// comm/fused_comm.cu
+bool launch_rs_muon_prepare(const float* const* grads, float* const* bufs, void* packed, float* sumsq, int n_mats, int rows, int cols,
+                            long long g_stride, long long b_stride, float momentum, int nesterov, int transpose,
+                            const long long* peer_deltas, int world, cudaStream_t s);
+bool launch_muon_apply_push(float* const* weights, void* const* weights_bf16, const void* update, int n_mats, int rows, int cols,
+                            long long w_stride, long long wb_stride, float alpha, int transpose, const long long* peer_deltas, int world,
+                            cudaStream_t s);
+bool launch_adamw_sharded(float* params, const float* grads, void* m, void* v, bool moments_bf16, const float* decay, long long lo,
+                          long long n, float lr, float beta1, float beta2, float eps, float bc1, float bc2_sqrt,
+                          const long long* grad_deltas, const long long* param_deltas, int world, cudaStream_t s);
+
 }  // namespace gm

@@ -99,10 +99,33 @@ def _cast_into(src: Tensor, dst: Tensor) -> None:
         dst.copy_(src.detach())
 
 
+def _compute_view(weights: Sequence[Tensor], stack: bool) -> Optional[Tensor]:
+    """When an engine maintains bf16 copies (`param.compute`) laid out back to back, the concatenation / stack of
+    the weights is simply a view of that memory."""
+    copies = [getattr(w, "compute", None) for w in weights]
+    if any(c is None for c in copies):
+        return None
+    first = copies[0]
+    ptr = first.data_ptr()
+    for c in copies:
+        if c.data_ptr() != ptr or not c.is_contiguous():
+            return None
+        ptr += c.numel() * c.element_size()
+    if stack:
+        if any(c.shape != first.shape for c in copies):
+            return None
+        return torch.as_strided(first, (len(copies),) + tuple(first.shape), (first.numel(),) + tuple(first.stride()))
+    rows = sum(c.shape[0] for c in copies)
+    return torch.as_strided(first, (rows,) + tuple(first.shape[1:]), first.stride())
+
+
 def bf16_weight(weights: Sequence[Tensor]) -> Tensor:
     """bf16 copy of `cat(weights, dim=0)` (one tensor: just its copy)."""
     if len(weights) == 1 and weights[0].dtype == BF16:
         return weights[0].detach()
+    view = _compute_view(weights, stack=False)
+    if view is not None:
+        return view
 
     def build(old):
         rows = sum(w.shape[0] for w in weights)
@@ -118,6 +141,10 @@ def bf16_weight(weights: Sequence[Tensor]) -> Tensor:
 
 def stacked_weight(weights: Sequence[Tensor]) -> Tensor:
     """bf16 [E, N, K] stack of same-shape expert weights."""
+    view = _compute_view(weights, stack=True)
+    if view is not None:
+        return view
+
     def build(old):
         out = old if old is not None else torch.empty((len(weights),) + tuple(weights[0].shape), dtype=BF16, device=weights[0].device)
         for e, w in enumerate(weights):

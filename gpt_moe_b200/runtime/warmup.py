@@ -24,6 +24,7 @@ def kernel_warmup(run, num_train_steps: int = 2) -> float:
     t0 = time.time()
     model_state = copy.deepcopy(run.raw_gpt_model.state_dict())
     opt_state = {k: copy.deepcopy(o.state_dict()) for k, o in run.optimizers.items()}
+    engine_state = trainer.engine.snapshot() if hasattr(trainer.engine, "snapshot") else None
     cpu_rng = torch.get_rng_state()
     cuda_rng = torch.cuda.get_rng_state() if trainer.device_type == "cuda" else None
     saved = (trainer.train_tokens_processed, trainer.schedule_state())
@@ -44,7 +45,9 @@ def kernel_warmup(run, num_train_steps: int = 2) -> float:
     run.raw_gpt_model.load_state_dict(model_state)
     for k, o in run.optimizers.items():
         o.load_state_dict(opt_state[k])
-    if hasattr(trainer.engine, "refresh_from_parameters"):
+    if engine_state is not None:
+        trainer.engine.restore(engine_state)
+    elif hasattr(trainer.engine, "refresh_from_parameters"):
         trainer.engine.refresh_from_parameters()
     torch.set_rng_state(cpu_rng)
     if cuda_rng is not None:

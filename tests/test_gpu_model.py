@@ -94,3 +94,25 @@ def test_short_training_reduces_loss():
     batch = [(ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), None)]
     losses = [trainer.train_step(batch)["loss"] for _ in range(8)]
     assert losses[-1] < losses[0] - 0.5, losses
+
+
+def test_fused_engine_matches_plain_optimizers_on_one_gpu():
+    """Flat-buffer engine (world of one) against the per-parameter CUDA optimizers: same losses, same weights."""
+    from gpt_moe_b200.runtime.trainer import Trainer
+    results = []
+    for fused in (True, False):
+        gc, tc = _tiny()
+        tc.kernel_warmup_train_steps = 0
+        tc.use_fused_collectives = fused
+        trainer = Trainer(gc, tc, device_type="cuda", quiet=True)
+        assert type(trainer.engine).__name__ == ("FusedEngine" if fused else "CudaHostEngine")
+        gen = torch.Generator().manual_seed(5)
+        losses = []
+        for _ in range(4):
+            ids = torch.randint(0, gc.vocab_size, (2, 257), generator=gen)
+            losses.append(trainer.train_step([(ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), None)])["loss"])
+        results.append((losses, {n: p.detach().float().cpu().clone() for n, p in trainer.raw_gpt_model.named_parameters()}))
+    (la, pa), (lb, pb) = results
+    assert la == pytest.approx(lb, abs=2e-2)
+    for n in pa:
+        assert (pa[n] - pb[n]).norm().item() <= 5e-2 * pb[n].norm().item() + 1e-3, n
