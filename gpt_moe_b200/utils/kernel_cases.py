@@ -1,0 +1,94 @@
+"""Run one hot kernel on a small, fixed case: `python -m gpt_moe_b200.utils.kernel_cases <case> [--iters N]`.
+
+Meant for profiling (`ncu -k regex:<kernel> ... python -m gpt_moe_b200.utils.kernel_cases <case>`) and for quick timing
+with CUDA events.  Cases are larger than the 126 MB L2 where DRAM traffic matters and hold at most a few GB.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+
+def _timed(fn, iters):
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / iters
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["gemm", "gemm_wgrad", "grouped", "attn_fwd", "attn_bwd", "rs_muon", "ce", "rmsnorm"])
+    ap.add_argument("--iters", type=int, default=3)
+    args = ap.parse_args()
+    from gpt_moe_b200.ops import attention_tc, cuda_ops
+    c = cuda_ops.ext()
+    dev = "cuda"
+    torch.manual_seed(0)
+    flops = bytes_ = 0
+    if args.case == "gemm":                      # QKV projection shape: [32768, 768] x [2304, 768]^T
+        a = torch.randn(32768, 768, device=dev).bfloat16(); b = torch.randn(2304, 768, device=dev).bfloat16()
+        d = torch.empty(32768, 2304, device=dev, dtype=torch.bfloat16)
+        fn = lambda: c.gemm_bf16(a, b, d)
+        flops = 2 * 32768 * 2304 * 768
+    elif args.case == "gemm_wgrad":              # dW = dY^T X, both operands MN-major, fp32 output, split-K
+        dy = torch.randn(32768, 2304, device=dev).bfloat16(); x = torch.randn(32768, 768, device=dev).bfloat16()
+        dw = torch.empty(2304, 768, device=dev)
+        fn = lambda: c.gemm_bf16(dy, x, dw, True, True)
+        flops = 2 * 32768 * 2304 * 768
+    elif args.case == "grouped":                 # expert up-projection: 8 experts, 32768 routed rows
+        idx = torch.randint(0, 8, (32768, 1), device=dev)
+        dest, src, seg, counts, tiles, meta = c.route(idx, 8)
+        hidden = torch.randn(32768, 768, device=dev).bfloat16()
+        packed = c.gather_rows(hidden, src, meta, 1)
+        w = torch.randn(8, 6144, 768, device=dev).bfloat16()
+        out = torch.empty(packed.shape[0], 6144, device=dev, dtype=torch.bfloat16)
+        fn = lambda: c.gemm_bf16(packed, w, out, False, False, 1.0, 0.0, None, False, 1, tiles, meta, None)
+        flops = 2 * 32768 * 6144 * 768
+    elif args.case in ("attn_fwd", "attn_bwd"):  # 4 x 2048 tokens, 12 heads, window 1024
+        b_, t, h, d = 4, 2048, 12, 64
+        packed = torch.randn(b_, t, 3 * h * d, device=dev).bfloat16().requires_grad_()
+        q, k, v = cuda_ops.split_qkv(packed, h, h, d)
+        keys = sum(min(i, 1024) + 1 for i in range(t))
+        if args.case == "attn_fwd":
+            fn = lambda: c.attn_fwd(q.detach(), k.detach(), v.detach(), 1024, d ** -0.5)
+            flops = 4 * d * keys * b_ * h
+        else:
+            out = attention_tc.attention(q, k, v, window=1024, scale=None)
+            g = torch.randn_like(out)
+            fn = lambda: torch.autograd.grad(out, packed, g, retain_graph=True)
+            flops = 10 * d * keys * b_ * h
+    elif args.case == "rs_muon":                 # reduce + momentum + pack for 16 matrices of 6144 x 768 (world of one)
+        grads = [torch.randn(6144, 768, device=dev) for _ in range(16)]
+        bufs = [torch.zeros(6144, 768, device=dev) for _ in range(16)]
+        packed = torch.empty(16, 768, 6144, device=dev, dtype=torch.bfloat16)
+        sumsq = torch.zeros(16, device=dev)
+        gp, bp = cuda_ops._ptr_table(grads), cuda_ops._ptr_table(bufs)
+        fn = lambda: c.rs_muon_prepare(gp, bp, packed, sumsq, 6144, 768, 768, 768, 0.95, True, True, [0])
+        bytes_ = 16 * 6144 * 768 * (4 + 4 + 4 + 2 + 2 + 2)
+    elif args.case == "ce":
+        logits = torch.randn(4096, 50304, device=dev).bfloat16()
+        targets = torch.randint(0, 50304, (4096,), device=dev)
+        scale = torch.ones(1, device=dev)
+        fn = lambda: c.ce_fwd_bwd(logits, targets, scale, -100, True)
+        bytes_ = 4096 * 50304 * 2 * 3
+    else:
+        x = torch.randn(32768, 768, device=dev)
+        w = torch.ones(768, device=dev)
+        fn = lambda: c.rmsnorm_fwd(x, w, 1e-6)
+        bytes_ = 32768 * 768 * 6
+    ms = _timed(fn, args.iters)
+    cuda_ops.check_status()
+    rate = f"{flops / ms / 1e9:.1f} TFLOP/s" if flops else f"{bytes_ / ms / 1e6:.1f} GB/s"
+    print(f"{args.case}: {ms * 1e3:.1f} us per call, {rate}")
+
+
+if __name__ == "__main__":
+    main()
