@@ -152,6 +152,78 @@ void gemm_bf16(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& d,
     GM_CHECK(e == cudaSuccess, cudaGetErrorString(e));
 }
 
+// ---- MXFP8 ----------------------------------------------------------------------------------------
+int64_t sf_records(int64_t rows, int64_t k) { return ((rows + 127) / 128) * ((k + 127) / 128); }
+
+// x [.., rows, cols] bf16 (last dim contiguous, uniform row pitch) -> (q e4m3 as uint8 [.., rows, cols], scales uint8 [batch, records * 512])
+std::vector<torch::Tensor> mxfp8_quantize(const torch::Tensor& x, const c10::optional<torch::Tensor>& rows_limit) {
+    c10::cuda::CUDAGuard guard(x.device());
+    GM_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && (x.dim() == 2 || x.dim() == 3), "mxfp8_quantize wants a 2-D or 3-D bf16 CUDA tensor");
+    GM_CHECK(x.stride(-1) == 1 && x.size(-1) % 32 == 0 && x.stride(-2) % 8 == 0, "mxfp8_quantize: last dimension contiguous, multiple of 32");
+    const int64_t batch = x.dim() == 3 ? x.size(0) : 1, rows = x.size(-2), cols = x.size(-1);
+    GM_CHECK(batch == 1 || rows % 128 == 0 || x.is_contiguous(), "mxfp8_quantize: batched input must be contiguous");
+    auto q = torch::empty(x.sizes(), x.options().dtype(torch::kUInt8));
+    auto sf = torch::zeros({batch, sf_records(rows, cols) * 512}, x.options().dtype(torch::kUInt8));
+    for (int64_t z = 0; z < batch; ++z) {
+        const auto* src = static_cast<const at::BFloat16*>(x.data_ptr()) + (x.dim() == 3 ? z * x.stride(0) : 0);
+        gm::launch_quantize_rows(src, q.data_ptr<uint8_t>() + z * rows * cols, sf.data_ptr<uint8_t>() + z * sf.stride(0), rows,
+                                 static_cast<int>(cols), x.stride(-2), rows_limit.has_value() ? rows_limit->data_ptr<int>() : nullptr,
+                                 current_stream());
+    }
+    return {q, sf};
+}
+
+// w [.., rows, cols] bf16 contiguous -> (q [.., cols, rows] e4m3, scales) with the groups of 32 running along `rows`
+std::vector<torch::Tensor> mxfp8_quantize_transposed(const torch::Tensor& w) {
+    c10::cuda::CUDAGuard guard(w.device());
+    GM_CHECK(w.is_cuda() && w.scalar_type() == torch::kBFloat16 && w.is_contiguous() && (w.dim() == 2 || w.dim() == 3), "mxfp8_quantize_transposed wants a contiguous bf16 CUDA tensor");
+    const int64_t batch = w.dim() == 3 ? w.size(0) : 1, rows = w.size(-2), cols = w.size(-1);
+    GM_CHECK(rows % 32 == 0, "mxfp8_quantize_transposed: the contraction dimension must be a multiple of 32");
+    auto q = w.dim() == 3 ? torch::empty({batch, cols, rows}, w.options().dtype(torch::kUInt8)) : torch::empty({cols, rows}, w.options().dtype(torch::kUInt8));
+    auto sf = torch::zeros({batch, sf_records(cols, rows) * 512}, w.options().dtype(torch::kUInt8));
+    gm::launch_quantize_transposed(w.data_ptr(), q.data_ptr(), sf.data_ptr(), static_cast<int>(batch), static_cast<int>(rows), static_cast<int>(cols),
+                                   sf.stride(0), current_stream());
+    return {q, sf};
+}
+
+// d [.., M, N] bf16 = alpha * a [.., M, K] b [.., N, K]^T from e4m3 bytes and their scale records.
+// grouped: a [rows, K] in padded expert-major order, b [E, N, K], tile_expert / num_m_tiles on the device.
+void gemm_mxfp8(const torch::Tensor& a, const torch::Tensor& sfa, const torch::Tensor& b, const torch::Tensor& sfb, torch::Tensor& d, double alpha,
+                const c10::optional<torch::Tensor>& tile_expert, const c10::optional<torch::Tensor>& num_m_tiles) {
+    c10::cuda::CUDAGuard guard(a.device());
+    GM_CHECK(a.is_cuda() && a.scalar_type() == torch::kUInt8 && b.scalar_type() == torch::kUInt8 && a.is_contiguous() && b.is_contiguous(), "mxfp8 operands are contiguous uint8 tensors");
+    GM_CHECK(d.scalar_type() == torch::kBFloat16 && d.stride(-1) == 1 && d.stride(-2) % 8 == 0, "mxfp8 output is bf16 with a 16-byte aligned row pitch");
+    gm::Mxfp8Params p;
+    std::memset(&p, 0, sizeof(p));
+    p.M = d.size(-2); p.N = d.size(-1); p.K = a.size(-1);
+    GM_CHECK(b.size(-1) == p.K && b.size(-2) == p.N && p.K % 128 == 0, "mxfp8 GEMM shapes (K must be a multiple of 128)");
+    p.grouped = tile_expert.has_value();
+    if (p.grouped) {
+        GM_CHECK(a.dim() == 2 && b.dim() == 3 && d.dim() == 2 && num_m_tiles.has_value() && a.size(0) % 128 == 0, "grouped mxfp8 operand ranks");
+        p.tile_expert = tile_expert->data_ptr<int>();
+        p.num_m_tiles = num_m_tiles->data_ptr<int>();
+        p.batch = 1;
+    } else {
+        GM_CHECK(a.size(-2) == p.M && a.dim() == d.dim() && b.dim() == d.dim(), "mxfp8 GEMM: operand ranks");
+        p.batch = d.dim() == 3 ? d.size(0) : 1;
+    }
+    p.sfa_row_blocks = (a.size(-2) + 127) / 128;
+    p.sfb_row_blocks = (p.N + 127) / 128;
+    const int64_t kb = p.K / 128;
+    GM_CHECK(sfa.numel() == (a.dim() == 3 ? a.size(0) : 1) * p.sfa_row_blocks * kb * 512, "mxfp8 GEMM: A scale tensor size");
+    GM_CHECK(sfb.numel() == (b.dim() == 3 ? b.size(0) : 1) * p.sfb_row_blocks * kb * 512, "mxfp8 GEMM: B scale tensor size");
+    p.sfa = sfa.data_ptr<uint8_t>();
+    p.sfb = sfb.data_ptr<uint8_t>();
+    p.alpha = static_cast<float>(alpha);
+    p.status = status_tensor(a.device().index()).data_ptr<int>();
+    const uint64_t ab = a.dim() == 3 ? a.size(0) : 1, bb = b.dim() == 3 ? b.size(0) : 1;
+    const CUtensorMap& ta = cached_map(a.data_ptr(), 1, p.K, a.size(-2), ab, p.K, a.size(-2) * static_cast<uint64_t>(p.K), 128, 128, 128);
+    const CUtensorMap& tb = cached_map(b.data_ptr(), 1, p.K, p.N, bb, p.K, static_cast<uint64_t>(p.N) * p.K, 128, 128, 128);
+    const CUtensorMap& td = cached_map(d.data_ptr(), 2, p.N, p.M, d.dim() == 3 ? d.size(0) : 1, d.stride(-2) * 2, d.dim() == 3 ? d.stride(0) * 2 : 0, 64, 128, 128);
+    cudaError_t e = gm::launch_gemm_mxfp8(ta, tb, td, p, sm_count(), current_stream());
+    GM_CHECK(e == cudaSuccess, cudaGetErrorString(e));
+}
+
 // map over a [B, T, H, 64] bf16 view whose tokens are rows of a wider matrix (e.g. the packed QKV projection output)
 const CUtensorMap& head_map(const torch::Tensor& t, int box_rows) {
     GM_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 4, "attention operands must be [B, T, H, D] bf16 CUDA tensors");
@@ -222,6 +294,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("alpha") = 1.0, py::arg("beta") = 0.0, py::arg("c") = py::none(), py::arg("accumulate") = false,
           py::arg("mode") = 0, py::arg("tile_expert") = py::none(), py::arg("num_m_tiles") = py::none(),
           py::arg("seg_ends") = py::none());
+    m.def("mxfp8_quantize", &mxfp8_quantize, py::arg("x"), py::arg("rows_limit") = py::none());
+    m.def("mxfp8_quantize_transposed", &mxfp8_quantize_transposed);
+    m.def("gemm_mxfp8", &gemm_mxfp8, py::arg("a"), py::arg("sfa"), py::arg("b"), py::arg("sfb"), py::arg("d"), py::arg("alpha") = 1.0,
+          py::arg("tile_expert") = py::none(), py::arg("num_m_tiles") = py::none());
     m.def("attn_fwd", &attn_fwd);
     m.def("attn_bwd", &attn_bwd);
     gm::register_kernels(m);

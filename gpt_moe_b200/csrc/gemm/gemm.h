@@ -37,4 +37,29 @@ bool make_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, uint64_
 cudaError_t launch_gemm_bf16(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmParams& p, bool a_mn,
                              bool b_mn, int sms, cudaStream_t stream);
 
+// Block-scaled MXFP8 GEMM: D[M,N] (bf16) = alpha * A[M,K] B[N,K]^T, e4m3 operands, UE8M0 scales per 32 elements of K.
+// Scales are stored as 512-byte records [row block of 128][K block of 128]; byte (r % 32) * 16 + (r / 32) * 4 + g of a record
+// belongs to row r of the block and the g-th group of 32 inside the K block.
+struct Mxfp8Params {
+    int M, N, K;
+    int batch;                   // dense: batched problems
+    int grouped;                 // 1: A rows are expert-major padded segments, B is [E, N, K]
+    const uint8_t* sfa;          // [batch, sfa_row_blocks, K/128, 512]
+    const uint8_t* sfb;          // [batch or E, sfb_row_blocks, K/128, 512]
+    int sfa_row_blocks, sfb_row_blocks;
+    float alpha;
+    const int* tile_expert;
+    const int* num_m_tiles;
+    int* status;
+};
+
+cudaError_t launch_gemm_mxfp8(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const Mxfp8Params& p, int sms,
+                              cudaStream_t stream);
+// x [rows, cols] bf16 with row pitch ld -> q [rows, cols] e4m3 and scale records; rows at or beyond *rows_limit (optional,
+// device) are left untouched.  cols must be a multiple of 32.
+void launch_quantize_rows(const void* x, void* q, void* sf, long long rows, int cols, long long ld, const int* rows_limit, cudaStream_t s);
+// w [batch, rows, cols] bf16 -> q [batch, cols, rows] e4m3 (transposed) with scales along the original row index.
+// rows must be a multiple of 32.
+void launch_quantize_transposed(const void* w, void* q, void* sf, int batch, int rows, int cols, long long sf_batch_stride, cudaStream_t s);
+
 }  // namespace gm

@@ -25,7 +25,7 @@ def _timed(fn, iters):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_wgrad", "grouped", "attn_fwd", "attn_bwd", "rs_muon", "ce", "rmsnorm"])
+    ap.add_argument("case", choices=["gemm", "gemm_mxfp8", "quantize", "gemm_wgrad", "grouped", "attn_fwd", "attn_bwd", "rs_muon", "ce", "rmsnorm"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     from gpt_moe_b200.ops import attention_tc, cuda_ops
@@ -38,6 +38,16 @@ def main() -> None:
         d = torch.empty(32768, 2304, device=dev, dtype=torch.bfloat16)
         fn = lambda: c.gemm_bf16(a, b, d)
         flops = 2 * 32768 * 2304 * 768
+    elif args.case == "gemm_mxfp8":              # same shape on e4m3 operands with 32-element UE8M0 block scales
+        a = torch.randn(32768, 768, device=dev).bfloat16(); b = torch.randn(2304, 768, device=dev).bfloat16()
+        aq, asf = c.mxfp8_quantize(a); bq, bsf = c.mxfp8_quantize(b)
+        d = torch.empty(32768, 2304, device=dev, dtype=torch.bfloat16)
+        fn = lambda: c.gemm_mxfp8(aq, asf, bq, bsf, d)
+        flops = 2 * 32768 * 2304 * 768
+    elif args.case == "quantize":                # bf16 -> e4m3 + scale records, 256 MB in
+        a = torch.randn(65536, 2048, device=dev).bfloat16()
+        fn = lambda: c.mxfp8_quantize(a)
+        bytes_ = 65536 * 2048 * 3 + 65536 * 2048 // 32
     elif args.case == "gemm_wgrad":              # dW = dY^T X, both operands MN-major, fp32 output, split-K
         dy = torch.randn(32768, 2304, device=dev).bfloat16(); x = torch.randn(32768, 768, device=dev).bfloat16()
         dw = torch.empty(2304, 768, device=dev)

@@ -1,0 +1,138 @@
+"""Block-scaled MXFP8 kernels against the fp32 emulation in `ops.reference` (quantise -> expand -> fp32 matmul).
+
+The quantiser must agree bit for bit with the emulation (same power-of-two scale rule, round-to-nearest-even e4m3), so the
+GEMM is compared against the product of the expanded operands with only the bf16 output rounding as tolerance.
+"""
+import pytest
+import torch
+
+from gpt_moe_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+def rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from gpt_moe_b200.ops import cuda_ops
+    cuda_ops.ext().reset_status()
+    yield cuda_ops
+    cuda_ops.check_status()
+
+
+def unpack_scales(sf: torch.Tensor, rows: int, k: int) -> torch.Tensor:
+    """[records * 512] bytes -> fp32 scales [rows, k / 32] following the record layout of the kernels."""
+    kb = (k + 127) // 128
+    r = torch.arange(rows, device=sf.device)[:, None]
+    g = torch.arange(k // 32, device=sf.device)[None, :]
+    off = ((r // 128) * kb + g // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + g % 4
+    e = sf.view(-1)[off].to(torch.int32)
+    return (e << 23).view(torch.float32)
+
+
+@pytest.mark.parametrize("rows,cols", [(256, 128), (1000, 768), (130, 3072)])
+def test_quantize_matches_emulation(ops, rows, cols):
+    torch.manual_seed(0)
+    x = (torch.randn(rows, cols, device="cuda") * torch.logspace(-6, 4, cols, device="cuda")).bfloat16()
+    x[3, :64] = 0
+    q, sf = ops.ext().mxfp8_quantize(x)
+    want_q, want_s = ref.mxfp8_quantize(x.float(), -1)
+    assert torch.equal(unpack_scales(sf[0], rows, cols), want_s)
+    assert torch.equal(q.view(torch.float8_e4m3fn).float(), want_q.float())
+    # transposed: blocks run along the original rows
+    if rows % 32 == 0:
+        qt, sft = ops.ext().mxfp8_quantize_transposed(x)
+        want_q, want_s = ref.mxfp8_quantize(x.float().t().contiguous(), -1)
+        assert torch.equal(unpack_scales(sft[0], cols, rows), want_s)
+        assert torch.equal(qt.view(torch.float8_e4m3fn).float(), want_q.float())
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (1000, 768, 768), (4096, 2304, 768), (200, 1000, 256)])
+def test_gemm_mxfp8_dense(ops, m, n, k):
+    torch.manual_seed(1)
+    c = ops.ext()
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+    aq, asf = c.mxfp8_quantize(a)
+    bq, bsf = c.mxfp8_quantize(b)
+    d = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    c.gemm_mxfp8(aq, asf, bq, bsf, d)
+    want = ref.mxfp8_linear(a.float(), b.float())
+    assert rel(d, want) < 4e-3
+    assert rel(d, a.float() @ b.float().t()) < 6e-2          # and the quantisation error itself is the expected few percent
+
+
+def test_gemm_mxfp8_batched_and_grouped(ops):
+    torch.manual_seed(2)
+    c = ops.ext()
+    a = torch.randn(3, 256, 256, device="cuda").bfloat16()
+    b = torch.randn(3, 384, 256, device="cuda").bfloat16()
+    aq, asf = c.mxfp8_quantize(a)
+    bq, bsf = c.mxfp8_quantize(b)
+    d = torch.empty(3, 256, 384, device="cuda", dtype=torch.bfloat16)
+    c.gemm_mxfp8(aq, asf, bq, bsf, d, 0.5)
+    want = torch.stack([0.5 * ref.mxfp8_linear(a[i].float(), b[i].float()) for i in range(3)])
+    assert rel(d, want) < 4e-3
+    counts, e, n, k = [0, 128, 384, 256], 4, 512, 256
+    rows = sum(counts)
+    x = torch.randn(rows + 128, k, device="cuda").bfloat16()          # one spare tile beyond the routed rows
+    w = torch.randn(e, n, k, device="cuda").bfloat16()
+    tiles = torch.tensor(sum([[i] * (cnt // 128) for i, cnt in enumerate(counts)], []) + [0], dtype=torch.int32, device="cuda")
+    meta = torch.tensor([rows // 128, rows], dtype=torch.int32, device="cuda")
+    xq, xsf = c.mxfp8_quantize(x, meta[1:2])
+    wq, wsf = c.mxfp8_quantize(w)
+    y = torch.zeros(rows + 128, n, device="cuda", dtype=torch.bfloat16)
+    c.gemm_mxfp8(xq, xsf, wq, wsf, y, 1.0, tiles, meta)
+    starts = [0, 0, 128, 512]
+    want = torch.cat([ref.mxfp8_linear(x[s:s + cnt].float(), w[i].float()) for i, (s, cnt) in enumerate(zip(starts, counts))])
+    assert rel(y[:rows], want) < 4e-3
+    assert y[rows:].abs().max().item() == 0.0                           # tiles beyond num_m_tiles are not written
+
+
+def test_mxfp8_linear_autograd(ops):
+    torch.manual_seed(3)
+    x = torch.randn(4, 96, 256, device="cuda").bfloat16().requires_grad_()
+    w1 = (torch.randn(256, 256, device="cuda") * 0.05).requires_grad_()
+    w2 = (torch.randn(128, 256, device="cuda") * 0.05).requires_grad_()
+    y = ops.linear_multi(x, (w1, w2), "mxfp8")
+    g = torch.randn_like(y)
+    y.backward(g)
+    x2 = x.detach().float().requires_grad_()
+    wc = torch.cat((w1, w2)).detach().bfloat16().float().requires_grad_()
+    want = ref.mxfp8_linear(x2.reshape(-1, 256), wc)
+    assert rel(y.reshape(-1, 384), want) < 4e-3
+    g2 = g.float().reshape(-1, 384)
+    dx = ref.mxfp8_roundtrip(g2, -1) @ ref.mxfp8_roundtrip(wc.detach(), 0)
+    assert rel(x.grad.reshape(-1, 256), dx) < 4e-3
+    dw = g2.t() @ x2.detach().reshape(-1, 256)                           # weight gradient stays bf16 x bf16 -> fp32
+    assert rel(torch.cat((w1.grad, w2.grad)), dw) < 1e-4
+
+
+@pytest.mark.parametrize("top_k,experts,act", [(1, 8, "swiglu"), (2, 4, "relu2")])
+def test_mxfp8_moe_experts(ops, top_k, experts, act):
+    torch.manual_seed(4)
+    m, d, h = 1000, 128, 256
+    up_w = 2 * h if act == "swiglu" else h
+    hidden = torch.randn(m, d, device="cuda").bfloat16().requires_grad_()
+    logits = torch.randn(m, experts, device="cuda")
+    logits[:, 1] = -1e4
+    top_idx, gates, _ = ref.router_gates(logits, top_k, False)
+    gates = gates.detach().requires_grad_()
+    ups = [torch.randn(up_w, d, device="cuda").mul_(0.05).requires_grad_() for _ in range(experts)]
+    downs = [torch.randn(d, h, device="cuda").mul_(0.05).requires_grad_() for _ in range(experts)]
+    out = ops.moe_experts(hidden, top_idx, gates, ups, downs, None, None, act, "mxfp8", "mxfp8")
+    g = torch.randn_like(out)
+    out.backward(g)
+    grads = [t.grad.clone() for t in [hidden, gates] + ups + downs]
+    for t in [hidden, gates] + ups + downs:
+        t.grad = None
+    want = ops.moe_experts(hidden, top_idx, gates, ups, downs, None, None, act, "default", "default")
+    want.backward(g)
+    assert rel(out, want) < 1e-1                                          # fp8 against bf16: quantisation error only
+    for a, b in zip(grads, [t.grad for t in [hidden, gates] + ups + downs]):
+        assert rel(a, b) < 1.2e-1
+    assert grads[2 + 1].abs().max().item() == 0.0
