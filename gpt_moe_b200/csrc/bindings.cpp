@@ -287,6 +287,10 @@ torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const tor
 
 }  // namespace
 
+namespace gm {
+int* status_word(int device) { return status_tensor(device).data_ptr<int>(); }
+}  // namespace gm
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("read_status", &read_status, "status word of the current device (0 = no bounded wait gave up)");
     m.def("reset_status", &reset_status);

@@ -298,6 +298,82 @@ void cast_bf16(const Tensor& src, Tensor& dst) {
 
 }  // namespace
 
+// ---- expert-parallel dispatch / combine over peer memory ---------------------------------------------------------------
+// `table` is this rank's [world, experts] int32 count table inside a symmetric buffer; deltas[r] = rank r's base - this rank's base.
+void ep_push_counts(const Tensor& counts, Tensor& table, const std::vector<int64_t>& deltas, int64_t me) {
+    c10::cuda::CUDAGuard guard(counts.device());
+    GM_CHECK(counts.scalar_type() == torch::kInt32 && table.scalar_type() == torch::kInt32 && table.is_contiguous(), "ep_push_counts: int32 tensors");
+    auto d = to_deltas(deltas);
+    GM_CHECK(table.numel() >= static_cast<int64_t>(d.size()) * counts.numel(), "ep_push_counts: count table too small");
+    GM_CHECK(launch_ep_push_counts(counts.data_ptr<int>(), table.data_ptr<int>(), d.data(), d.size(), me, counts.numel(), stream()),
+             "ep_push_counts: at most 16 ranks and 128 experts");
+}
+
+// -> my_base [E], seg_ends [E_local], valid_ends [E_local], tile_expert [cap / 128], meta {tiles, padded rows}
+std::vector<Tensor> ep_plan(const Tensor& table, int64_t world, int64_t me, int64_t experts, int64_t cap_rows) {
+    c10::cuda::CUDAGuard guard(table.device());
+    GM_CHECK(experts % world == 0 && cap_rows % 128 == 0, "ep_plan: experts divisible by the group size, capacity a multiple of 128");
+    const int per_rank = experts / world;
+    auto opt = table.options().dtype(torch::kInt32);
+    Tensor my_base = torch::empty({experts}, opt), seg = torch::empty({per_rank}, opt), valid = torch::empty({per_rank}, opt);
+    Tensor tiles = torch::zeros({cap_rows / 128}, opt), meta = torch::empty({2}, opt);
+    GM_CHECK(launch_ep_plan(table.data_ptr<int>(), my_base.data_ptr<int>(), seg.data_ptr<int>(), valid.data_ptr<int>(), tiles.data_ptr<int>(),
+                            meta.data_ptr<int>(), world, me, experts, per_rank, cap_rows, status_word(table.device().index()), stream()),
+             "ep_plan: at most 16 ranks and 128 experts");
+    return {my_base, seg, valid, tiles, meta};
+}
+
+void ep_zero_pads(Tensor& buf, const Tensor& seg_ends, const Tensor& valid_ends) {
+    c10::cuda::CUDAGuard guard(buf.device());
+    check_bf16(buf, "buf");
+    GM_CHECK(buf.size(-1) % 8 == 0, "row width must be a multiple of 8");
+    launch_ep_zero_pads(buf.data_ptr(), seg_ends.data_ptr<int>(), valid_ends.data_ptr<int>(), seg_ends.numel(), buf.size(-1), stream());
+}
+
+// Store row (token of slot i) of `src` into the owner's `recv` buffer; returns (route_row [slots], dgates or empty).
+// gates given: rows are scaled by the slot's gate; saved_rows given as well: dgates[i] = <src row, saved_rows[i]>.
+std::vector<Tensor> ep_dispatch(const Tensor& src, const Tensor& top_idx, const Tensor& dest, const Tensor& local_seg_ends, const Tensor& my_base,
+                                const c10::optional<Tensor>& gates, const c10::optional<Tensor>& saved_rows, Tensor& recv,
+                                const std::vector<int64_t>& deltas, int64_t per_rank) {
+    c10::cuda::CUDAGuard guard(src.device());
+    check_bf16(src, "src");
+    check_bf16(recv, "recv");
+    GM_CHECK(top_idx.scalar_type() == torch::kInt64 && top_idx.is_contiguous() && top_idx.dim() == 2, "top_idx must be contiguous int64 [tokens, k]");
+    const int slots = top_idx.numel(), top_k = top_idx.size(1), d = src.size(-1);
+    GM_CHECK(src.size(0) * top_k == slots && recv.size(-1) == d, "ep_dispatch: shapes");
+    if (gates.has_value()) GM_CHECK(gates->scalar_type() == torch::kFloat32 && gates->is_contiguous() && gates->numel() == slots, "gates must be contiguous fp32");
+    if (saved_rows.has_value()) { check_bf16(*saved_rows, "saved_rows"); GM_CHECK(saved_rows->numel() == static_cast<int64_t>(slots) * d, "saved rows shape"); }
+    Tensor route_row = torch::empty({slots}, dest.options());
+    Tensor dgates = saved_rows.has_value() ? torch::empty({slots / top_k, top_k}, src.options().dtype(torch::kFloat32)) : Tensor();
+    auto dl = to_deltas(deltas);
+    GM_CHECK(launch_ep_dispatch(src.data_ptr(), reinterpret_cast<const long long*>(top_idx.data_ptr<int64_t>()), dest.data_ptr<int>(),
+                                local_seg_ends.data_ptr<int>(), my_base.data_ptr<int>(), gates.has_value() ? gates->data_ptr<float>() : nullptr,
+                                saved_rows.has_value() ? saved_rows->data_ptr() : nullptr, saved_rows.has_value() ? dgates.data_ptr<float>() : nullptr,
+                                recv.data_ptr(), route_row.data_ptr<int>(), dl.data(), dl.size(), slots, d, top_k, per_rank, recv.size(0),
+                                status_word(src.device().index()), stream()),
+             "ep_dispatch: at most 16 ranks, row width a multiple of 8");
+    if (saved_rows.has_value()) return {route_row, dgates};
+    return {route_row};
+}
+
+// out[t] = sum_k gates[t, k] * (row route_row[t, k] of the owner's `ret` buffer); keep = true also returns the loaded rows [slots, d].
+std::vector<Tensor> ep_combine(const Tensor& ret, const Tensor& top_idx, const Tensor& route_row, const c10::optional<Tensor>& gates, bool keep,
+                               const std::vector<int64_t>& deltas, int64_t per_rank) {
+    c10::cuda::CUDAGuard guard(ret.device());
+    check_bf16(ret, "ret");
+    const int tokens = top_idx.size(0), top_k = top_idx.size(1), d = ret.size(-1);
+    if (gates.has_value()) GM_CHECK(gates->scalar_type() == torch::kFloat32 && gates->is_contiguous(), "gates must be contiguous fp32");
+    Tensor out = torch::empty({tokens, d}, ret.options());
+    Tensor rows = keep ? torch::empty({tokens * top_k, d}, ret.options()) : Tensor();
+    auto dl = to_deltas(deltas);
+    GM_CHECK(launch_ep_combine(ret.data_ptr(), reinterpret_cast<const long long*>(top_idx.data_ptr<int64_t>()), route_row.data_ptr<int>(),
+                               gates.has_value() ? gates->data_ptr<float>() : nullptr, out.data_ptr(), keep ? rows.data_ptr() : nullptr, dl.data(),
+                               dl.size(), tokens, d, top_k, per_rank, ret.size(0), stream()),
+             "ep_combine: at most 16 ranks, row width a multiple of 8");
+    if (keep) return {out, rows};
+    return {out};
+}
+
 void register_kernels(pybind11::module_& m) {
     namespace py = pybind11;
     m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("eps"), py::arg("branch") = py::none(),
@@ -320,6 +396,11 @@ void register_kernels(pybind11::module_& m) {
     m.def("rs_muon_prepare", &rs_muon_prepare);
     m.def("muon_apply_push", &muon_apply_push);
     m.def("adamw_sharded", &adamw_sharded);
+    m.def("ep_push_counts", &ep_push_counts);
+    m.def("ep_plan", &ep_plan);
+    m.def("ep_zero_pads", &ep_zero_pads);
+    m.def("ep_dispatch", &ep_dispatch);
+    m.def("ep_combine", &ep_combine);
 }
 
 }  // namespace gm

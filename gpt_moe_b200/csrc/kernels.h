@@ -7,4 +7,6 @@ namespace pybind11 { class module_; }
 
 namespace gm {
 void register_kernels(pybind11::module_& m);
+// device pointer of the per-device status word that kernels set when a bounded wait or a capacity check gives up
+int* status_word(int device);
 }

@@ -58,4 +58,15 @@ bool launch_adamw_sharded(float* params, const float* grads, void* m, void* v, b
                           long long n, float lr, float beta1, float beta2, float eps, float bc1, float bc2_sqrt,
                           const long long* grad_deltas, const long long* param_deltas, int world, cudaStream_t s);
 
+// ---- expert-parallel dispatch / combine over peer memory (comm/ep_comm.cu) -------------------------------------------
+bool launch_ep_push_counts(const int* counts, int* table, const long long* deltas, int world, int me, int experts, cudaStream_t s);
+bool launch_ep_plan(const int* table, int* my_base, int* seg_ends, int* valid_ends, int* tile_expert, int* meta, int world, int me,
+                    int experts, int per_rank, int cap_rows, int* status, cudaStream_t s);
+void launch_ep_zero_pads(void* buf, const int* seg_ends, const int* valid_ends, int per_rank, int d, cudaStream_t s);
+bool launch_ep_dispatch(const void* src, const long long* idx, const int* dest, const int* local_seg_ends, const int* my_base,
+                        const float* gates, const void* saved_rows, float* dgates, void* recv, int* route_row, const long long* deltas,
+                        int world, int slots, int d, int top_k, int per_rank, int cap_rows, int* status, cudaStream_t s);
+bool launch_ep_combine(const void* ret, const long long* idx, const int* route_row, const float* gates, void* out, void* keep_rows,
+                       const long long* deltas, int world, int tokens, int d, int top_k, int per_rank, int cap_rows, cudaStream_t s);
+
 }  // namespace gm

@@ -38,15 +38,21 @@ class _AllToAll(torch.autograd.Function):
         return out, None, None, None
 
 
-def attach_expert_parallel(model, group) -> None:
-    """Give every MoE layer of `model` its expert-parallel process group."""
+def attach_expert_parallel(model, group, fused: bool = False, capacity_factor: float = 2.0) -> None:
+    """Give every MoE layer of `model` its expert-parallel process group.  `fused` selects the CUDA path whose dispatch and
+    combine kernels store / load rows directly in the peers' memory (`parallel.ep_fused`); it needs symmetric memory."""
     from ..models.moe import MoE
     for module in model.modules():
         if isinstance(module, MoE):
             module.ep_group = group
+            module.ep_fused = fused
+            module.ep_capacity_factor = capacity_factor
 
 
 def expert_parallel_moe(moe, hidden: Tensor, top_idx: Tensor, gates: Tensor, args: dict) -> Tensor:
+    from . import ep_fused
+    if ep_fused.supported(moe, hidden):
+        return ep_fused.fused_expert_parallel_moe(moe, hidden, top_idx, gates, args)
     group, ep, per_rank = moe.ep_group, moe.ep_size, moe.experts_per_rank
     top_k = top_idx.shape[1]
     _, order, inverse, offsets = ref.counted_expert_routing(top_idx, moe.num_experts)

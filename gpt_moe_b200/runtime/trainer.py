@@ -129,7 +129,9 @@ class Trainer:
                 group = dist.new_group(ranks)
                 if self.rank in ranks:
                     self.ep_group = group
-            attach_expert_parallel(self.raw_gpt_model, self.ep_group)
+            attach_expert_parallel(self.raw_gpt_model, self.ep_group,
+                                   fused=self.device_type == "cuda" and cfg.use_fused_collectives,
+                                   capacity_factor=cfg.ep_capacity_factor)
 
         self.optimizers = self.raw_gpt_model.configure_optimizers(
             cfg.adamw_max_lr, cfg.adamw_betas, cfg.adamw_eps, cfg.adamw_weight_decay, self.device_type,
@@ -484,6 +486,9 @@ class Trainer:
         if self.watchdog is not None:
             self.watchdog.stop()
         du.barrier()
+        if self.ep_size > 1 and self.device_type == "cuda":
+            from ..parallel.ep_fused import release_workspaces
+            release_workspaces()
         if du.is_dist():
             dist.destroy_process_group()
 

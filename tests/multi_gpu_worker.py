@@ -11,7 +11,7 @@ import torch
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def run(fused: bool, steps: int = 4):
+def run(fused: bool, steps: int = 4, ep: int = 1):
     from gpt_moe_b200.config import get_preset
     from gpt_moe_b200.runtime.trainer import Trainer
     from gpt_moe_b200.schedules.token import custom_schedule
@@ -23,6 +23,7 @@ def run(fused: bool, steps: int = 4):
     tc.swa_values_schedule = {"fn": custom_schedule, "kwargs": {"values": [128]}}
     tc.kernel_warmup_train_steps = 0
     tc.use_fused_collectives = fused
+    tc.expert_parallel_size = ep
     trainer = Trainer(gc, tc, device_type="cuda", quiet=True)
     want = "FusedEngine" if fused else "CudaHostEngine"
     assert type(trainer.engine).__name__ == want, type(trainer.engine).__name__
@@ -37,9 +38,68 @@ def run(fused: bool, steps: int = 4):
     return trainer, losses, params
 
 
+class _Shard:
+    """What `expert_parallel_moe` reads of a MoE layer."""
+
+    def __init__(self, group, world, experts, fused):
+        self.ep_group, self.ep_size, self.num_experts, self.experts_per_rank = group, world, experts, experts // world
+        self.ep_fused, self.ep_capacity_factor = fused, float(world)
+
+
+def check_expert_parallel_ops():
+    """Fused dispatch/combine kernels and the NCCL all-to-all path against all experts computed locally."""
+    import torch.distributed as dist
+    from gpt_moe_b200.ops import cuda_ops, reference as ref
+    from gpt_moe_b200.parallel.ep import expert_parallel_moe
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    experts, top_k, d, h, tokens = 4 * world, 2, 128, 256, 777
+    torch.manual_seed(7)
+    ups = [torch.randn(2 * h, d, device=dev).mul_(0.05).requires_grad_() for _ in range(experts)]
+    downs = [torch.randn(d, h, device=dev).mul_(0.05).requires_grad_() for _ in range(experts)]
+    torch.manual_seed(100 + rank)
+    hidden = torch.randn(tokens, d, device=dev).bfloat16().requires_grad_()
+    logits = torch.randn(tokens, experts, device=dev)
+    logits[:, 1] = -1e4
+    top_idx, gates, _ = ref.router_gates(logits, top_k, False)
+    gates = gates.detach().requires_grad_()
+    g = torch.randn(tokens, d, device=dev).bfloat16()
+    tensors = [hidden, gates] + ups + downs
+
+    def grads_of(out):
+        out.backward(g)
+        got = [t.grad.clone() if t.grad is not None else torch.zeros_like(t) for t in tensors]
+        for t in tensors:
+            t.grad = None
+        return got
+
+    want_out = cuda_ops.moe_experts(hidden, top_idx, gates, ups, downs, None, None, "swiglu", "default", "default")
+    want = grads_of(want_out)
+    for t in want[2:]:
+        dist.all_reduce(t)                                    # an expert's gradient sums over the tokens of every rank
+    lo, n = rank * (experts // world), experts // world
+    args = dict(up_weights=ups[lo:lo + n], down_weights=downs[lo:lo + n], up_biases=None, down_biases=None, activation="swiglu",
+                up_precision="default", down_precision="default")
+    worst = 0.0
+    for fused in (True, False, True):
+        out = expert_parallel_moe(_Shard(dist.group.WORLD, world, experts, fused), hidden, top_idx, gates, args)
+        got = grads_of(out)
+        errs = [((out.float() - want_out.float()).norm() / want_out.float().norm()).item()]
+        local = [0, 1] + [2 + lo + i for i in range(n)] + [2 + experts + lo + i for i in range(n)]
+        for i in local:
+            errs.append(((got[i].float() - want[i].float()).norm() / (want[i].float().norm() + 1e-6)).item())
+        worst = max(worst, max(errs))
+    cuda_ops.check_status()
+    return worst
+
+
 def main():
     trainer, fused_losses, fused_params = run(True)
     _, nccl_losses, nccl_params = run(False)
+    ep_err = check_expert_parallel_ops()
+    _, ep_fused_losses, _ = run(True, ep=2)
+    _, ep_nccl_losses, _ = run(False, ep=2)
+    ep_ok = ep_err < 2e-2 and all(abs(a - b) < 3e-2 for a, b in zip(ep_fused_losses, ep_nccl_losses))
     ok = all(abs(a - b) < 3e-2 for a, b in zip(fused_losses, nccl_losses))
     worst = ("", 0.0)
     for n in fused_params:
@@ -48,13 +108,16 @@ def main():
         err = err / 4 if "router" in n else err
         if err > worst[1]:
             worst = (n, err)
-    ok = ok and worst[1] < 5e-2
+    ok = ok and worst[1] < 5e-2 and ep_ok
     flag = torch.tensor([1.0 if ok else 0.0], device=trainer.device)
     torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
     if trainer.rank == 0:
         print("fused losses", fused_losses)
         print("nccl  losses", nccl_losses)
         print("worst parameter difference", worst)
+        print("expert-parallel ops: worst relative error", ep_err)
+        print("expert-parallel fused losses", ep_fused_losses)
+        print("expert-parallel nccl  losses", ep_nccl_losses)
         print("MULTI_GPU_ENGINE_OK" if flag.item() == 1.0 else "MULTI_GPU_ENGINE_MISMATCH", flush=True)
     trainer.close()
 
