@@ -138,7 +138,7 @@ def run_ours(args) -> dict:
         "dtype": "bf16" if args.precision == "default" else "bf16+mxfp8", "data": "synthetic",
         "config": {"model": "GPT-MoE-small (12L d768 12x64 heads, SWA 1024, 8 SwiGLU experts h3072 top-1, vocab 50304)",
                    "global_batch": cfg.gpu_batch_size_train * world, "seq_len": cfg.seq_len_train,
-                   "parallelism": f"dp{world}", "optimizer": "muon(polar express)+adamw",
+                   "parallelism": f"dp{world}" + (f"+ep{trainer.ep_size}" if trainer.ep_size > 1 else ""), "optimizer": "muon(polar express)+adamw",
                    "l2": "per-step working set >> 126 MB L2; no explicit flush"},
         "clocks": clocks,
         "e2e": {"value": tokens_per_step * args.steps / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,

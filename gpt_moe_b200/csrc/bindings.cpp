@@ -137,14 +137,14 @@ void gemm_bf16(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& d,
     // split-K: a long contraction with too few output tiles to fill the GPU (weight gradients) is shared by several CTAs per tile
     p.split_k = 1;
     if (mode == gm::GEMM_DENSE && p.out_fp32) {
-        const int64_t tiles = ((p.M + 127) / 128) * ((p.N + 255) / 256) * p.batch;
+        const int64_t tiles = ((p.M + 255) / 256) * 2 * ((p.N + 255) / 256) * p.batch;      // CTA pairs own 256-row tiles
         const int64_t k_blocks = (p.K + 63) / 64;
         if (tiles * 2 <= sm_count() && k_blocks >= 16)
             p.split_k = static_cast<int>(std::min<int64_t>(sm_count() / tiles, k_blocks / 8));
         if (p.split_k > 1 && !accumulate) d.zero_();
     }
     const CUtensorMap& ta = operand_map(a, a_mn, 128);
-    const CUtensorMap& tb = operand_map(b, b_mn, 256);
+    const CUtensorMap& tb = operand_map(b, b_mn, 128);
     const int eb = p.out_fp32 ? 4 : 2;
     const CUtensorMap& td = cached_map(d.data_ptr(), eb, p.N, p.M, d.dim() == 3 ? d.size(0) : 1, p.ldd * eb,
                                        d.dim() == 3 ? d.stride(0) * eb : 0, 128 / eb, 128, 128);

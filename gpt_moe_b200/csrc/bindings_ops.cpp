@@ -113,7 +113,7 @@ std::vector<Tensor> route(const Tensor& top_idx, int64_t experts) {
     c10::cuda::CUDAGuard guard(top_idx.device());
     GM_CHECK(top_idx.is_cuda() && top_idx.scalar_type() == torch::kInt64 && top_idx.is_contiguous(), "top_idx must be contiguous int64");
     const int slots = top_idx.numel();
-    const int cap = (slots + 127) / 128 * 128 + experts * 128;
+    const int cap = (slots + 255) / 256 * 256 + experts * 256;      // every expert segment is padded to 256 rows
     const int chunks = (slots + 1023) / 1024;
     auto opt = top_idx.options().dtype(torch::kInt32);
     Tensor hist = torch::empty({2, chunks, experts}, opt);
@@ -312,7 +312,7 @@ void ep_push_counts(const Tensor& counts, Tensor& table, const std::vector<int64
 // -> my_base [E], seg_ends [E_local], valid_ends [E_local], tile_expert [cap / 128], meta {tiles, padded rows}
 std::vector<Tensor> ep_plan(const Tensor& table, int64_t world, int64_t me, int64_t experts, int64_t cap_rows) {
     c10::cuda::CUDAGuard guard(table.device());
-    GM_CHECK(experts % world == 0 && cap_rows % 128 == 0, "ep_plan: experts divisible by the group size, capacity a multiple of 128");
+    GM_CHECK(experts % world == 0 && cap_rows % 256 == 0, "ep_plan: experts divisible by the group size, capacity a multiple of 256");
     const int per_rank = experts / world;
     auto opt = table.options().dtype(torch::kInt32);
     Tensor my_base = torch::empty({experts}, opt), seg = torch::empty({per_rank}, opt), valid = torch::empty({per_rank}, opt);

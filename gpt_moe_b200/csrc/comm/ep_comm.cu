@@ -8,7 +8,7 @@
 //
 //   ep_push_counts   this rank's per-expert slot counts are stored into row `me` of every rank's count table
 //   ep_plan          (one block) from the full W x E table every rank derives, identically, the owners' layouts:
-//                    segment of expert e in its owner's buffer = rows of source 0, source 1, ..., padded to 128;
+//                    segment of expert e in its owner's buffer = rows of source 0, source 1, ..., padded to 256;
 //                    emits my_base[e] (first row of MY rows for expert e) and this rank's own plan
 //                    (segment ends, valid ends, tile -> local expert table, tile / row totals)
 //   ep_zero_pads     zero the pad rows of the local receive buffer (between a segment's valid end and its padded end)
@@ -28,6 +28,7 @@ namespace gm {
 
 constexpr int EP_MAX_RANKS = 16;
 constexpr int EP_MAX_EXPERTS = 128;
+constexpr int EP_SEG_PAD = 256;           // same unit as the local routing: a CTA pair of the GEMM owns 256 rows of one expert
 struct EpDeltas { long long d[EP_MAX_RANKS]; };
 
 __global__ void ep_push_counts_kernel(const int* __restrict__ counts, int* __restrict__ table, EpDeltas peers, int world, int me, int experts) {
@@ -60,7 +61,7 @@ ep_plan_kernel(const int* __restrict__ table, int* __restrict__ my_base, int* __
     if (e < experts) {
         const int first = e / per_rank * per_rank;
         int s = 0;
-        for (int j = first; j < e; ++j) s += (total[j] + 127) / 128 * 128;
+        for (int j = first; j < e; ++j) s += (total[j] + EP_SEG_PAD - 1) / EP_SEG_PAD * EP_SEG_PAD;
         start[e] = s;
         my_base[e] = s + before[e];
     }
@@ -68,15 +69,15 @@ ep_plan_kernel(const int* __restrict__ table, int* __restrict__ my_base, int* __
     const int lo = me * per_rank;
     if (e < per_rank) {
         const int g = lo + e;
-        const int padded = (total[g] + 127) / 128 * 128;
+        const int padded = (total[g] + EP_SEG_PAD - 1) / EP_SEG_PAD * EP_SEG_PAD;
         seg_ends[e] = min(start[g] + padded, cap_rows);
         valid_ends[e] = min(start[g] + total[g], cap_rows);
         for (int t = start[g] / 128; t < (start[g] + padded) / 128 && t < cap_rows / 128; ++t) tile_expert[t] = e;
     }
     if (e == 0) {
         const int last = lo + per_rank - 1;
-        int rows = start[last] + (total[last] + 127) / 128 * 128;
-        if (rows > cap_rows) { atomicExch(status, 501); rows = cap_rows / 128 * 128; }
+        int rows = start[last] + (total[last] + EP_SEG_PAD - 1) / EP_SEG_PAD * EP_SEG_PAD;
+        if (rows > cap_rows) { atomicExch(status, 501); rows = cap_rows / EP_SEG_PAD * EP_SEG_PAD; }
         meta[0] = rows / 128;
         meta[1] = rows;
     }

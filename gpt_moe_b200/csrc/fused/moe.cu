@@ -3,8 +3,8 @@
 //
 // Layout produced by routing: the S = M*k (token, slot) pairs are bucketed by expert, order inside a bucket
 // is the original slot order (stable, no atomics decide placement), and every bucket is padded to a multiple
-// of 128 rows.  Consequences: a 128-row GEMM tile never straddles two experts, the weight-gradient GEMM can
-// contract over whole padded segments, and pad rows are written as zeros so they contribute nothing.
+// of 256 rows (SEG_PAD).  Consequences: the 256-row tile of a CTA pair of the GEMM never straddles two experts, the
+// weight-gradient GEMM can contract over whole padded segments, and pad rows are written as zeros so they contribute nothing.
 //   dest[slot]        row of the packed buffer that holds this (token, slot)
 //   src_of_row[row]   slot stored in that row, -1 for pad rows
 //   seg_ends[e]       cumulative padded end of expert e;  counts[e] the true row count
@@ -18,6 +18,7 @@ namespace gm {
 
 constexpr int ROUTE_CHUNK = 1024;
 constexpr int MAX_EXPERTS = 128;
+constexpr int SEG_PAD = 256;
 
 __global__ void __launch_bounds__(ROUTE_CHUNK)
 route_count_kernel(const long long* __restrict__ idx, int* __restrict__ chunk_hist, int slots, int experts) {
@@ -48,7 +49,7 @@ route_plan_kernel(const int* __restrict__ chunk_hist, int* __restrict__ chunk_st
         int acc = 0;
         for (int i = 0; i < experts; ++i) {
             pstart[i] = acc;
-            acc += (cnt[i] + 127) / 128 * 128;
+            acc += (cnt[i] + SEG_PAD - 1) / SEG_PAD * SEG_PAD;
             seg_ends[i] = acc;
         }
         pstart[experts] = acc;

@@ -1,9 +1,13 @@
 // Persistent, warp-specialised bf16 GEMM for sm_100a: D = alpha * A * B^T (+ beta * C) (+ D).
 //
-// One CTA per SM walks a list of 128 x 256 output tiles.  Roles:
-//   warp 0  : TMA producer   - fills a 4-stage ring of {A 128x64, B 256x64} bf16 tiles (128B swizzle)
-//   warp 1  : MMA issuer     - one thread issues tcgen05.mma (M128 N256 K16) into one of two TMEM
-//                              accumulators (2 x 256 columns), commits to free the smem stage
+// CTAs run as pairs (a cluster of two on neighbouring SMs, tcgen05 cta_group::2).  A pair walks a list of
+// 256 x 256 output tiles: each CTA owns 128 of the rows and stages only HALF of the B tile, the tensor cores of
+// both SMs read both halves, so a CTA pulls 32 KB instead of 48 KB through L2 per 128 x 256 x 64 block of work -
+// the main loop of a one-CTA kernel is bound by exactly that traffic.  Roles inside each CTA:
+//   warp 0  : TMA producer   - fills a 6-stage ring of {A 128x64, B 128x64} bf16 tiles (128B swizzle); the
+//                              bytes of both CTAs are counted on the leader's (even CTA's) barrier
+//   warp 1  : MMA issuer     - leader CTA only: one thread issues tcgen05.mma (M256 N256 K16) into one of
+//                              two TMEM accumulators (2 x 256 columns in each CTA), commits to both CTAs
 //   warps 2-5: epilogue      - tcgen05.ld the finished accumulator (thread = row), scale / add C, convert,
 //                              stage 128-byte-swizzled slabs in shared memory and hand them to TMA
 //                              (store, or reduce-add for fp32 accumulation and split-K); overlaps the
@@ -27,10 +31,11 @@
 
 namespace gm {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 6;
+constexpr int BN_HALF = BN / 2;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN_HALF * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int GEMM_THREADS = 192;
-constexpr int GROUP_M = 8;
+constexpr int GROUP_M = 4;               // in pair tiles (256 rows each)
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int STAGING_BYTES = 2 * BM * 128;      // two slabs of [128 rows][128 bytes]
 
@@ -42,32 +47,35 @@ struct TileCoord {
     bool store_zeros;  // no contraction work at all for this output tile: write zeros unless accumulating
 };
 
+// Work is enumerated in PAIR tiles (two vertically adjacent 128-row tiles, one per CTA of the pair); `m_tiles` counts
+// the 128-row tiles rounded up to an even number.
 __device__ __forceinline__ int total_tiles(const GemmParams& p, int& m_tiles, int& n_tiles) {
     n_tiles = (p.N + BN - 1) / BN;
     if (p.mode == GEMM_GROUPED_M) {
-        m_tiles = *p.num_m_tiles;
-        return m_tiles * n_tiles;
+        m_tiles = (*p.num_m_tiles + 1) & ~1;
+        return m_tiles / 2 * n_tiles;
     }
-    m_tiles = (p.M + BM - 1) / BM;
-    return m_tiles * n_tiles * p.batch * p.split_k;
+    m_tiles = ((p.M + BM - 1) / BM + 1) & ~1;
+    return m_tiles / 2 * n_tiles * p.batch * p.split_k;
 }
 
-__device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, int m_tiles, int n_tiles) {
+__device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, int cta_rank, int m_tiles, int n_tiles) {
     TileCoord t;
     int split = 0;
     if (p.mode != GEMM_GROUPED_M && p.split_k > 1) {
         split = tile % p.split_k;
         tile /= p.split_k;
     }
-    const int per_batch = m_tiles * n_tiles;
+    const int m_pairs = m_tiles / 2;
+    const int per_batch = m_pairs * n_tiles;
     const int z = (p.mode == GEMM_GROUPED_M) ? 0 : tile / per_batch;
     int r = tile - z * per_batch;
-    // grouped raster: GROUP_M row-tiles share their column sweep so A tiles stay in L2
+    // grouped raster: GROUP_M pair-rows share their column sweep so A tiles stay in L2
     const int group = r / (GROUP_M * n_tiles);
     const int first_m = group * GROUP_M;
-    const int rows_in_group = min(GROUP_M, m_tiles - first_m);
+    const int rows_in_group = min(GROUP_M, m_pairs - first_m);
     r -= group * GROUP_M * n_tiles;
-    const int mt = first_m + r % rows_in_group;
+    const int mt = 2 * (first_m + r % rows_in_group) + cta_rank;
     const int nt = r / rows_in_group;
     t.m0 = mt * BM;
     t.n0 = nt * BN;
@@ -79,8 +87,8 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, i
     if (p.mode == GEMM_GROUPED_M) {
         t.az = 0;
         t.dz = 0;
-        t.bz = p.tile_expert[mt];
-        t.m_limit = m_tiles * BM;
+        t.bz = p.tile_expert[mt & ~1];          // both tiles of a pair belong to one expert (segments are padded to 256 rows)
+        t.m_limit = *p.num_m_tiles * BM;
     } else if (p.mode == GEMM_GROUPED_K) {
         const int begin = z == 0 ? 0 : p.seg_ends[z - 1];
         t.az = t.bz = 0;
@@ -113,59 +121,63 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cta_rank = static_cast<int>(cluster_ctarank());     // 0 = leader of the pair
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 128); }
+        // acc_empty of the leader collects the epilogue threads of both CTAs
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 256); }
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
         tma_prefetch_desc(&tmap_d);
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc_pair(tmem_slot, TMEM_COLS); tmem_relinquish_pair(); }
     tc_fence_before();
-    __syncthreads();
+    cluster_sync_all();                                            // both CTAs' barriers exist before either signals the other
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
     int m_tiles, n_tiles;
     const int tiles = total_tiles(p, m_tiles, n_tiles);
+    const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
     bool ok = true;
 
     if (warp == 0) {
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                const TileCoord t = tile_coord(p, tile, m_tiles, n_tiles);
+            for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
+                const TileCoord t = tile_coord(p, tile, cta_rank, m_tiles, n_tiles);
                 for (int kb = 0; kb < t.k_blocks; ++kb) {
                     if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(p.status, 101); ok = false; break; }
-                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    if (cta_rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);      // both CTAs' copies land on the leader's barrier
                     uint8_t* a_dst = smem + s * STAGE_BYTES;
                     uint8_t* b_dst = a_dst + A_BYTES;
                     const int k = t.k_begin + kb * BK;
+                    const int bn0 = t.n0 + cta_rank * BN_HALF;                          // this CTA stages its half of the B tile
                     if (A_MN) {
-                        for (int i = 0; i < BM / 64; ++i) tma_load_3d(a_dst + i * (64 * BK * 2), &tmap_a, &full[s], t.m0 + 64 * i, k, t.az);
+                        for (int i = 0; i < BM / 64; ++i) tma_load_3d_pair(a_dst + i * (64 * BK * 2), &tmap_a, &full[s], t.m0 + 64 * i, k, t.az);
                     } else {
-                        tma_load_3d(a_dst, &tmap_a, &full[s], k, t.m0, t.az);
+                        tma_load_3d_pair(a_dst, &tmap_a, &full[s], k, t.m0, t.az);
                     }
                     if (B_MN) {
-                        for (int i = 0; i < BN / 64; ++i) tma_load_3d(b_dst + i * (64 * BK * 2), &tmap_b, &full[s], t.n0 + 64 * i, k, t.bz);
+                        for (int i = 0; i < BN_HALF / 64; ++i) tma_load_3d_pair(b_dst + i * (64 * BK * 2), &tmap_b, &full[s], bn0 + 64 * i, k, t.bz);
                     } else {
-                        tma_load_3d(b_dst, &tmap_b, &full[s], k, t.n0, t.bz);
+                        tma_load_3d_pair(b_dst, &tmap_b, &full[s], k, bn0, t.bz);
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
             // K-major: 8-row groups are 1024 B apart, 16 K-elements = 32 B.  MN-major: 64-element column slabs are
             // BK*128 B apart (leading offset), 8-K-row groups 1024 B apart, 16 K-rows = 2048 B.
             constexpr uint32_t a_lbo = A_MN ? BK * 128 : 16, b_lbo = B_MN ? BK * 128 : 16;
             constexpr uint32_t a_kstep = A_MN ? 2048 : 32, b_kstep = B_MN ? 2048 : 32;
             int s = 0; uint32_t ph = 0; int acc = 0; uint32_t acc_ph = 0;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                const TileCoord t = tile_coord(p, tile, m_tiles, n_tiles);
+            for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
+                const TileCoord t = tile_coord(p, tile, cta_rank, m_tiles, n_tiles);
                 if (t.k_blocks == 0) continue;
                 if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1)) { atomicExch(p.status, 102); ok = false; break; }
                 tc_fence_after();
@@ -177,13 +189,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     for (int k4 = 0; k4 < BK / 16; ++k4) {
                         const uint64_t adesc = make_smem_desc(a_addr + k4 * a_kstep, a_lbo, 1024);
                         const uint64_t bdesc = make_smem_desc(b_addr + k4 * b_kstep, b_lbo, 1024);
-                        umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k4) != 0);
+                        umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb | k4) != 0);
                     }
-                    umma_commit(&empty[s]);
+                    umma_commit_pair(&empty[s]);
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 if (!ok) break;
-                umma_commit(&acc_full[acc]);
+                umma_commit_pair(&acc_full[acc]);
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
         }
@@ -199,8 +211,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint8_t* my_row = staging + row_in_tile * 128;
         const int sw = row_in_tile & 7;
         int acc = 0; uint32_t acc_ph = 0;
-        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-            const TileCoord t = tile_coord(p, tile, m_tiles, n_tiles);
+        for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
+            const TileCoord t = tile_coord(p, tile, cta_rank, m_tiles, n_tiles);
             const bool have_acc = t.k_blocks != 0;
             if (!have_acc && !(t.store_zeros && !p.accumulate)) continue;      // nothing to add, nothing to clear
             const int row = t.m0 + row_in_tile;
@@ -270,14 +282,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
                 if (have_acc && round == rounds - 1) {                        // accumulator fully read: release it early
                     tc_fence_before();
-                    mbar_arrive(&acc_empty[acc]);
+                    mbar_arrive_cluster(&acc_empty[acc], 0);
                 }
                 fence_proxy_async();
                 asm volatile("bar.sync 1, 128;" ::: "memory");                 // slabs complete and visible to the async proxy
                 if (leader) {
                     for (int sl = 0; sl < 2; ++sl) {
                         const int col = round_col0 + sl * cols_per_slab;
-                        if (col >= t.n_limit) break;
+                        if (col >= t.n_limit || t.m0 >= t.m_limit) break;
                         const uint32_t src = smem_u32(staging + sl * (BM * 128));
                         if (reduce) {
                             asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4}], [%1];"
@@ -293,7 +305,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (have_acc) {
                 // tiles narrower than BN leave the round loop early: the accumulator is released here in that case
                 const int rounds_done = min(rounds, (t.n_limit - t.n0 + chunks_per_round * 32 - 1) / (chunks_per_round * 32));
-                if (rounds_done < rounds) { tc_fence_before(); mbar_arrive(&acc_empty[acc]); }
+                if (rounds_done < rounds) { tc_fence_before(); mbar_arrive_cluster(&acc_empty[acc], 0); }
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
         }
@@ -302,7 +314,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
     // common teardown: every path (including a timed-out wait) reaches it, so TMEM is always released
     tc_fence_before();
-    __syncthreads();
+    cluster_sync_all();                       // the partner no longer reads this CTA's shared memory or signals its barriers
     if (warp == 1) {
         if (*reinterpret_cast<volatile int*>(p.status) != 0) {
             // a wait gave up: give any TMA copy still in flight time to land before the CTA's smem is recycled
@@ -310,7 +322,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             while (clock64() - start < 200000) {}
         }
         tc_fence_after();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
     }
 }
 
@@ -326,8 +338,19 @@ static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, 
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    kernel<<<sms, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, td, p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sms & ~1);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = GEMM_SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, ta, tb, td, p);
 }
 
 cudaError_t launch_gemm_bf16(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmParams& p, bool a_mn,

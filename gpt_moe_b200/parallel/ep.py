@@ -38,7 +38,7 @@ class _AllToAll(torch.autograd.Function):
         return out, None, None, None
 
 
-def attach_expert_parallel(model, group, fused: bool = False, capacity_factor: float = 2.0) -> None:
+def attach_expert_parallel(model, group, fused: bool = False, capacity_factor: float = 0.0) -> None:
     """Give every MoE layer of `model` its expert-parallel process group.  `fused` selects the CUDA path whose dispatch and
     combine kernels store / load rows directly in the peers' memory (`parallel.ep_fused`); it needs symmetric memory."""
     from ..models.moe import MoE

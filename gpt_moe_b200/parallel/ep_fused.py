@@ -11,9 +11,10 @@ forward of one MoE layer is then
 
 and the backward runs the same two kernels the other way round (dispatch of gate * dOut with the gate gradient's dot
 product in the same pass; combine of the input gradients with unit gates).  No row is staged, sorted or copied for the
-exchange, and there are no host synchronisations: sizes stay on the device, buffers are sized by a capacity factor
-(`capacity_factor * slots` rows per rank, capped at the worst case) and a row that does not fit sets the device
-status word, which invalidates the step instead of dropping tokens silently.
+exchange, and there are no host synchronisations: sizes stay on the device.  Buffers hold the worst case by default
+(every slot of every rank routed to one rank); `ep_capacity_factor > 0` shrinks them to that many times a rank's own
+slots, and a row that then does not fit sets the device status word, which invalidates the step instead of dropping
+tokens silently.
 
 The NCCL path (`parallel.ep.expert_parallel_moe`) is the baseline this replaces and the oracle of the tests.
 The reference keeps all experts on every rank (model/feedforward/moe.py:30); expert parallelism is an addition.
@@ -35,14 +36,15 @@ class EPWorkspace:
     """Symmetric buffers of one expert-parallel group: count table, one return buffer, one gradient receive buffer, and one
     receive buffer per MoE layer (it doubles as the saved grouped-GEMM input of that layer, so nothing is copied)."""
 
-    def __init__(self, group, slots: int, d: int, experts: int, device, capacity_factor: float = 2.0) -> None:
+    def __init__(self, group, slots: int, d: int, experts: int, device, capacity_factor: float = 0.0) -> None:
         from .fused_engine import SymmetricBuffer
         self.group = group
         self.world, self.rank = du.world_size(group), du.get_rank(group)
         assert experts % self.world == 0
         self.experts, self.per_rank, self.d, self.slots = experts, experts // self.world, d, slots
-        rows = min(self.world * slots, int(capacity_factor * slots + 0.5))
-        self.cap_rows = (rows + 127) // 128 * 128 + self.per_rank * 128
+        # capacity_factor <= 0: room for the worst case (every slot of every rank routed to this rank's experts)
+        rows = self.world * slots if capacity_factor <= 0 else min(self.world * slots, int(capacity_factor * slots + 0.5))
+        self.cap_rows = (rows + 255) // 256 * 256 + self.per_rank * 256
         self.device = device
         self._make = lambda numel, dtype: SymmetricBuffer(numel, dtype, device, group)
         self.table = self._make(self.world * experts, torch.int32)
@@ -156,7 +158,7 @@ def fused_expert_parallel_moe(moe, hidden: Tensor, top_idx: Tensor, gates: Tenso
     if args["up_biases"] is not None or args["down_biases"] is not None:
         raise NotImplementedError("expert biases are not supported by the fused expert-parallel path")
     h2 = hidden.reshape(-1, hidden.shape[-1])
-    ws = workspace_for(moe.ep_group, top_idx.numel(), h2.shape[-1], moe.num_experts, hidden.device, float(getattr(moe, "ep_capacity_factor", 2.0)))
+    ws = workspace_for(moe.ep_group, top_idx.numel(), h2.shape[-1], moe.num_experts, hidden.device, float(getattr(moe, "ep_capacity_factor", 0.0)))
     return _FusedEPMoEFn.apply(h2, gates, top_idx, args["activation"], ws, id(moe), *args["up_weights"], *args["down_weights"])
 
 

@@ -68,7 +68,7 @@ def test_dispatch_and_combine_between_two_virtual_ranks(ops):
     c = ops.ext()
     torch.manual_seed(6)
     world, experts, per_rank, top_k, d, tokens = 2, 6, 3, 2, 64, 300
-    cap = 2 * tokens * top_k // 128 * 128 + 128 + per_rank * 128
+    cap = 2048 + per_rank * 256
     tables = [torch.zeros(world * experts, dtype=torch.int32, device="cuda") for _ in range(world)]
     recvs = [torch.full((cap, d), 7.0, device="cuda").bfloat16() for _ in range(world)]
     rets = [torch.empty(cap, d, device="cuda").bfloat16() for _ in range(world)]
@@ -106,7 +106,7 @@ def test_dispatch_and_combine_between_two_virtual_ranks(ops):
             assert valid_ends[j].item() == start + n
             assert torch.equal(recvs[owner][start:start + n], want)
             end = seg_ends[j].item()
-            assert end == start + (n + 127) // 128 * 128
+            assert end == start + (n + 255) // 256 * 256
             assert recvs[owner][start + n:end].abs().max().item() == 0.0 if end > start + n else True
             assert (tiles[start // 128:end // 128] == j).all()
             start = end

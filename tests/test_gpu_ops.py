@@ -52,8 +52,8 @@ def test_gemm_epilogue_batched_grouped(ops):
     acc = torch.ones(256, 512, device="cuda")
     c.gemm_bf16(a[0], b[0], acc, False, False, 1.0, 0.0, None, True)
     assert rel(acc, 1 + a[0].float() @ b[0].float().t()) < 1e-5
-    # ragged expert segments with an empty expert (counts padded to 128 by construction)
-    counts, e, n, k = [0, 128, 384, 256], 4, 512, 256
+    # ragged expert segments with an empty expert (segments padded to 256 rows, the unit of a CTA pair, by construction)
+    counts, e, n, k = [0, 256, 768, 512], 4, 512, 256
     rows = sum(counts)
     x = torch.randn(rows, k, device="cuda").bfloat16()
     w = torch.randn(e, n, k, device="cuda").bfloat16()
@@ -61,11 +61,11 @@ def test_gemm_epilogue_batched_grouped(ops):
     meta = torch.tensor([rows // 128, rows], dtype=torch.int32, device="cuda")
     y = torch.zeros(rows, n, device="cuda", dtype=torch.bfloat16)
     c.gemm_bf16(x, w, y, False, False, 1.0, 0.0, None, False, 1, tiles, meta, None)
-    starts = [0, 0, 128, 512]
+    starts = [0, 0, 256, 1024]
     want = torch.cat([x[s:s + cnt].float() @ w[i].float().t() for i, (s, cnt) in enumerate(zip(starts, counts))])
     assert rel(y, want) < BF16_TOL
     dy = torch.randn(rows, n, device="cuda").bfloat16()
-    ends = torch.tensor([0, 128, 512, 768], dtype=torch.int32, device="cuda")
+    ends = torch.tensor([0, 256, 1024, 1536], dtype=torch.int32, device="cuda")
     dw = torch.full((e, n, k), 7.0, device="cuda")
     c.gemm_bf16(dy, x, dw, True, True, 1.0, 0.0, None, False, 2, None, None, ends)
     want = torch.stack([dy[s:s + cnt].float().t() @ x[s:s + cnt].float() for s, cnt in zip(starts, counts)])
