@@ -77,15 +77,18 @@ std::vector<Tensor> residual_bwd(const Tensor& dxn, const Tensor& branch, const 
 
 // qkv: [tokens, row_stride] bf16 holding q heads then k heads (then anything else) of width D each.
 // forward writes rotated+normalised q,k into `out` (same layout; may alias a separate buffer)
+// `copy_cols` trailing columns after the q and k heads (the value heads of a packed row) are copied from x to out as they are
 void rope_qknorm_fwd(const Tensor& x, Tensor& out, const OptTensor& cos_t, const OptTensor& sin_t, const OptTensor& q_scale,
                      const OptTensor& k_scale, int64_t seq_len, int64_t q_heads, int64_t k_heads, int64_t head_dim, double eps,
-                     bool rms, double smin, double smax) {
+                     bool rms, double smin, double smax, int64_t copy_cols) {
     c10::cuda::CUDAGuard guard(x.device());
     GM_CHECK(x.scalar_type() == torch::kBFloat16 && x.stride(-1) == 1 && out.stride(-1) == 1, "rope_qknorm needs bf16 rows");
+    GM_CHECK(copy_cols % 8 == 0 && ((q_heads + k_heads) * head_dim) % 8 == 0 && x.stride(0) % 8 == 0 && out.stride(0) % 8 == 0 &&
+             (q_heads + k_heads) * head_dim + copy_cols <= x.size(-1), "rope_qknorm: pass-through columns must be 16-byte aligned");
     const long long tokens = x.size(0);
     GM_CHECK(launch_rope_qknorm(false, head_dim, x.data_ptr(), nullptr, out.data_ptr(), fptr(cos_t), fptr(sin_t), fptr(q_scale),
                                 fptr(k_scale), nullptr, tokens, seq_len, q_heads, k_heads, x.stride(0), out.stride(0),
-                                static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), stream()),
+                                static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), copy_cols, stream()),
              "unsupported head size for rope_qknorm");
 }
 
@@ -101,7 +104,7 @@ Tensor rope_qknorm_bwd(const Tensor& x, const Tensor& dy, Tensor& dx, const OptT
     GM_CHECK(x.stride(0) == dx.stride(0), "dx must share x's row stride");
     GM_CHECK(launch_rope_qknorm(true, head_dim, x.data_ptr(), dy.data_ptr(), dx.data_ptr(), fptr(cos_t), fptr(sin_t), fptr(q_scale),
                                 fptr(k_scale), partial.data_ptr<float>(), tokens, seq_len, q_heads, k_heads, x.stride(0),
-                                dy.stride(0), static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), stream()),
+                                dy.stride(0), static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), 0, stream()),
              "unsupported head size for rope_qknorm");
     Tensor dscale = torch::empty({heads}, partial.options());
     launch_column_sum(partial.data_ptr<float>(), dscale.data_ptr<float>(), blocks, heads, 0, stream());
@@ -380,7 +383,9 @@ void register_kernels(pybind11::module_& m) {
           py::arg("alpha") = py::none(), py::arg("beta") = py::none());
     m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("dres") = py::none());
     m.def("residual_bwd", &residual_bwd);
-    m.def("rope_qknorm_fwd", &rope_qknorm_fwd);
+    m.def("rope_qknorm_fwd", &rope_qknorm_fwd, py::arg("x"), py::arg("out"), py::arg("cos"), py::arg("sin"), py::arg("q_scale"), py::arg("k_scale"),
+          py::arg("seq_len"), py::arg("q_heads"), py::arg("k_heads"), py::arg("head_dim"), py::arg("eps"), py::arg("rms"), py::arg("smin"),
+          py::arg("smax"), py::arg("copy_cols") = 0);
     m.def("rope_qknorm_bwd", &rope_qknorm_bwd);
     m.def("route", &route);
     m.def("gather_rows", &gather_rows);

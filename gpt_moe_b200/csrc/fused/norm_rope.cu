@@ -260,75 +260,114 @@ void launch_column_sum(const float* partial, float* out, int rows, int cols, int
 // heads use k_scale.  pos = t % seq_len indexes the cos/sin tables [seq_len, D/2].
 // forward:  r = rope(x);  g = rsqrt(mean|sum(r^2) + eps);  y = r * g * clamp(scale[h])
 // backward: dr = g*s*(dy - r * g^2 * mean|sum(dy*r));  dx = rope^T(dr);  dscale[h] += sum(dy * r * g) inside the clamp range
+// One warp works on ROPE_GROUP heads of a token at a time so that several independent 128-byte rows are in flight per warp.
+// Forward also copies `copy_cols` trailing columns (the value heads of a packed QKV row) from x to out; backward may run
+// in place (out == dy): every element is read by the thread that later writes it.
+constexpr int ROPE_GROUP = 4;
+
 template <int D, bool BWD>
 __global__ void __launch_bounds__(256)
-rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ out,
+rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* dy, __nv_bfloat16* out,
                    const float* __restrict__ cos_t, const float* __restrict__ sin_t, const float* __restrict__ q_scale,
                    const float* __restrict__ k_scale, float* __restrict__ dscale_partial, long long tokens, int seq_len,
-                   int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin, float smax) {
+                   int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin, float smax,
+                   int copy_cols) {
     constexpr int PAIRS = D / 2;
     constexpr int PER_LANE = (PAIRS + 31) / 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int heads = q_heads + k_heads;
-    const long long total = tokens * heads;
+    const int groups = (heads + ROPE_GROUP - 1) / ROPE_GROUP;
+    const long long total = tokens * groups;
+    const bool has_norm = q_scale != nullptr;
     __shared__ float ds_smem[8][64];
     if (BWD) {
         for (int i = threadIdx.x; i < 8 * 64; i += blockDim.x) (&ds_smem[0][0])[i] = 0.f;
         __syncthreads();
     }
     for (long long idx = static_cast<long long>(blockIdx.x) * 8 + warp; idx < total; idx += static_cast<long long>(gridDim.x) * 8) {
-        const long long t = idx / heads;
-        const int h = static_cast<int>(idx - t * heads);
+        const long long t = idx / groups;
+        const int h0 = static_cast<int>(idx - t * groups) * ROPE_GROUP;
         const int pos = static_cast<int>(t % seq_len);
-        const float raw = h < q_heads ? (q_scale ? q_scale[h] : 1.f) : (k_scale ? k_scale[h - q_heads] : 1.f);
-        const bool has_norm = q_scale != nullptr;
-        const float sc = fminf(fmaxf(raw, smin), smax);
-        float r1[PER_LANE], r2[PER_LANE], c[PER_LANE], sn[PER_LANE], g1[PER_LANE], g2[PER_LANE];
-        float ss = 0.f, dot = 0.f;
+        float r1[ROPE_GROUP][PER_LANE], r2[ROPE_GROUP][PER_LANE], g1[ROPE_GROUP][PER_LANE], g2[ROPE_GROUP][PER_LANE];
+        float c[PER_LANE], sn[PER_LANE], ss[ROPE_GROUP], dot[ROPE_GROUP];
 #pragma unroll
         for (int i = 0; i < PER_LANE; ++i) {
             const int pr = lane + 32 * i;
-            r1[i] = r2[i] = g1[i] = g2[i] = 0.f; c[i] = 1.f; sn[i] = 0.f;
-            if (pr < PAIRS) {
-                const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(x + t * x_stride + h * D + 2 * pr);
-                const float2 xf = __bfloat1622float2(xv);
-                if (cos_t) { c[i] = cos_t[pos * PAIRS + pr]; sn[i] = sin_t[pos * PAIRS + pr]; }
-                r1[i] = xf.x * c[i] - xf.y * sn[i];
-                r2[i] = xf.x * sn[i] + xf.y * c[i];
-                ss += r1[i] * r1[i] + r2[i] * r2[i];
+            c[i] = 1.f; sn[i] = 0.f;
+            if (cos_t && pr < PAIRS) { c[i] = cos_t[pos * PAIRS + pr]; sn[i] = sin_t[pos * PAIRS + pr]; }
+        }
+        __nv_bfloat162 xv[ROPE_GROUP][PER_LANE], gv[ROPE_GROUP][PER_LANE];
+#pragma unroll
+        for (int u = 0; u < ROPE_GROUP; ++u) {
+#pragma unroll
+            for (int i = 0; i < PER_LANE; ++i) {
+                const int pr = lane + 32 * i;
+                xv[u][i] = __floats2bfloat162_rn(0.f, 0.f);
+                gv[u][i] = xv[u][i];
+                if (h0 + u < heads && pr < PAIRS) {
+                    xv[u][i] = *reinterpret_cast<const __nv_bfloat162*>(x + t * x_stride + (h0 + u) * D + 2 * pr);
+                    if (BWD) gv[u][i] = *reinterpret_cast<const __nv_bfloat162*>(dy + t * o_stride + (h0 + u) * D + 2 * pr);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < ROPE_GROUP; ++u) {
+            ss[u] = dot[u] = 0.f;
+#pragma unroll
+            for (int i = 0; i < PER_LANE; ++i) {
+                const float2 xf = __bfloat1622float2(xv[u][i]);
+                r1[u][i] = xf.x * c[i] - xf.y * sn[i];
+                r2[u][i] = xf.x * sn[i] + xf.y * c[i];
+                ss[u] += r1[u][i] * r1[u][i] + r2[u][i] * r2[u][i];
                 if (BWD) {
-                    const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dy + t * o_stride + h * D + 2 * pr));
-                    g1[i] = gf.x; g2[i] = gf.y;
-                    dot += g1[i] * r1[i] + g2[i] * r2[i];
+                    const float2 gf = __bfloat1622float2(gv[u][i]);
+                    g1[u][i] = gf.x; g2[u][i] = gf.y;
+                    dot[u] += g1[u][i] * r1[u][i] + g2[u][i] * r2[u][i];
                 }
             }
         }
-        float gain = 1.f, mult = 1.f;
-        if (has_norm) {
-            ss = warp_sum(ss);
-            gain = rsqrtf((rms ? ss / D : ss) + eps);
-            mult = gain * sc;
-        }
-        if (BWD) {
-            dot = warp_sum(dot);
-            if (has_norm && lane == 0 && raw >= smin && raw <= smax) ds_smem[warp][h] += dot * gain;
-            const float coef = has_norm ? gain * gain * (rms ? dot / D : dot) : 0.f;
 #pragma unroll
-            for (int i = 0; i < PER_LANE; ++i) {
-                const int pr = lane + 32 * i;
-                if (pr < PAIRS) {
-                    const float d1 = mult * (g1[i] - r1[i] * coef), d2 = mult * (g2[i] - r2[i] * coef);
-                    const float o1 = d1 * c[i] + d2 * sn[i], o2 = -d1 * sn[i] + d2 * c[i];
-                    *reinterpret_cast<__nv_bfloat162*>(out + t * x_stride + h * D + 2 * pr) = __floats2bfloat162_rn(o1, o2);
+        for (int u = 0; u < ROPE_GROUP; ++u) {
+            const int h = h0 + u;
+            if (h >= heads) break;                                                     // uniform across the warp
+            const float raw = h < q_heads ? (q_scale ? q_scale[h] : 1.f) : (k_scale ? k_scale[h - q_heads] : 1.f);
+            const float sc = fminf(fmaxf(raw, smin), smax);
+            float gain = 1.f, mult = 1.f;
+            if (has_norm) {
+                const float total_ss = warp_sum(ss[u]);
+                gain = rsqrtf((rms ? total_ss / D : total_ss) + eps);
+                mult = gain * sc;
+            }
+            if (BWD) {
+                const float d = warp_sum(dot[u]);
+                if (has_norm && lane == 0 && raw >= smin && raw <= smax) ds_smem[warp][h] += d * gain;
+                const float coef = has_norm ? gain * gain * (rms ? d / D : d) : 0.f;
+#pragma unroll
+                for (int i = 0; i < PER_LANE; ++i) {
+                    const int pr = lane + 32 * i;
+                    if (pr < PAIRS) {
+                        const float d1 = mult * (g1[u][i] - r1[u][i] * coef), d2 = mult * (g2[u][i] - r2[u][i] * coef);
+                        const float o1 = d1 * c[i] + d2 * sn[i], o2 = -d1 * sn[i] + d2 * c[i];
+                        *reinterpret_cast<__nv_bfloat162*>(out + t * x_stride + h * D + 2 * pr) = __floats2bfloat162_rn(o1, o2);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < PER_LANE; ++i) {
+                    const int pr = lane + 32 * i;
+                    if (pr < PAIRS)
+                        *reinterpret_cast<__nv_bfloat162*>(out + t * o_stride + h * D + 2 * pr) = __floats2bfloat162_rn(r1[u][i] * mult, r2[u][i] * mult);
                 }
             }
-        } else {
-#pragma unroll
-            for (int i = 0; i < PER_LANE; ++i) {
-                const int pr = lane + 32 * i;
-                if (pr < PAIRS)
-                    *reinterpret_cast<__nv_bfloat162*>(out + t * o_stride + h * D + 2 * pr) = __floats2bfloat162_rn(r1[i] * mult, r2[i] * mult);
-            }
+        }
+    }
+    if (!BWD && copy_cols > 0) {
+        const int vecs = copy_cols / 8;
+        const long long n = tokens * vecs;
+        for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+            const long long t = i / vecs;
+            const int v = static_cast<int>(i - t * vecs);
+            *reinterpret_cast<uint4*>(out + t * o_stride + heads * D + v * 8) = *reinterpret_cast<const uint4*>(x + t * x_stride + heads * D + v * 8);
         }
     }
     if (BWD && dscale_partial) {
@@ -343,25 +382,25 @@ rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 }
 
 int rope_blocks(long long tokens, int heads) {
-    const long long want = (tokens * heads + 7) / 8;
+    const long long want = (tokens * ((heads + ROPE_GROUP - 1) / ROPE_GROUP) + 7) / 8;
     return static_cast<int>(want < 2368 ? want : 2368);
 }
 
 bool launch_rope_qknorm(bool bwd, int D, const void* x, const void* dy, void* out, const float* cos_t, const float* sin_t,
                         const float* q_scale, const float* k_scale, float* dscale_partial, long long tokens, int seq_len,
                         int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin,
-                        float smax, cudaStream_t s) {
+                        float smax, int copy_cols, cudaStream_t s) {
     if (q_heads + k_heads > 64) return false;
     const int blocks = rope_blocks(tokens, q_heads + k_heads);
 #define GM_ROPE(DD)                                                                                                            \
     if (bwd)                                                                                                                   \
         rope_qknorm_kernel<DD, true><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), \
             static_cast<__nv_bfloat16*>(out), cos_t, sin_t, q_scale, k_scale, dscale_partial, tokens, seq_len, q_heads, k_heads,  \
-            x_stride, o_stride, eps, rms, smin, smax);                                                                         \
+            x_stride, o_stride, eps, rms, smin, smax, 0);                                                                      \
     else                                                                                                                       \
         rope_qknorm_kernel<DD, false><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), nullptr,                     \
             static_cast<__nv_bfloat16*>(out), cos_t, sin_t, q_scale, k_scale, nullptr, tokens, seq_len, q_heads, k_heads,        \
-            x_stride, o_stride, eps, rms, smin, smax);
+            x_stride, o_stride, eps, rms, smin, smax, copy_cols);
     switch (D) {
         case 32: GM_ROPE(32); break;
         case 64: GM_ROPE(64); break;

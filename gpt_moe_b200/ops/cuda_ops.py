@@ -349,10 +349,11 @@ class _RopeQKNormFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, qkv: Tensor, cos, sin, q_scale, k_scale, seq_len, hq, hk, d, eps, rms, smin, smax):
-        out = qkv.clone()
+        out = torch.empty_like(qkv)
         qs = None if q_scale is None else q_scale.detach().float().reshape(-1).contiguous()
         ks = None if k_scale is None else k_scale.detach().float().reshape(-1).contiguous()
-        ext().rope_qknorm_fwd(qkv, out, cos, sin, qs, ks, seq_len, hq, hk, d, eps, rms, smin, smax)
+        # the kernel rotates / normalises the q and k heads and passes the remaining (value) columns through
+        ext().rope_qknorm_fwd(qkv, out, cos, sin, qs, ks, seq_len, hq, hk, d, eps, rms, smin, smax, qkv.shape[-1] - (hq + hk) * d)
         ctx.save_for_backward(qkv, cos if cos is not None else qkv.new_empty(0), sin if sin is not None else qkv.new_empty(0),
                               qs if qs is not None else qkv.new_empty(0), ks if ks is not None else qkv.new_empty(0))
         ctx.cfg = (seq_len, hq, hk, d, eps, rms, smin, smax, cos is not None, q_scale is not None)
@@ -365,7 +366,7 @@ class _RopeQKNormFn(torch.autograd.Function):
         qkv, cos, sin, qs, ks = ctx.saved_tensors
         seq_len, hq, hk, d, eps, rms, smin, smax, has_rope, has_norm = ctx.cfg
         dout = dout if dout.is_contiguous() else dout.contiguous()
-        dx = dout.clone()                     # v columns pass through unchanged
+        dx = dout                             # in place: q and k columns are rewritten, v columns pass through unchanged
         dscale = ext().rope_qknorm_bwd(qkv, dout, dx, cos if has_rope else None, sin if has_rope else None,
                                        qs if has_norm else None, ks if has_norm else None, seq_len, hq, hk, d, eps, rms, smin, smax)
         dq = dk = None
