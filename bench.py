@@ -75,6 +75,13 @@ class ClockSampler:
                 "samples": len(clocks), "reasons": sorted(reasons)}
 
 
+MODEL_NAMES = {
+    "small": "GPT-MoE-small (12L d768 12x64 heads, SWA 1024, 8 SwiGLU experts h3072 top-1, vocab 50304)",
+    "wide_ep": "GPT-MoE-wide (12L d768 12x64 heads, SWA 1024, 32 SwiGLU experts h1536 top-2, expert parallel, vocab 50304)",
+    "mla": "GPT-MoE-MLA (24L d1024 16 heads, MLA kv rank 512 + rope 64, 64 routed SwiGLU experts h1024 top-1 + shared h2048, expert parallel, vocab 50304)",
+}
+
+
 def run_ours(args) -> dict:
     import torch
     import torch.distributed as dist
@@ -83,7 +90,7 @@ def run_ours(args) -> dict:
     from gpt_moe_b200.parallel import dist_utils as du
     from gpt_moe_b200.runtime.trainer import Trainer
 
-    gpt_config, training_config = get_preset("small", precision=args.precision)
+    gpt_config, training_config = get_preset(args.preset, precision=args.precision)
     apply_overrides(gpt_config, training_config, args.overrides)
     training_config.kernel_warmup_train_steps = 0
     trainer = Trainer(gpt_config, training_config, device_type="cuda", quiet=True)
@@ -136,7 +143,7 @@ def run_ours(args) -> dict:
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if args.precision == "default" else "bf16+mxfp8", "data": "synthetic",
-        "config": {"model": "GPT-MoE-small (12L d768 12x64 heads, SWA 1024, 8 SwiGLU experts h3072 top-1, vocab 50304)",
+        "config": {"model": MODEL_NAMES.get(args.preset, args.preset),
                    "global_batch": cfg.gpu_batch_size_train * world, "seq_len": cfg.seq_len_train,
                    "parallelism": f"dp{world}" + (f"+ep{trainer.ep_size}" if trainer.ep_size > 1 else ""), "optimizer": "muon(polar express)+adamw",
                    "l2": "per-step working set >> 126 MB L2; no explicit flush"},
@@ -157,6 +164,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default="default", choices=["default", "mxfp8"])
+    ap.add_argument("--preset", default="small", choices=["small", "wide_ep", "mla"],
+                    help="small is the headline configuration; wide_ep and mla are the expert-parallel configurations (ours only)")
     ap.add_argument("--set", dest="overrides", action="append", default=[])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

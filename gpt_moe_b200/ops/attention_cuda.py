@@ -56,9 +56,14 @@ def attention(q: Tensor, k: Tensor, v: Tensor, *, causal: bool = True, window=No
         if attention_tc.supported(q, k, v, softcap_value):
             return attention_tc.attention(q, k, v, window=w, scale=scale)
         flash = _flash_attn()
-        if flash and q.dtype == torch.bfloat16 and dk == v.shape[-1] and softcap_value == 0.0:
-            return flash(q, k, v, softmax_scale=scale, causal=True, window_size=(w if w is not None else -1, 0 if w is not None else -1)
-                         if w is not None else (-1, -1))
+        dv = v.shape[-1]
+        if flash and q.dtype == torch.bfloat16 and dv <= dk and dk <= 256 and softcap_value == 0.0:
+            # head sizes the tcgen05 kernel is not built for (e.g. MLA: 128-wide keys, 64-wide values) go to the library kernel;
+            # it wants equal widths, so narrower values are zero-padded and the padding columns of the result dropped
+            vp = v if dv == dk else F.pad(v, (0, dk - dv))
+            out = flash(q, k, vp, softmax_scale=scale if scale is not None else dk ** -0.5, causal=True,
+                        window_size=(w, 0) if w is not None else (-1, -1))
+            return out if dv == dk else out[..., :dv]
     if softcap_value > 0.0:
         return ref.attention(q, k, v, causal=causal, window=w, scale=scale, softcap_value=softcap_value,
                              tanh_backend=tanh_backend, attn_mask=attn_mask, document_ids=document_ids)

@@ -118,3 +118,44 @@ def test_fused_engine_matches_plain_optimizers_on_one_gpu():
         # the tiny router matrices take a bf16 Polar Express whose result is sensitive to summation order
         tol = 2e-1 if "router" in n else 5e-2
         assert (pa[n] - pb[n]).norm().item() <= tol * pb[n].norm().item() + 1e-3, n
+
+
+def test_mla_shared_expert_model_against_cpu_and_trains():
+    """Multi-head latent attention (128-wide keys, 64-wide values) plus a shared expert: loss against the CPU oracle, then training."""
+    from gpt_moe_b200.models.gpt import GPT
+    from gpt_moe_b200.runtime.trainer import Trainer
+    torch.manual_seed(1)
+    gc, tc = _tiny()
+    gc.use_mla, gc.mla_kv_rank, gc.mla_qk_content_dim, gc.mla_qk_rope_dim, gc.mla_value_dim = True, 128, 64, 64, 64
+    gc.moe_shared_expert_hidden_dim = 256
+    cpu = GPT(gc, tc)
+    with torch.no_grad():
+        for block in cpu.transformer.h:
+            block.mlp.router.weight.mul_(40.0)
+    gpu = copy.deepcopy(cpu).cuda()
+    ids = torch.randint(0, gc.vocab_size, (2, 257))
+    x, y = ids[:, :-1], ids[:, 1:]
+    loss_g = gpu(x.cuda(), y.cuda())[0]
+    loss_g.backward()
+    loss_c = cpu(x, y)[0]
+    assert abs(loss_c.item() - loss_g.item()) < 3e-2
+    assert all(torch.isfinite(p.grad).all() for p in gpu.parameters() if p.grad is not None)
+    tc.kernel_warmup_train_steps = 0
+    trainer = Trainer(gc, tc, device_type="cuda", quiet=True)
+    ids = torch.randint(0, 512, (2, 257))
+    batch = [(ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), None)]
+    losses = [trainer.train_step(batch)["loss"] for _ in range(8)]
+    assert losses[-1] < losses[0] - 0.5, losses
+
+
+def test_mxfp8_precision_trains():
+    from gpt_moe_b200.config import get_preset
+    from gpt_moe_b200.runtime.trainer import Trainer
+    gc, tc = _tiny()
+    tc.linear_config = get_preset("small", precision="mxfp8")[1].linear_config
+    tc.kernel_warmup_train_steps = 0
+    trainer = Trainer(gc, tc, device_type="cuda", quiet=True)
+    ids = torch.randint(0, 512, (2, 257))
+    batch = [(ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), None)]
+    losses = [trainer.train_step(batch)["loss"] for _ in range(8)]
+    assert losses[-1] < losses[0] - 0.5, losses
