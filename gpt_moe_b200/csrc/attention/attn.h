@@ -1,4 +1,4 @@
-// Host-visible interface of the tcgen05 attention kernels (head size 64).
+// Host-visible interface of the tcgen05 attention kernels (value heads 64 wide; query/key heads 64 or 128 wide).
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -9,6 +9,7 @@ namespace gm {
 struct AttnParams {
     int batch, heads, seq_len;      // q heads
     int group;                      // q heads per kv head
+    int qk_dim;                     // width of a query / key head: 64 or 128
     int q_col0, k_col0, v_col0;     // first column of head 0 inside each tensor map
     int window;                     // inclusive look-back W (a query sees keys q-W..q); >= seq_len means plain causal
     const int* window_ptr;          // optional device-resident window (overrides `window`)
@@ -19,10 +20,10 @@ struct AttnParams {
     float* lse;                     // [batch, heads, seq] natural-log LSE of the scaled scores
     // backward
     const float* delta;             // [batch, heads, seq] rowsum(dO * O)
-    float* dq_accum;                // [tokens, heads*64] fp32, zero-initialised; reduced into by TMA
-    void* dk;                       // [tokens, kv_heads*64] bf16
+    float* dq_accum;                // [tokens, heads*qk_dim] fp32, zero-initialised; reduced into by TMA
+    void* dk;                       // [tokens, kv_heads*qk_dim] bf16; dv is [tokens, kv_heads*64] with its own pitch
     void* dv;
-    long long dkv_stride;
+    long long dkv_stride, dv_stride;
     int* status;
 };
 

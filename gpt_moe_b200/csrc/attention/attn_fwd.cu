@@ -1,4 +1,5 @@
-// Causal sliding-window attention forward for sm_100a, head size 64, bf16 in / bf16 out + fp32 log-sum-exp.
+// Causal sliding-window attention forward for sm_100a, bf16 in / bf16 out + fp32 log-sum-exp.  Value heads are 64 wide;
+// query / key heads are 64 wide (DQK = 64) or 128 wide (DQK = 128: multi-head latent attention, content + rotary parts).
 //
 // One CTA owns 128 query rows of one (batch, head) and walks the key tiles its rows can see:
 // keys kv with  q - W <= kv <= q  (window inclusive, W + 1 keys), tiles of 128 keys.
@@ -23,7 +24,8 @@ namespace gm {
 
 constexpr int AT_BM = 128, AT_BN = 128, AT_D = 64;
 constexpr int AT_THREADS = 288;
-constexpr int Q_BYTES = AT_BM * AT_D * 2, K_BYTES = AT_BN * AT_D * 2, V_BYTES = K_BYTES, P_BYTES = AT_BM * AT_BN * 2;
+constexpr int SLAB_BYTES = AT_BM * 64 * 2;          // 128 rows x 64 bf16 columns (one 128-byte-swizzled TMA box)
+constexpr int V_BYTES = AT_BN * AT_D * 2;
 constexpr uint32_t AT_TMEM_COLS = 256;
 constexpr int POLY_PER_8 = 3;     // of every 8 exponentials, how many run on the FMA pipe instead of MUFU
 constexpr int KV_STAGES = 2;      // key/value tiles in flight: the global->shared latency of a strided tile spans more than one tile of work
@@ -106,9 +108,12 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_addr, uint32_t p_addr, i
     row_sum = (sum[0] + sum[1]) + (sum[2] + sum[3]);
 }
 
-__global__ void __launch_bounds__(AT_THREADS, 2)
+template <int DQK>
+__global__ void __launch_bounds__(AT_THREADS, DQK == 64 ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+    constexpr int QK_SLABS = DQK / 64;
+    constexpr int Q_BYTES = QK_SLABS * SLAB_BYTES, K_BYTES = Q_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sq = smem;
@@ -134,7 +139,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int n_tiles = (q0 + AT_BM - kv_lo) / AT_BN;
     const int kv_head = head / p.group;                       // grouped-query attention: several q heads share a kv head
     const int row0 = batch * p.seq_len;
-    const int q_col = p.q_col0 + head * AT_D, k_col = p.k_col0 + kv_head * AT_D, v_col = p.v_col0 + kv_head * AT_D;
+    const int q_col = p.q_col0 + head * DQK, k_col = p.k_col0 + kv_head * DQK, v_col = p.v_col0 + kv_head * AT_D;
 
     if (threadIdx.x == 0) {
         mbar_init(bar_q, 1); mbar_init(bar_s, 1); mbar_init(bar_p, 256); mbar_init(bar_o, 1);
@@ -156,15 +161,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const uint32_t q_addr = smem_u32(sq), k_addr = smem_u32(sk), v_addr = smem_u32(sv);
             auto issue_s = [&](int st) {
 #pragma unroll
-                for (int k4 = 0; k4 < AT_D / 16; ++k4)
-                    umma_f16(tmem_s, make_smem_desc(q_addr + k4 * 32, 16, 1024),
-                             make_smem_desc(k_addr + st * K_BYTES + k4 * 32, 16, 1024), idesc_s, k4 != 0);
+                for (int sl = 0; sl < QK_SLABS; ++sl)
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4)
+                        umma_f16(tmem_s, make_smem_desc(q_addr + sl * SLAB_BYTES + k4 * 32, 16, 1024),
+                                 make_smem_desc(k_addr + st * K_BYTES + sl * SLAB_BYTES + k4 * 32, 16, 1024), idesc_s, (sl | k4) != 0);
                 umma_commit(bar_s);
             };
             auto load_k = [&](int tile) {
                 const int st = tile % KV_STAGES;
                 mbar_expect_tx(&bar_k[st], K_BYTES);
-                tma_load_2d_as3d(sk + st * K_BYTES, &tmap_k, &bar_k[st], k_col, row0 + kv_lo + tile * AT_BN);
+#pragma unroll
+                for (int sl = 0; sl < QK_SLABS; ++sl)
+                    tma_load_2d_as3d(sk + st * K_BYTES + sl * SLAB_BYTES, &tmap_k, &bar_k[st], k_col + 64 * sl, row0 + kv_lo + tile * AT_BN);
             };
             auto load_v = [&](int tile) {
                 const int st = tile % KV_STAGES;
@@ -172,7 +181,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 tma_load_2d_as3d(sv + st * V_BYTES, &tmap_v, &bar_v[st], v_col, row0 + kv_lo + tile * AT_BN);
             };
             mbar_expect_tx(bar_q, Q_BYTES);
-            tma_load_2d_as3d(sq, &tmap_q, bar_q, q_col, row0 + q0);
+#pragma unroll
+            for (int sl = 0; sl < QK_SLABS; ++sl) tma_load_2d_as3d(sq + sl * SLAB_BYTES, &tmap_q, bar_q, q_col + 64 * sl, row0 + q0);
             for (int t = 0; t < KV_STAGES && t < n_tiles; ++t) { load_k(t); load_v(t); }
             if (!mbar_wait(bar_q, 0) || !mbar_wait(&bar_k[0], 0)) { atomicExch(p.status, 201); ok = false; }
             if (ok) { tc_fence_after(); issue_s(0); }
@@ -276,20 +286,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
 }
 
-constexpr int AT_FWD_SMEM = Q_BYTES + KV_STAGES * (K_BYTES + V_BYTES) + 1024 + 128 + 2 * AT_BM * 4;
-
-cudaError_t launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t stream) {
+template <int DQK>
+static cudaError_t launch_fwd_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t stream) {
+    constexpr int smem = (DQK / 64) * SLAB_BYTES * (1 + KV_STAGES) + KV_STAGES * V_BYTES + 1024 + 128 + 2 * AT_BM * 4;
+    auto kernel = attn_fwd_kernel<DQK>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_FWD_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return e;
         configured = true;
     }
     dim3 grid(p.seq_len / AT_BM, p.heads, p.batch);
-    attn_fwd_kernel<<<grid, AT_THREADS, AT_FWD_SMEM, stream>>>(tq, tk, tv, p);
+    kernel<<<grid, AT_THREADS, smem, stream>>>(tq, tk, tv, p);
     return cudaGetLastError();
+}
+
+cudaError_t launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t stream) {
+    if (p.qk_dim == 128) return launch_fwd_variant<128>(tq, tk, tv, p, stream);
+    return launch_fwd_variant<64>(tq, tk, tv, p, stream);
 }
 
 }  // namespace gm

@@ -236,16 +236,17 @@ const CUtensorMap& head_map(const torch::Tensor& t, int box_rows) {
 std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, int64_t window, double scale) {
     c10::cuda::CUDAGuard guard(q.device());
     const int B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
-    GM_CHECK(D == 64 && v.size(3) == 64 && T % 128 == 0 && H % Hkv == 0, "attention kernel: head size 64, sequence length multiple of 128");
+    GM_CHECK((D == 64 || D == 128) && k.size(3) == D && v.size(3) == 64 && T % 128 == 0 && H % Hkv == 0,
+             "attention kernel: query/key heads 64 or 128 wide, value heads 64 wide, sequence length multiple of 128");
     gm::AttnParams p;
     std::memset(&p, 0, sizeof(p));
-    p.batch = B; p.heads = H; p.seq_len = T; p.group = H / Hkv;
+    p.batch = B; p.heads = H; p.seq_len = T; p.group = H / Hkv; p.qk_dim = D;
     p.window = static_cast<int>(std::min<int64_t>(window, T));
     p.scale = static_cast<float>(scale);
     p.scale_log2e = static_cast<float>(scale * 1.4426950408889634);
-    auto out = torch::empty({B, T, H, D}, q.options());
+    auto out = torch::empty({B, T, H, 64}, q.options());
     auto lse = torch::empty({B, H, T}, q.options().dtype(torch::kFloat32));
-    p.out = out.data_ptr(); p.out_stride = H * D; p.lse = lse.data_ptr<float>();
+    p.out = out.data_ptr(); p.out_stride = H * 64; p.lse = lse.data_ptr<float>();
     p.status = status_tensor(q.device().index()).data_ptr<int>();
     cudaError_t e = gm::launch_attn_fwd(head_map(q, 128), head_map(k, 128), head_map(v, 128), p, current_stream());
     GM_CHECK(e == cudaSuccess, cudaGetErrorString(e));
@@ -259,13 +260,14 @@ torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const tor
                        double scale) {
     c10::cuda::CUDAGuard guard(q.device());
     const int B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
-    GM_CHECK(D == 64 && T % 128 == 0 && H % Hkv == 0, "attention kernel: head size 64, sequence length multiple of 128");
-    GM_CHECK(dk.stride(3) == 1 && dk.stride(2) == 64 && dv.stride(3) == 1 && dv.stride(2) == 64 && dk.stride(1) == dv.stride(1),
-             "dk/dv must be token-major views with contiguous heads and equal row pitch");
+    GM_CHECK((D == 64 || D == 128) && k.size(3) == D && v.size(3) == 64 && T % 128 == 0 && H % Hkv == 0,
+             "attention kernel: query/key heads 64 or 128 wide, value heads 64 wide, sequence length multiple of 128");
+    GM_CHECK(dk.stride(3) == 1 && dk.stride(2) == D && dv.stride(3) == 1 && dv.stride(2) == 64 && dk.stride(1) % 8 == 0 && dv.stride(1) % 8 == 0,
+             "dk/dv must be token-major views with contiguous heads and 16-byte aligned rows");
     GM_CHECK(out.stride(3) == 1 && out.stride(2) == 64 && d_out.stride(3) == 1 && d_out.stride(2) == 64, "out/d_out layout");
     gm::AttnParams p;
     std::memset(&p, 0, sizeof(p));
-    p.batch = B; p.heads = H; p.seq_len = T; p.group = H / Hkv;
+    p.batch = B; p.heads = H; p.seq_len = T; p.group = H / Hkv; p.qk_dim = D;
     p.window = static_cast<int>(std::min<int64_t>(window, T));
     p.scale = static_cast<float>(scale);
     p.scale_log2e = static_cast<float>(scale * 1.4426950408889634);
@@ -274,7 +276,7 @@ torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const tor
     auto dq = torch::zeros({B, T, H, D}, lse.options());
     p.delta = delta.data_ptr<float>();
     p.dq_accum = dq.data_ptr<float>();
-    p.dk = dk.data_ptr(); p.dv = dv.data_ptr(); p.dkv_stride = dk.stride(1);
+    p.dk = dk.data_ptr(); p.dv = dv.data_ptr(); p.dkv_stride = dk.stride(1); p.dv_stride = dv.stride(1);
     p.status = status_tensor(q.device().index()).data_ptr<int>();
     const CUtensorMap& tdq = cached_map(dq.data_ptr(), 4, static_cast<uint64_t>(H) * D, static_cast<uint64_t>(B) * T, 1,
                                         static_cast<uint64_t>(H) * D * 4, 0, 32, 128, 128);

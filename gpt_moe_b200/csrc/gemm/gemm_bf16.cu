@@ -4,14 +4,15 @@
 // 256 x 256 output tiles: each CTA owns 128 of the rows and stages only HALF of the B tile, the tensor cores of
 // both SMs read both halves, so a CTA pulls 32 KB instead of 48 KB through L2 per 128 x 256 x 64 block of work -
 // the main loop of a one-CTA kernel is bound by exactly that traffic.  Roles inside each CTA:
-//   warp 0  : TMA producer   - fills a 6-stage ring of {A 128x64, B 128x64} bf16 tiles (128B swizzle); the
+//   warp 0  : TMA producer   - fills a 5-stage ring of {A 128x64, B 128x64} bf16 tiles (128B swizzle); the
 //                              bytes of both CTAs are counted on the leader's (even CTA's) barrier
 //   warp 1  : MMA issuer     - leader CTA only: one thread issues tcgen05.mma (M256 N256 K16) into one of
 //                              two TMEM accumulators (2 x 256 columns in each CTA), commits to both CTAs
-//   warps 2-5: epilogue      - tcgen05.ld the finished accumulator (thread = row), scale / add C, convert,
-//                              stage 128-byte-swizzled slabs in shared memory and hand them to TMA
-//                              (store, or reduce-add for fp32 accumulation and split-K); overlaps the
-//                              next tile's main loop.  TMA clips rows/columns outside the tensor.
+//   warps 2-9: epilogue      - tcgen05.ld the finished accumulator (thread = row; two warps per TMEM lane
+//                              quadrant split the columns), scale / add C, convert, stage 128-byte-swizzled
+//                              slabs in one of two shared-memory buffers and hand them to TMA (store, or
+//                              reduce-add for fp32 accumulation and split-K); overlaps the next tile's main
+//                              loop.  TMA clips rows/columns outside the tensor.
 // Operands may be K-major ([rows, K] with K contiguous) or MN-major ([K, rows] with rows
 // contiguous); both are read straight from row-major tensors by TMA, so forward (X W^T), input
 // gradient (dY W) and weight gradient (dY^T X) all run without a transposed copy.
@@ -31,13 +32,13 @@
 
 namespace gm {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 6;
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 5;
 constexpr int BN_HALF = BN / 2;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN_HALF * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;           // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
 constexpr int GROUP_M = 4;               // in pair tiles (256 rows each)
 constexpr uint32_t TMEM_COLS = 512;
-constexpr int STAGING_BYTES = 2 * BM * 128;      // two slabs of [128 rows][128 bytes]
+constexpr int STAGING_BYTES = 2 * BM * 128;      // two slabs of [128 rows][128 bytes]; the staging area holds two such buffers
 
 struct TileCoord {
     int m0, n0;        // element offsets of the tile in the output
@@ -114,7 +115,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* staging = smem + STAGES * STAGE_BYTES;
-    uint64_t* full = reinterpret_cast<uint64_t*>(staging + STAGING_BYTES);
+    uint64_t* full = reinterpret_cast<uint64_t*>(staging + 2 * STAGING_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;
     uint64_t* acc_empty = acc_full + 2;
@@ -124,8 +125,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int cta_rank = static_cast<int>(cluster_ctarank());     // 0 = leader of the pair
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        // acc_empty of the leader collects the epilogue threads of both CTAs
-        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 256); }
+        // acc_empty of the leader collects the 256 epilogue threads of each of the two CTAs
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 512); }
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
@@ -200,17 +201,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
         }
     } else {
-        const int quad = warp & 3;                  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+        // Eight epilogue warps: TMEM lanes 32*quad .. 32*quad+31 are readable by warps with warp % 4 == quad, so two warps share
+        // a lane quadrant and split the columns of every round between them (half 0: first slab, half 1: second slab).
+        const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row_in_tile = quad * 32 + lane;
         const bool leader = threadIdx.x == 64;      // first epilogue thread issues the TMA stores
         const int elem = p.out_fp32 ? 4 : 2;
         const int chunks_per_round = p.out_fp32 ? 2 : 4;          // 32-column accumulator chunks staged per round
+        const int my_chunks = chunks_per_round / 2;               // per warp half
         const int rounds = (BN / 32) / chunks_per_round;
         const int cols_per_slab = 128 / elem;
         const bool reduce = p.accumulate || p.split_k > 1;
-        uint8_t* my_row = staging + row_in_tile * 128;
         const int sw = row_in_tile & 7;
         int acc = 0; uint32_t acc_ph = 0;
+        uint32_t stores = 0;                                       // committed store groups: selects the staging buffer
         for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
             const TileCoord t = tile_coord(p, tile, cta_rank, m_tiles, n_tiles);
             const bool have_acc = t.k_blocks != 0;
@@ -224,51 +229,65 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int round = 0; round < rounds; ++round) {
                 const int round_col0 = t.n0 + round * chunks_per_round * 32;
                 if (round_col0 >= t.n_limit) break;                           // uniform across the CTA
-                if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                asm volatile("bar.sync 1, 128;" ::: "memory");                 // staging buffer is free again
-                for (int cc = 0; cc < chunks_per_round; ++cc) {
-                    const int chunk = round * chunks_per_round + cc;
-                    const int col0 = t.n0 + chunk * 32;
-                    uint32_t r[32];
-                    if (have_acc) {
-                        tmem_ld_32x32b_x32(tmem_base + acc * BN + chunk * 32 + (static_cast<uint32_t>(quad * 32) << 16), r);
-                        tmem_ld_wait();
-                    } else {
+                uint8_t* buf = staging + (stores & 1) * STAGING_BYTES;
+                // the store that read this buffer two rounds ago must have finished reading it
+                if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                uint32_t r[2][32];
+                if (have_acc) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) r[j] = 0u;
+                    for (int j = 0; j < 2; ++j) {
+                        if (j < my_chunks) {
+                            const int chunk = round * chunks_per_round + half * my_chunks + j;
+                            tmem_ld_32x32b_x32(tmem_base + acc * BN + chunk * 32 + (static_cast<uint32_t>(quad * 32) << 16), r[j]);
+                        }
                     }
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[j][i] = 0u;
+                }
+                if (have_acc && round == rounds - 1) {                        // accumulator fully read: release it early
+                    tc_fence_before();
+                    mbar_arrive_cluster(&acc_empty[acc], 0);
+                }
+                uint8_t* slab_row = buf + half * (BM * 128) + row_in_tile * 128;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    if (j >= my_chunks) break;
+                    const int col0 = round_col0 + (half * my_chunks + j) * 32;
                     float v[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[j][i]) * p.alpha;
                     if (p.C != nullptr && row_ok && col0 < t.n_limit) {
                         const __nv_bfloat16* c = reinterpret_cast<const __nv_bfloat16*>(p.C) +
                             static_cast<long long>(t.dz) * p.c_batch_stride + static_cast<long long>(row) * p.ldc + col0;
                         if (col0 + 32 <= t.n_limit) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                const uint4 q = *reinterpret_cast<const uint4*>(c + j);
+                            for (int i = 0; i < 32; i += 8) {
+                                const uint4 q = *reinterpret_cast<const uint4*>(c + i);
                                 const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
                                     const float2 f = __bfloat1622float2(h[e]);
-                                    v[j + 2 * e] += p.beta * f.x;
-                                    v[j + 2 * e + 1] += p.beta * f.y;
+                                    v[i + 2 * e] += p.beta * f.x;
+                                    v[i + 2 * e + 1] += p.beta * f.y;
                                 }
                             }
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < t.n_limit) v[j] += p.beta * __bfloat162float(c[j]);
+                            for (int i = 0; i < 32; ++i)
+                                if (col0 + i < t.n_limit) v[i] += p.beta * __bfloat162float(c[i]);
                         }
                     }
                     // 16-byte pieces of this thread's row go to piece index (i ^ row%8) of the 128-byte slab row
                     if (p.out_fp32) {
-                        uint8_t* slab = my_row + cc * (BM * 128);
 #pragma unroll
                         for (int q = 0; q < 8; ++q)
-                            *reinterpret_cast<float4*>(slab + ((q ^ sw) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                            *reinterpret_cast<float4*>(slab_row + ((q ^ sw) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                     } else {
-                        uint8_t* slab = my_row + (cc >> 1) * (BM * 128);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             uint4 o;
@@ -276,21 +295,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                             o.y = pack_bf16x2(v[8 * q + 2], v[8 * q + 3]);
                             o.z = pack_bf16x2(v[8 * q + 4], v[8 * q + 5]);
                             o.w = pack_bf16x2(v[8 * q + 6], v[8 * q + 7]);
-                            *reinterpret_cast<uint4*>(slab + ((((cc & 1) * 4 + q) ^ sw) << 4)) = o;
+                            *reinterpret_cast<uint4*>(slab_row + (((j * 4 + q) ^ sw) << 4)) = o;
                         }
                     }
                 }
-                if (have_acc && round == rounds - 1) {                        // accumulator fully read: release it early
-                    tc_fence_before();
-                    mbar_arrive_cluster(&acc_empty[acc], 0);
-                }
                 fence_proxy_async();
-                asm volatile("bar.sync 1, 128;" ::: "memory");                 // slabs complete and visible to the async proxy
+                asm volatile("bar.sync 1, 256;" ::: "memory");                 // slabs complete and visible to the async proxy
                 if (leader) {
                     for (int sl = 0; sl < 2; ++sl) {
                         const int col = round_col0 + sl * cols_per_slab;
                         if (col >= t.n_limit || t.m0 >= t.m_limit) break;
-                        const uint32_t src = smem_u32(staging + sl * (BM * 128));
+                        const uint32_t src = smem_u32(buf + sl * (BM * 128));
                         if (reduce) {
                             asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4}], [%1];"
                                          ::"l"(&tmap_d), "r"(src), "r"(col), "r"(t.m0), "r"(t.dz) : "memory");
@@ -301,6 +316,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     }
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
+                ++stores;
             }
             if (have_acc) {
                 // tiles narrower than BN leave the round loop early: the accumulator is released here in that case
@@ -326,7 +342,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
 }
 
-constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 2 * STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 template <bool A_MN, bool B_MN>
 static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const GemmParams& p, int sms,

@@ -1,4 +1,5 @@
-"""Front end of the tcgen05 attention kernels (`csrc/attention`): causal, optionally sliding-window, head size 64."""
+"""Front end of the tcgen05 attention kernels (`csrc/attention`): causal, optionally sliding-window; value heads 64 wide,
+query / key heads 64 wide or 128 wide (multi-head latent attention: content + rotary parts)."""
 from __future__ import annotations
 
 from typing import Optional
@@ -9,8 +10,9 @@ from torch import Tensor
 
 def supported(q: Tensor, k: Tensor, v: Tensor, softcap_value: float) -> bool:
     b, t, h, d = q.shape
-    return (q.dtype == torch.bfloat16 and d == 64 and v.shape[-1] == 64 and t % 128 == 0 and softcap_value == 0.0
-            and h % k.shape[2] == 0 and all(x.stride(3) == 1 and x.stride(2) == 64 and x.stride(0) == t * x.stride(1) for x in (q, k, v)))
+    return (q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16 and d in (64, 128) and k.shape[-1] == d
+            and v.shape[-1] == 64 and t % 128 == 0 and softcap_value == 0.0 and h % k.shape[2] == 0
+            and all(x.stride(3) == 1 and x.stride(2) == x.shape[3] and x.stride(0) == t * x.stride(1) and x.stride(1) % 8 == 0 for x in (q, k, v)))
 
 
 class _AttentionFn(torch.autograd.Function):
@@ -29,7 +31,12 @@ class _AttentionFn(torch.autograd.Function):
         window, scale = ctx.cfg
         b, t, h, d = q.shape
         hk = k.shape[2]
-        d_out = d_out if (d_out.stride(3) == 1 and d_out.stride(2) == d and d_out.stride(0) == t * d_out.stride(1)) else d_out.contiguous()
+        d_out = d_out if (d_out.stride(3) == 1 and d_out.stride(2) == 64 and d_out.stride(0) == t * d_out.stride(1)) else d_out.contiguous()
+        if d != 64:                   # wide query / key heads: separate gradient tensors
+            dk = torch.empty((b, t, hk, d), dtype=q.dtype, device=q.device)
+            dv = torch.empty((b, t, hk, 64), dtype=q.dtype, device=q.device)
+            dq32 = ext().attn_bwd(q, k, v, out, d_out, lse, dk, dv, window, scale)
+            return dq32.to(q.dtype), dk, dv, None, None
         # one packed gradient buffer [B, T, (H + 2 Hkv) * 64]: dk and dv are written in place by the kernel, dq is converted into it
         packed = torch.empty((b, t, (h + 2 * hk) * d), dtype=q.dtype, device=q.device)
         dk = packed[..., h * d: (h + hk) * d].unflatten(-1, (hk, d))

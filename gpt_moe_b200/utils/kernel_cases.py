@@ -25,7 +25,7 @@ def _timed(fn, iters):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_mxfp8", "quantize", "gemm_wgrad", "grouped", "attn_fwd", "attn_bwd", "rs_muon", "ce", "rmsnorm"])
+    ap.add_argument("case", choices=["gemm", "gemm_mxfp8", "quantize", "gemm_wgrad", "grouped", "attn_fwd", "attn_bwd", "rs_muon", "ce", "rmsnorm", "rope", "rope_bwd", "ep_dispatch", "ep_combine", "rmsnorm_bwd"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     from gpt_moe_b200.ops import attention_tc, cuda_ops
@@ -89,6 +89,41 @@ def main() -> None:
         scale = torch.ones(1, device=dev)
         fn = lambda: c.ce_fwd_bwd(logits, targets, scale, -100, True)
         bytes_ = 4096 * 50304 * 2 * 3
+    elif args.case == "rmsnorm_bwd":            # backward of the fused residual + RMSNorm: fp32 residual stream, bf16 dy, residual gradient added
+        x = torch.randn(32768, 768, device=dev); dy = torch.randn(32768, 768, device=dev).bfloat16()
+        w = torch.ones(768, device=dev); rstd = torch.ones(32768, device=dev); res = torch.randn(32768, 768, device=dev)
+        fn = lambda: c.rmsnorm_bwd(dy, x, w, rstd, res)
+        bytes_ = 32768 * 768 * 14
+    elif args.case in ("rope", "rope_bwd"):     # packed QKV rows of 32768 tokens: 12 q + 12 k heads rotated and normalised, 12 v heads passed through
+        qkv = torch.randn(32768, 2304, device=dev).bfloat16()
+        out = torch.empty_like(qkv)
+        pos = torch.arange(2048, device=dev).float()[:, None] * (10000.0 ** (-torch.arange(32, device=dev).float() / 32))[None, :]
+        cos, sin = pos.cos().contiguous(), pos.sin().contiguous()
+        qs, ks = torch.ones(12, device=dev), torch.ones(12, device=dev)
+        if args.case == "rope":
+            fn = lambda: c.rope_qknorm_fwd(qkv, out, cos, sin, qs, ks, 2048, 12, 12, 64, 1e-6, True, -3e38, 5.0, 768)
+            bytes_ = 32768 * 2304 * 2 * 2
+        else:
+            dy = torch.randn_like(qkv)
+            fn = lambda: c.rope_qknorm_bwd(qkv, dy, dy, cos, sin, qs, ks, 2048, 12, 12, 64, 1e-6, True, -3e38, 5.0)
+            bytes_ = 32768 * 1536 * 2 * 3
+    elif args.case in ("ep_dispatch", "ep_combine"):   # group of one: every row takes the peer-memory path with a zero offset
+        tokens, d, experts = 32768, 768, 8
+        idx = torch.randint(0, experts, (tokens, 1), device=dev)
+        hidden = torch.randn(tokens, d, device=dev).bfloat16()
+        dest, _, local_ends, counts, _, _ = c.route(idx, experts)
+        table = torch.zeros(experts, dtype=torch.int32, device=dev)
+        c.ep_push_counts(counts, table, [0], 0)
+        cap = tokens + experts * 256
+        my_base, seg_ends, valid_ends, tiles, meta = c.ep_plan(table, 1, 0, experts, cap)
+        recv = torch.zeros(cap, d, device=dev, dtype=torch.bfloat16)
+        (route_row,) = c.ep_dispatch(hidden, idx, dest, local_ends, my_base, None, None, recv, [0], experts)
+        gates = torch.ones(tokens, 1, device=dev)
+        if args.case == "ep_dispatch":
+            fn = lambda: c.ep_dispatch(hidden, idx, dest, local_ends, my_base, None, None, recv, [0], experts)
+        else:
+            fn = lambda: c.ep_combine(recv, idx, route_row, gates, False, [0], experts)
+        bytes_ = tokens * d * 2 * 2
     else:
         x = torch.randn(32768, 768, device=dev)
         w = torch.ones(768, device=dev)

@@ -257,3 +257,25 @@ def test_attention_backward_kernel(ops, t, window, hq, hk):
             assert got[..., sl].abs().max().item() < 1e-4, name
         else:
             assert rel(got[..., sl], exp[..., sl]) < 2e-2, name
+
+
+@pytest.mark.parametrize("t,window,hq,hk", [(256, 1000, 2, 2), (512, 128, 4, 2), (1024, 2000, 2, 1)])
+def test_attention_kernels_wide_query_key_heads(ops, t, window, hq, hk):
+    """Multi-head latent attention shape: 128-wide query / key heads (content + rotary), 64-wide value heads."""
+    from gpt_moe_b200.ops import attention_tc
+    torch.manual_seed(11)
+    b, dqk, dv = 2, 128, 64
+    q = torch.randn(b, t, hq, dqk, device="cuda").mul_(0.5).bfloat16().requires_grad_()
+    k = torch.randn(b, t, hk, dqk, device="cuda").mul_(0.5).bfloat16().requires_grad_()
+    v = torch.randn(b, t, hk, dv, device="cuda").bfloat16().requires_grad_()
+    assert attention_tc.supported(q, k, v, 0.0)
+    out = attention_tc.attention(q, k, v, window=window, scale=None)
+    g = torch.randn_like(out)
+    out.backward(g)
+    rq, rk, rv = (x.detach().float().requires_grad_() for x in (q, k, v))
+    want = ref.attention(rq, rk, rv, causal=True, window=window)
+    want.backward(g.float())
+    assert out.shape == (b, t, hq, dv)
+    assert rel(out, want) < 1e-2
+    for name, got, exp in (("dq", q.grad, rq.grad), ("dk", k.grad, rk.grad), ("dv", v.grad, rv.grad)):
+        assert rel(got, exp) < 2e-2, name
