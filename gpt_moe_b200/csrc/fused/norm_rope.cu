@@ -92,19 +92,29 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const TX* __restrict__ 
     for (int row = blockIdx.x * NORM_WARPS + warp; row < rows; row += gridDim.x * NORM_WARPS) {
         const long long base = static_cast<long long>(row) * d;
         const float r = rstd[row];
-        float4 xh[MAX_CHUNKS], g[MAX_CHUNKS];
+        // one dependent memory phase per row: x, dy and the residual gradient are all requested before the row reduction
+        float4 xh[MAX_CHUNKS], e[MAX_CHUNKS];
+        uint2 dyraw[MAX_CHUNKS];
         float dot = 0.f;
 #pragma unroll
         for (int c = 0; c < MAX_CHUNKS; ++c) {
             if (c < chunks) {
                 const int col = (c * 32 + lane) * 4;
-                const float4 xv = load4<TX>(x + base + col);
-                const float4 dv = load4<__nv_bfloat16>(dy + base + col);
+                xh[c] = load4<TX>(x + base + col);
+                dyraw[c] = *reinterpret_cast<const uint2*>(dy + base + col);
+                if (dres) e[c] = load4<TX>(dres + base + col);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < MAX_CHUNKS; ++c) {
+            if (c < chunks) {
+                const int col = (c * 32 + lane) * 4;
+                const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dyraw[c].x));
+                const float2 d23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dyraw[c].y));
                 const float4 wv = w ? *reinterpret_cast<const float4*>(w + col) : make_float4(1.f, 1.f, 1.f, 1.f);
-                xh[c] = make_float4(xv.x * r, xv.y * r, xv.z * r, xv.w * r);
-                acc[c].x += dv.x * xh[c].x; acc[c].y += dv.y * xh[c].y; acc[c].z += dv.z * xh[c].z; acc[c].w += dv.w * xh[c].w;
-                g[c] = make_float4(dv.x * wv.x, dv.y * wv.y, dv.z * wv.z, dv.w * wv.w);
-                dot += g[c].x * xh[c].x + g[c].y * xh[c].y + g[c].z * xh[c].z + g[c].w * xh[c].w;
+                xh[c] = make_float4(xh[c].x * r, xh[c].y * r, xh[c].z * r, xh[c].w * r);
+                acc[c].x += d01.x * xh[c].x; acc[c].y += d01.y * xh[c].y; acc[c].z += d23.x * xh[c].z; acc[c].w += d23.y * xh[c].w;
+                dot += d01.x * wv.x * xh[c].x + d01.y * wv.y * xh[c].y + d23.x * wv.z * xh[c].z + d23.y * wv.w * xh[c].w;
             }
         }
         dot = warp_sum(dot) / d;
@@ -112,12 +122,12 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const TX* __restrict__ 
         for (int c = 0; c < MAX_CHUNKS; ++c) {
             if (c < chunks) {
                 const int col = (c * 32 + lane) * 4;
-                float4 o = make_float4(r * (g[c].x - xh[c].x * dot), r * (g[c].y - xh[c].y * dot),
-                                       r * (g[c].z - xh[c].z * dot), r * (g[c].w - xh[c].w * dot));
-                if (dres) {
-                    const float4 e = load4<TX>(dres + base + col);
-                    o.x += e.x; o.y += e.y; o.z += e.z; o.w += e.w;
-                }
+                const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dyraw[c].x));
+                const float2 d23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dyraw[c].y));
+                const float4 wv = w ? *reinterpret_cast<const float4*>(w + col) : make_float4(1.f, 1.f, 1.f, 1.f);
+                float4 o = make_float4(r * (d01.x * wv.x - xh[c].x * dot), r * (d01.y * wv.y - xh[c].y * dot),
+                                       r * (d23.x * wv.z - xh[c].z * dot), r * (d23.y * wv.w - xh[c].w * dot));
+                if (dres) { o.x += e[c].x; o.y += e[c].y; o.z += e[c].z; o.w += e[c].w; }
                 store4<TX>(dx + base + col, o);
             }
         }
@@ -260,10 +270,16 @@ void launch_column_sum(const float* partial, float* out, int rows, int cols, int
 // heads use k_scale.  pos = t % seq_len indexes the cos/sin tables [seq_len, D/2].
 // forward:  r = rope(x);  g = rsqrt(mean|sum(r^2) + eps);  y = r * g * clamp(scale[h])
 // backward: dr = g*s*(dy - r * g^2 * mean|sum(dy*r));  dx = rope^T(dr);  dscale[h] += sum(dy * r * g) inside the clamp range
-// One warp works on ROPE_GROUP heads of a token at a time so that several independent 128-byte rows are in flight per warp.
-// Forward also copies `copy_cols` trailing columns (the value heads of a packed QKV row) from x to out; backward may run
-// in place (out == dy): every element is read by the thread that later writes it.
-constexpr int ROPE_GROUP = 4;
+// A lane owns four rotation pairs (16 bytes) of one head, so a head of D elements takes D/8 lanes and a warp works on
+// 256/D heads of a token at once; statistics are reduced inside the head's lane group.  Forward also copies `copy_cols`
+// trailing columns (the value heads of a packed QKV row) from x to out; backward may run in place (out == dy): every
+// element is read by the lane that later writes it.
+template <int D>
+__device__ __forceinline__ float head_sum(float v) {
+#pragma unroll
+    for (int o = D / 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
 
 template <int D, bool BWD>
 __global__ void __launch_bounds__(256)
@@ -273,10 +289,12 @@ rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* dy,
                    int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin, float smax,
                    int copy_cols) {
     constexpr int PAIRS = D / 2;
-    constexpr int PER_LANE = (PAIRS + 31) / 32;
+    constexpr int LANES = D / 8;                 // lanes per head
+    constexpr int HEADS_PER_WARP = 32 / LANES;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane / LANES, li = lane % LANES;
     const int heads = q_heads + k_heads;
-    const int groups = (heads + ROPE_GROUP - 1) / ROPE_GROUP;
+    const int groups = (heads + HEADS_PER_WARP - 1) / HEADS_PER_WARP;
     const long long total = tokens * groups;
     const bool has_norm = q_scale != nullptr;
     __shared__ float ds_smem[8][64];
@@ -286,79 +304,61 @@ rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* dy,
     }
     for (long long idx = static_cast<long long>(blockIdx.x) * 8 + warp; idx < total; idx += static_cast<long long>(gridDim.x) * 8) {
         const long long t = idx / groups;
-        const int h0 = static_cast<int>(idx - t * groups) * ROPE_GROUP;
+        const int h = static_cast<int>(idx - t * groups) * HEADS_PER_WARP + sub;
+        const bool live = h < heads;
         const int pos = static_cast<int>(t % seq_len);
-        float r1[ROPE_GROUP][PER_LANE], r2[ROPE_GROUP][PER_LANE], g1[ROPE_GROUP][PER_LANE], g2[ROPE_GROUP][PER_LANE];
-        float c[PER_LANE], sn[PER_LANE], ss[ROPE_GROUP], dot[ROPE_GROUP];
-#pragma unroll
-        for (int i = 0; i < PER_LANE; ++i) {
-            const int pr = lane + 32 * i;
-            c[i] = 1.f; sn[i] = 0.f;
-            if (cos_t && pr < PAIRS) { c[i] = cos_t[pos * PAIRS + pr]; sn[i] = sin_t[pos * PAIRS + pr]; }
+        float c[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+        if (cos_t) {
+            const float4 cv = *reinterpret_cast<const float4*>(cos_t + pos * PAIRS + li * 4);
+            const float4 sv = *reinterpret_cast<const float4*>(sin_t + pos * PAIRS + li * 4);
+            c[0] = cv.x; c[1] = cv.y; c[2] = cv.z; c[3] = cv.w;
+            sn[0] = sv.x; sn[1] = sv.y; sn[2] = sv.z; sn[3] = sv.w;
         }
-        __nv_bfloat162 xv[ROPE_GROUP][PER_LANE], gv[ROPE_GROUP][PER_LANE];
-#pragma unroll
-        for (int u = 0; u < ROPE_GROUP; ++u) {
-#pragma unroll
-            for (int i = 0; i < PER_LANE; ++i) {
-                const int pr = lane + 32 * i;
-                xv[u][i] = __floats2bfloat162_rn(0.f, 0.f);
-                gv[u][i] = xv[u][i];
-                if (h0 + u < heads && pr < PAIRS) {
-                    xv[u][i] = *reinterpret_cast<const __nv_bfloat162*>(x + t * x_stride + (h0 + u) * D + 2 * pr);
-                    if (BWD) gv[u][i] = *reinterpret_cast<const __nv_bfloat162*>(dy + t * o_stride + (h0 + u) * D + 2 * pr);
-                }
-            }
+        uint4 xraw = make_uint4(0, 0, 0, 0), graw = make_uint4(0, 0, 0, 0);
+        if (live) {
+            xraw = *reinterpret_cast<const uint4*>(x + t * x_stride + h * D + li * 8);
+            if (BWD) graw = *reinterpret_cast<const uint4*>(dy + t * o_stride + h * D + li * 8);
         }
+        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xraw);
+        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&graw);
+        float r1[4], r2[4], g1[4], g2[4];
+        float ss = 0.f, dot = 0.f;
 #pragma unroll
-        for (int u = 0; u < ROPE_GROUP; ++u) {
-            ss[u] = dot[u] = 0.f;
-#pragma unroll
-            for (int i = 0; i < PER_LANE; ++i) {
-                const float2 xf = __bfloat1622float2(xv[u][i]);
-                r1[u][i] = xf.x * c[i] - xf.y * sn[i];
-                r2[u][i] = xf.x * sn[i] + xf.y * c[i];
-                ss[u] += r1[u][i] * r1[u][i] + r2[u][i] * r2[u][i];
-                if (BWD) {
-                    const float2 gf = __bfloat1622float2(gv[u][i]);
-                    g1[u][i] = gf.x; g2[u][i] = gf.y;
-                    dot[u] += g1[u][i] * r1[u][i] + g2[u][i] * r2[u][i];
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < ROPE_GROUP; ++u) {
-            const int h = h0 + u;
-            if (h >= heads) break;                                                     // uniform across the warp
-            const float raw = h < q_heads ? (q_scale ? q_scale[h] : 1.f) : (k_scale ? k_scale[h - q_heads] : 1.f);
-            const float sc = fminf(fmaxf(raw, smin), smax);
-            float gain = 1.f, mult = 1.f;
-            if (has_norm) {
-                const float total_ss = warp_sum(ss[u]);
-                gain = rsqrtf((rms ? total_ss / D : total_ss) + eps);
-                mult = gain * sc;
-            }
+        for (int i = 0; i < 4; ++i) {
+            const float2 xf = __bfloat1622float2(xp[i]);
+            r1[i] = xf.x * c[i] - xf.y * sn[i];
+            r2[i] = xf.x * sn[i] + xf.y * c[i];
+            ss += r1[i] * r1[i] + r2[i] * r2[i];
             if (BWD) {
-                const float d = warp_sum(dot[u]);
-                if (has_norm && lane == 0 && raw >= smin && raw <= smax) ds_smem[warp][h] += d * gain;
-                const float coef = has_norm ? gain * gain * (rms ? d / D : d) : 0.f;
-#pragma unroll
-                for (int i = 0; i < PER_LANE; ++i) {
-                    const int pr = lane + 32 * i;
-                    if (pr < PAIRS) {
-                        const float d1 = mult * (g1[u][i] - r1[u][i] * coef), d2 = mult * (g2[u][i] - r2[u][i] * coef);
-                        const float o1 = d1 * c[i] + d2 * sn[i], o2 = -d1 * sn[i] + d2 * c[i];
-                        *reinterpret_cast<__nv_bfloat162*>(out + t * x_stride + h * D + 2 * pr) = __floats2bfloat162_rn(o1, o2);
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < PER_LANE; ++i) {
-                    const int pr = lane + 32 * i;
-                    if (pr < PAIRS)
-                        *reinterpret_cast<__nv_bfloat162*>(out + t * o_stride + h * D + 2 * pr) = __floats2bfloat162_rn(r1[u][i] * mult, r2[u][i] * mult);
-                }
+                const float2 gf = __bfloat1622float2(gp[i]);
+                g1[i] = gf.x; g2[i] = gf.y;
+                dot += g1[i] * r1[i] + g2[i] * r2[i];
             }
+        }
+        const float raw = !live ? 1.f : h < q_heads ? (q_scale ? q_scale[h] : 1.f) : (k_scale ? k_scale[h - q_heads] : 1.f);
+        const float sc = fminf(fmaxf(raw, smin), smax);
+        float gain = 1.f, mult = 1.f;
+        if (has_norm) {
+            ss = head_sum<D>(ss);
+            gain = rsqrtf((rms ? ss / D : ss) + eps);
+            mult = gain * sc;
+        }
+        uint4 oraw;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&oraw);
+        if (BWD) {
+            dot = head_sum<D>(dot);
+            if (has_norm && live && li == 0 && raw >= smin && raw <= smax) ds_smem[warp][h] += dot * gain;
+            const float coef = has_norm ? gain * gain * (rms ? dot / D : dot) : 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float d1 = mult * (g1[i] - r1[i] * coef), d2 = mult * (g2[i] - r2[i] * coef);
+                op[i] = __floats2bfloat162_rn(d1 * c[i] + d2 * sn[i], -d1 * sn[i] + d2 * c[i]);
+            }
+            if (live) *reinterpret_cast<uint4*>(out + t * x_stride + h * D + li * 8) = oraw;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) op[i] = __floats2bfloat162_rn(r1[i] * mult, r2[i] * mult);
+            if (live) *reinterpret_cast<uint4*>(out + t * o_stride + h * D + li * 8) = oraw;
         }
     }
     if (!BWD && copy_cols > 0) {
@@ -382,7 +382,7 @@ rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* dy,
 }
 
 int rope_blocks(long long tokens, int heads) {
-    const long long want = (tokens * ((heads + ROPE_GROUP - 1) / ROPE_GROUP) + 7) / 8;
+    const long long want = (tokens * ((heads + 3) / 4) + 7) / 8;      // at least 4 heads of a token per warp pass for every supported head size
     return static_cast<int>(want < 2368 ? want : 2368);
 }
 
