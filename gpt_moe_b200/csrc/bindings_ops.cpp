@@ -179,7 +179,7 @@ Tensor activation_fwd(const Tensor& pre, const std::string& name, const OptTenso
     const int kind = act_kind(name);
     const int in_w = pre.size(-1), h = kind == 4 ? in_w / 2 : in_w;
     const int rows = pre.numel() / in_w;
-    GM_CHECK(h % 2 == 0, "activation width must be even");
+    GM_CHECK(h % 8 == 0 && pre.is_contiguous(), "activation width must be a multiple of 8 (16-byte vectors) and rows contiguous");
     auto sizes = pre.sizes().vec();
     sizes.back() = h;
     Tensor act = torch::empty(sizes, pre.options());
@@ -193,6 +193,7 @@ Tensor activation_bwd(const Tensor& dact, const Tensor& pre, const std::string& 
     const int kind = act_kind(name);
     const int in_w = pre.size(-1), h = kind == 4 ? in_w / 2 : in_w;
     const int rows = pre.numel() / in_w;
+    GM_CHECK(h % 8 == 0 && pre.is_contiguous() && dact.is_contiguous(), "activation width must be a multiple of 8 (16-byte vectors) and rows contiguous");
     Tensor dpre = torch::empty_like(pre);
     launch_activation_bwd(dact.data_ptr(), pre.data_ptr(), dpre.data_ptr(), meta.has_value() ? meta->data_ptr<int>() : nullptr, rows, h, kind, stream());
     return dpre;

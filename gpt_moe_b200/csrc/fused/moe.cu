@@ -224,62 +224,93 @@ __device__ __forceinline__ float act_grad(int kind, float x) {
     }
 }
 
-// rows limited by meta[1] when meta != nullptr (padded expert rows), else by `rows`
+// rows limited by meta[1] when meta != nullptr (padded expert rows), else by `rows`.  A thread handles 8 consecutive
+// elements (16-byte loads and stores); SWIGLU is a template parameter so the common case carries no per-element switch.
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+    uint4 o;
+    o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]); o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+    return o;
+}
+
+template <bool SWIGLU>
 __global__ void __launch_bounds__(256)
 activation_fwd_kernel(const __nv_bfloat16* __restrict__ pre, __nv_bfloat16* __restrict__ act, const int* __restrict__ meta,
                       int rows, int h, int kind) {
     const int total = meta ? min(meta[1], rows) : rows;
-    const int per_row = h / 2;
+    const int per_row = h / 8;
     const long long n = static_cast<long long>(total) * per_row;
-    const int in_w = kind == 4 ? 2 * h : h;
+    const int in_w = SWIGLU ? 2 * h : h;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const long long r = i / per_row;
-        const int c = static_cast<int>(i - r * per_row) * 2;
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pre + r * in_w + c));
-        float2 o;
-        if (kind == 4) {
-            const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pre + r * in_w + h + c));
-            o.x = act_fwd(3, a.x) * u.x;
-            o.y = act_fwd(3, a.y) * u.y;
+        const int c = static_cast<int>(i - r * per_row) * 8;
+        float a[8], o[8];
+        unpack8(*reinterpret_cast<const uint4*>(pre + r * in_w + c), a);
+        if (SWIGLU) {
+            float u[8];
+            unpack8(*reinterpret_cast<const uint4*>(pre + r * in_w + h + c), u);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = a[j] / (1.f + __expf(-a[j])) * u[j];
         } else {
-            o.x = act_fwd(kind, a.x);
-            o.y = act_fwd(kind, a.y);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = act_fwd(kind, a[j]);
         }
-        *reinterpret_cast<__nv_bfloat162*>(act + r * h + c) = __floats2bfloat162_rn(o.x, o.y);
+        *reinterpret_cast<uint4*>(act + r * h + c) = pack8(o);
     }
 }
 
+template <bool SWIGLU>
 __global__ void __launch_bounds__(256)
 activation_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ pre, __nv_bfloat16* __restrict__ dpre,
                       const int* __restrict__ meta, int rows, int h, int kind) {
     const int total = meta ? min(meta[1], rows) : rows;
-    const int per_row = h / 2;
+    const int per_row = h / 8;
     const long long n = static_cast<long long>(total) * per_row;
-    const int in_w = kind == 4 ? 2 * h : h;
+    const int in_w = SWIGLU ? 2 * h : h;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const long long r = i / per_row;
-        const int c = static_cast<int>(i - r * per_row) * 2;
-        const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dact + r * h + c));
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pre + r * in_w + c));
-        if (kind == 4) {
-            const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pre + r * in_w + h + c));
-            *reinterpret_cast<__nv_bfloat162*>(dpre + r * in_w + c) =
-                __floats2bfloat162_rn(g.x * u.x * act_grad(3, a.x), g.y * u.y * act_grad(3, a.y));
-            *reinterpret_cast<__nv_bfloat162*>(dpre + r * in_w + h + c) =
-                __floats2bfloat162_rn(g.x * act_fwd(3, a.x), g.y * act_fwd(3, a.y));
+        const int c = static_cast<int>(i - r * per_row) * 8;
+        float g[8], a[8], d0[8];
+        unpack8(*reinterpret_cast<const uint4*>(dact + r * h + c), g);
+        unpack8(*reinterpret_cast<const uint4*>(pre + r * in_w + c), a);
+        if (SWIGLU) {
+            float u[8], d1[8];
+            unpack8(*reinterpret_cast<const uint4*>(pre + r * in_w + h + c), u);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float sg = 1.f / (1.f + __expf(-a[j]));
+                d0[j] = g[j] * u[j] * sg * (1.f + a[j] * (1.f - sg));      // d/d(gate): up * silu'(gate)
+                d1[j] = g[j] * a[j] * sg;                                    // d/d(up):   silu(gate)
+            }
+            *reinterpret_cast<uint4*>(dpre + r * in_w + h + c) = pack8(d1);
         } else {
-            *reinterpret_cast<__nv_bfloat162*>(dpre + r * in_w + c) =
-                __floats2bfloat162_rn(g.x * act_grad(kind, a.x), g.y * act_grad(kind, a.y));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) d0[j] = g[j] * act_grad(kind, a[j]);
         }
+        *reinterpret_cast<uint4*>(dpre + r * in_w + c) = pack8(d0);
     }
 }
 
 void launch_activation_fwd(const void* pre, void* act, const int* meta, int rows, int h, int kind, cudaStream_t s) {
-    activation_fwd_kernel<<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(act), meta, rows, h, kind);
+    if (kind == 4)
+        activation_fwd_kernel<true><<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(act), meta, rows, h, kind);
+    else
+        activation_fwd_kernel<false><<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(act), meta, rows, h, kind);
 }
 void launch_activation_bwd(const void* dact, const void* pre, void* dpre, const int* meta, int rows, int h, int kind, cudaStream_t s) {
-    activation_bwd_kernel<<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dact), static_cast<const __nv_bfloat16*>(pre),
-                                               static_cast<__nv_bfloat16*>(dpre), meta, rows, h, kind);
+    if (kind == 4)
+        activation_bwd_kernel<true><<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dact), static_cast<const __nv_bfloat16*>(pre),
+                                                         static_cast<__nv_bfloat16*>(dpre), meta, rows, h, kind);
+    else
+        activation_bwd_kernel<false><<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dact), static_cast<const __nv_bfloat16*>(pre),
+                                                          static_cast<__nv_bfloat16*>(dpre), meta, rows, h, kind);
 }
 
 }  // namespace gm
