@@ -302,6 +302,20 @@ void cast_bf16(const Tensor& src, Tensor& dst) {
 
 }  // namespace
 
+// Publish `value` into flags[index] of every rank / wait until flags[first .. first + world) of this rank have all reached `value`.
+void flag_signal(Tensor& flags, const std::vector<int64_t>& deltas, int64_t index, int64_t value) {
+    c10::cuda::CUDAGuard guard(flags.device());
+    GM_CHECK(flags.scalar_type() == torch::kInt32 && index >= 0 && index < flags.numel(), "flag_signal: int32 flag table, index in range");
+    auto d = to_deltas(deltas);
+    GM_CHECK(launch_flag_signal(flags.data_ptr<int>(), d.data(), d.size(), index, value, stream()), "flag_signal: at most 16 ranks");
+}
+
+void flag_wait(const Tensor& flags, int64_t first, int64_t world, int64_t value) {
+    c10::cuda::CUDAGuard guard(flags.device());
+    GM_CHECK(flags.scalar_type() == torch::kInt32 && first >= 0 && first + world <= flags.numel(), "flag_wait: int32 flag table, range inside it");
+    GM_CHECK(launch_flag_wait(flags.data_ptr<int>(), first, world, value, status_word(flags.device().index()), stream()), "flag_wait: at most 16 ranks");
+}
+
 // ---- expert-parallel dispatch / combine over peer memory ---------------------------------------------------------------
 // `table` is this rank's [world, experts] int32 count table inside a symmetric buffer; deltas[r] = rank r's base - this rank's base.
 void ep_push_counts(const Tensor& counts, Tensor& table, const std::vector<int64_t>& deltas, int64_t me) {
@@ -402,6 +416,8 @@ void register_kernels(pybind11::module_& m) {
     m.def("rs_muon_prepare", &rs_muon_prepare);
     m.def("muon_apply_push", &muon_apply_push);
     m.def("adamw_sharded", &adamw_sharded);
+    m.def("flag_signal", &flag_signal);
+    m.def("flag_wait", &flag_wait);
     m.def("ep_push_counts", &ep_push_counts);
     m.def("ep_plan", &ep_plan);
     m.def("ep_zero_pads", &ep_zero_pads);

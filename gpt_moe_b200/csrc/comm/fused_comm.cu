@@ -211,4 +211,43 @@ bool launch_adamw_sharded(float* params, const float* grads, void* m, void* v, b
     return true;
 }
 
+// ---- cross-rank readiness flags --------------------------------------------------------------------------------------------
+// flags[slot * world + src] on every rank holds the last step for which rank `src` has finished producing the data of `slot`
+// (the gradients of one transformer block).  flag_signal publishes this rank's value to every rank after a system-scope
+// fence; flag_wait polls this rank's own copy until every source has reached `value`.  The poll is bounded: when the
+// budget runs out the kernel records code 601 in the status word and returns, so a missing peer fails the step instead
+// of hanging the GPU.  The two kernels run on different GPUs (or at least never wait for one another on one GPU).
+__global__ void flag_signal_kernel(int* flags, PeerDeltas peers, int world, int index, int value) {
+    const int r = threadIdx.x;
+    if (r < world) {
+        __threadfence_system();
+        *reinterpret_cast<volatile int*>(reinterpret_cast<char*>(flags + index) + peers.d[r]) = value;
+    }
+}
+
+__global__ void flag_wait_kernel(const int* flags, int first, int world, int value, int* status) {
+    const int r = threadIdx.x;
+    if (r < world) {
+        const volatile int* f = flags + first + r;
+        const long long start = clock64();
+        while (*f < value) {
+            if (clock64() - start > kWaitBudgetCycles) { atomicExch(status, 601); break; }
+            __nanosleep(256);
+        }
+    }
+    __threadfence_system();
+}
+
+bool launch_flag_signal(int* flags, const long long* deltas, int world, int index, int value, cudaStream_t s) {
+    if (world > MAX_RANKS) return false;
+    flag_signal_kernel<<<1, 32, 0, s>>>(flags, make_deltas(deltas, world), world, index, value);
+    return true;
+}
+
+bool launch_flag_wait(const int* flags, int first, int world, int value, int* status, cudaStream_t s) {
+    if (world > MAX_RANKS) return false;
+    flag_wait_kernel<<<1, 32, 0, s>>>(flags, first, world, value, status);
+    return true;
+}
+
 }  // namespace gm

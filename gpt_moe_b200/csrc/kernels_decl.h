@@ -58,6 +58,9 @@ bool launch_adamw_sharded(float* params, const float* grads, void* m, void* v, b
                           long long n, float lr, float beta1, float beta2, float eps, float bc1, float bc2_sqrt,
                           const long long* grad_deltas, const long long* param_deltas, int world, cudaStream_t s);
 
+bool launch_flag_signal(int* flags, const long long* deltas, int world, int index, int value, cudaStream_t s);
+bool launch_flag_wait(const int* flags, int first, int world, int value, int* status, cudaStream_t s);
+
 // ---- expert-parallel dispatch / combine over peer memory (comm/ep_comm.cu) -------------------------------------------
 bool launch_ep_push_counts(const int* counts, int* table, const long long* deltas, int world, int me, int experts, cudaStream_t s);
 bool launch_ep_plan(const int* table, int* my_base, int* seg_ends, int* valid_ends, int* tile_expert, int* meta, int world, int me,

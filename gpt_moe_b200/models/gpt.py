@@ -245,7 +245,11 @@ class GPT(nn.Module):
         if chain:
             # residual update + following RMSNorm as one op per link (see Block.forward_prenormed)
             h = apply_norm(blocks[0].ln_1, x)
+            hook = getattr(self, "block_grad_hook", None) if grad_mode else None
             for i, block in enumerate(blocks):
+                if hook is not None and h.requires_grad:
+                    # the gradient of a block's normalised input is the last thing its backward produces
+                    h.register_hook(lambda grad, layer=i, fn=hook: fn(layer))
                 next_norm = blocks[i + 1].ln_1 if i + 1 < len(blocks) else self.transformer.ln_f
                 x, h, block_balance = block.forward_prenormed(x, h, ctx, next_norm)
                 if block_balance is not None:

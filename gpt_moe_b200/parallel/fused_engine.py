@@ -150,6 +150,22 @@ class FusedEngine:
         self.adamw_v = torch.zeros(per, dtype=moment_dtype, device=self.device)
         self.adamw_step = 0
         self._import_optimizer_state()
+
+        # ---- overlap of the Muon reduce / update / push with the backward pass ---------------------------------------------
+        # When the backward of a transformer block has been issued, this rank publishes a flag for that block; on a second
+        # stream the owner of a matrix waits (bounded) for the block's flags of all ranks and then runs reduce + momentum +
+        # Polar Express + push for its matrices of that block while the main stream continues with the earlier blocks.
+        self.overlap = bool(self.world > 1 and getattr(training_config, "overlap_grad_reduce", False))
+        self.layer_items: Dict[int, List[Tuple[str, nn.Parameter]]] = {}
+        for n, p in self.owned_shared:
+            parts = n.split(".")
+            layer = int(parts[2]) if len(parts) > 2 and parts[1] == "h" and parts[2].isdigit() else -1
+            self.layer_items.setdefault(layer, []).append((n, p))
+        n_slots = max([layer for layer in self.layer_items] + [0]) + 2
+        self.flags = SymmetricBuffer(n_slots * max(self.world, 1), torch.int32, self.device, dp_group) if self.overlap else None
+        self.comm_stream = torch.cuda.Stream(device=self.device) if self.overlap else None
+        self.step_counter = 0
+        self._early_layers: set = set()
         self._barrier()
 
     # ---- layout helpers ---------------------------------------------------------------------------------------------------
@@ -220,9 +236,36 @@ class FusedEngine:
     def forward_backward(self, model, x, y, document_ids, loss_scale: float, last_micro_step: bool):
         from ..ops import cuda_ops
         cuda_ops.set_loss_scale(loss_scale)
-        loss, token_loss, balance = model(x, y, document_ids=document_ids)
-        (loss * loss_scale).backward()
+        early = self.overlap and last_micro_step and self.optimizers.get("muon") is not None
+        if early:
+            self.step_counter += 1
+            self._early_layers = set()
+        self.model.block_grad_hook = self._on_block_backward if early else None
+        try:
+            loss, token_loss, balance = model(x, y, document_ids=document_ids)
+            (loss * loss_scale).backward()
+        finally:
+            self.model.block_grad_hook = None
         return loss, token_loss, balance
+
+    def _on_block_backward(self, layer: int) -> None:
+        """Called from the backward pass once every gradient of block `layer` has been issued on the current stream."""
+        from ..ops import cuda_ops
+        c = cuda_ops.ext()
+        if layer in self._early_layers:
+            return
+        self._early_layers.add(layer)
+        c.flag_signal(self.flags.tensor, self.flags.deltas, layer * self.world + self.rank, self.step_counter)
+        items = self.layer_items.get(layer)
+        if not items:
+            return
+        ready = torch.cuda.Event()
+        ready.record()
+        g = self.optimizers["muon"].param_groups[0]
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ready)
+            c.flag_wait(self.flags.tensor, layer * self.world, self.world, self.step_counter)
+            self._muon_update(items, self.grad_muon.deltas, self.compute.deltas, g["lr"], g["momentum"], g["nesterov"])
 
     def _muon_buckets(self, items: List[Tuple[str, nn.Parameter]]):
         buckets: Dict[Tuple[int, int], List[nn.Parameter]] = {}
@@ -297,7 +340,13 @@ class FusedEngine:
                         p = self.small[i][1]
                         p.data.add_(oi.to(p.dtype), alpha=-lr * max(shape) ** 0.5)
                         p.compute.copy_(p.data)
-            self._muon_update(self.owned_shared, self.grad_muon.deltas, self.compute.deltas, lr, momentum, nesterov)
+            remaining = self.owned_shared
+            if self._early_layers:
+                # blocks whose update already ran beside the backward pass: join that stream, then do what is left
+                torch.cuda.current_stream().wait_stream(self.comm_stream)
+                remaining = [(n, p) for layer, items in self.layer_items.items() if layer not in self._early_layers for n, p in items]
+                self._early_layers = set()
+            self._muon_update(remaining, self.grad_muon.deltas, self.compute.deltas, lr, momentum, nesterov)
             self._muon_update(self.owned_local, [0], [0], lr, momentum, nesterov)
         g0 = adamw.param_groups[0]
         self.adamw_step += 1

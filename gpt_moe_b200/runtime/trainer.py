@@ -255,6 +255,19 @@ class Trainer:
             self.next_batch_update_tokens = get_next_update_tokens(cfg.batch_size_schedule_keys, self.batch_schedule_idx, cfg.max_tokens)
         bs = self.current_batch_size
 
+        # token-based learning rate: it depends only on the tokens processed before this step, so it is set before the backward
+        # pass (the fused engine starts optimizer work for a block as soon as that block's gradients exist)
+        if self.train_tokens_processed >= self.next_lr_update_tokens and self.lr_schedule_idx + 1 < len(cfg.lr_schedule):
+            self.lr_schedule_idx += 1
+            self.next_lr_update_tokens = cfg.lr_schedule[self.lr_schedule_idx]["end"]
+        spec = cfg.lr_schedule[self.lr_schedule_idx]
+        adamw_lr = spec["fn"](self.train_tokens_processed - spec["start"], **spec["kwargs"])
+        for group in self.optimizers["adamw"].param_groups:
+            group["lr"] = adamw_lr
+        if "muon" in self.optimizers:
+            for group in self.optimizers["muon"].param_groups:
+                group["lr"] = adamw_lr * raw.muon_lr_scale
+
         if self.parallel_mode == "pp":
             pipeline_batches = [self.pipeline_runtime.next_batch(self.train_data_loader, bs, cfg.seq_len_train) for _ in range(accum)]
             with self.ctx:
@@ -272,22 +285,12 @@ class Trainer:
                 train_losses += torch.stack((loss.detach().float(), token_loss.detach().float(), balance.detach().float())) / accum
             du.all_reduce(train_losses, op="avg")
 
-        # token-based schedules
-        if self.train_tokens_processed >= self.next_lr_update_tokens and self.lr_schedule_idx + 1 < len(cfg.lr_schedule):
-            self.lr_schedule_idx += 1
-            self.next_lr_update_tokens = cfg.lr_schedule[self.lr_schedule_idx]["end"]
-        spec = cfg.lr_schedule[self.lr_schedule_idx]
-        adamw_lr = spec["fn"](self.train_tokens_processed - spec["start"], **spec["kwargs"])
+        # token-based window schedule
         if self.train_tokens_processed >= self.next_swa_update_tokens and self.swa_schedule_idx + 1 < len(cfg.swa_schedule_keys):
             self.swa_schedule_idx += 1
             self.current_window_size = cfg.swa_schedule_values[self.swa_schedule_idx]
             self.next_swa_update_tokens = get_next_update_tokens(cfg.swa_schedule_keys, self.swa_schedule_idx, cfg.max_tokens)
         raw.set_sliding_window(self.current_window_size)
-        for group in self.optimizers["adamw"].param_groups:
-            group["lr"] = adamw_lr
-        if "muon" in self.optimizers:
-            for group in self.optimizers["muon"].param_groups:
-                group["lr"] = adamw_lr * raw.muon_lr_scale
         raw.clear_fp8_weights()
         self.engine.step()
 

@@ -23,6 +23,7 @@ def run(fused: bool, steps: int = 4, ep: int = 1):
     tc.swa_values_schedule = {"fn": custom_schedule, "kwargs": {"values": [128]}}
     tc.kernel_warmup_train_steps = 0
     tc.use_fused_collectives = fused
+    tc.overlap_grad_reduce = fused           # exercise the per-block flags and the second stream as well
     tc.expert_parallel_size = ep
     trainer = Trainer(gc, tc, device_type="cuda", quiet=True)
     want = "FusedEngine" if fused else "CudaHostEngine"
