@@ -39,6 +39,8 @@ int64_t read_status() {
     return status_tensor(device).item<int32_t>();
 }
 void reset_status() { status_tensor(at::cuda::current_device()).zero_(); }
+// the device word itself, for an asynchronous copy to pinned host memory
+torch::Tensor status_word_tensor() { return status_tensor(at::cuda::current_device()); }
 
 // ---- tensor map cache -----------------------------------------------------------------------------
 struct MapKey {
@@ -296,6 +298,7 @@ int* status_word(int device) { return status_tensor(device).data_ptr<int>(); }
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("read_status", &read_status, "status word of the current device (0 = no bounded wait gave up)");
     m.def("reset_status", &reset_status);
+    m.def("status_word_tensor", &status_word_tensor);
     m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("a_mn") = false, py::arg("b_mn") = false,
           py::arg("alpha") = 1.0, py::arg("beta") = 0.0, py::arg("c") = py::none(), py::arg("accumulate") = false,
           py::arg("mode") = 0, py::arg("tile_expert") = py::none(), py::arg("num_m_tiles") = py::none(),

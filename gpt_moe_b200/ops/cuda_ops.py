@@ -68,6 +68,31 @@ def check_status() -> None:
         raise RuntimeError(f"a device-side bounded wait gave up (status {code}); the step is invalid")
 
 
+_status_host: dict = {}
+
+
+def check_status_deferred() -> None:
+    """`check_status` without a host synchronisation per call: the status word is copied to pinned host memory
+    behind the work issued so far, and the copy made by the PREVIOUS call is examined (it has long completed in a
+    training loop).  A step whose kernels gave up is therefore reported one call late; `check_status()` is the
+    immediate form."""
+    device = torch.cuda.current_device()
+    slot = _status_host.get(device)
+    if slot is None:
+        slot = _status_host[device] = {"host": torch.zeros(1, dtype=torch.int32).pin_memory(), "event": None}
+    if slot["event"] is not None:
+        slot["event"].synchronize()
+        code = int(slot["host"][0])
+        if code != 0:
+            slot["event"] = None
+            ext().reset_status()
+            raise RuntimeError(f"a device-side bounded wait gave up (status {code}); the step before this one is invalid")
+    slot["host"].copy_(ext().status_word_tensor(), non_blocking=True)
+    event = torch.cuda.Event()
+    event.record()
+    slot["event"] = event
+
+
 # ---- compute copies of weights ---------------------------------------------------------------------------
 _params_epoch = 0
 _weight_cache: dict = {}

@@ -49,7 +49,7 @@ class CudaHostEngine(HostEngine):
         from ..ops import cuda_ops
         super().step()
         cuda_ops.mark_parameters_updated()
-        cuda_ops.check_status()
+        cuda_ops.check_status_deferred()                  # no host synchronisation per step; a failed step is reported at the next one
 
 
 class SymmetricBuffer:
@@ -62,19 +62,29 @@ class SymmetricBuffer:
         self.handle = None
         if self.world == 1:
             self.tensor = torch.zeros(numel, dtype=dtype, device=device)
-            self.deltas = [0]
+            self._deltas = [0]
             return
         import torch.distributed._symmetric_memory as symm
         self.tensor = symm.empty(numel, dtype=dtype, device=device)
         self.tensor.zero_()
         self.handle = symm.rendezvous(self.tensor, group=group if group is not None else dist.group.WORLD)
         base = int(self.handle.buffer_ptrs[self.rank])
-        self.deltas = [int(ptr) - base for ptr in self.handle.buffer_ptrs]
+        self._deltas = [int(ptr) - base for ptr in self.handle.buffer_ptrs]
 
     def barrier(self) -> None:
         """All ranks' earlier work on the current streams is complete and visible before any rank continues."""
-        if self.handle is not None:
+        if self.handle is not None and not self.dry_run:
             self.handle.barrier(channel=0)
+
+    # Timing aid: with `dry_run` every "peer" offset points at this rank's own buffer and barriers are skipped, so a step
+    # does the same arithmetic and moves the same bytes through local HBM instead of NVLink.  The difference between a
+    # normal and a dry step is the communication time that is exposed (not hidden behind compute).  Results are wrong by
+    # construction (each rank sees only its own gradients); use it for measurement only.
+    dry_run = False
+
+    @property
+    def deltas(self) -> List[int]:
+        return [0] * len(self._deltas) if self.dry_run else self._deltas
 
 
 def _aligned(n: int, multiple: int = 64) -> int:
@@ -190,6 +200,11 @@ class FusedEngine:
 
     def _barrier(self) -> None:
         self.grad_muon.barrier()
+
+    def set_comm_dry_run(self, enabled: bool) -> None:
+        """Measurement mode: peer offsets collapse onto this rank and barriers are skipped (see `SymmetricBuffer.dry_run`)."""
+        for buf in (self.grad_muon, self.compute, self.adamw_param, self.adamw_grad):
+            buf.dry_run = enabled
 
     def refresh_from_parameters(self) -> None:
         """Rebuild the bf16 GEMM copies from the fp32 masters (after construction, a checkpoint load or a restore)."""
@@ -316,7 +331,7 @@ class FusedEngine:
             if self.small:
                 lo, hi = self.small_range
                 local = self.grad_muon.tensor[lo:hi]
-                if self.world > 1:
+                if self.world > 1 and not self.grad_muon.dry_run:
                     total = torch.zeros_like(local)
                     for r in range(self.world):
                         total += self.grad_muon.handle.get_buffer(r, (hi - lo,), torch.float32, lo)
@@ -355,7 +370,7 @@ class FusedEngine:
                         self.adamw_grad.deltas, self.adamw_param.deltas)
         self._barrier()                                   # every rank's pushes have landed
         cuda_ops.mark_parameters_updated()
-        cuda_ops.check_status()
+        cuda_ops.check_status_deferred()                  # no host synchronisation per step; a failed step is reported at the next one
 
     # ---- checkpoint helpers -------------------------------------------------------------------------------------------------------
     def sync_masters(self) -> None:

@@ -236,6 +236,13 @@ class Trainer:
         return t.to(self.device, non_blocking=True)
 
     # ------------------------------------------------------------------------------------------------
+    def _nvtx(self, name: str):
+        """NVTX range for profilers (`training.nvtx_ranges=True`); a no-op context otherwise."""
+        import contextlib
+        if self.device_type == "cuda" and getattr(self.cfg, "nvtx_ranges", False):
+            return torch.cuda.nvtx.range(name)
+        return contextlib.nullcontext()
+
     def train_step(self, batches: Optional[List[Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]]] = None,
                    read_losses: bool = True) -> Dict[str, float]:
         """One optimizer step.  `batches` (CPU tensors, one per micro-step) overrides the loader."""
@@ -280,7 +287,7 @@ class Trainer:
                 x, y = self._to_device(x[:bs]), self._to_device(y[:bs])
                 docs = self._to_device(docs[:bs]) if docs is not None else None
                 last = mini_step == accum - 1
-                with self.ctx:
+                with self.ctx, self._nvtx(f"forward_backward[{mini_step}]"):
                     loss, token_loss, balance = self.engine.forward_backward(model, x, y, docs, 1.0 / accum, last)
                 train_losses += torch.stack((loss.detach().float(), token_loss.detach().float(), balance.detach().float())) / accum
             du.all_reduce(train_losses, op="avg")
@@ -292,7 +299,8 @@ class Trainer:
             self.next_swa_update_tokens = get_next_update_tokens(cfg.swa_schedule_keys, self.swa_schedule_idx, cfg.max_tokens)
         raw.set_sliding_window(self.current_window_size)
         raw.clear_fp8_weights()
-        self.engine.step()
+        with self._nvtx("optimizer_step"):
+            self.engine.step()
 
         out = {"adamw_lr": adamw_lr, "tokens": bs * cfg.seq_len_train * self.effective_world_size * accum}
         if read_losses:
@@ -488,6 +496,9 @@ class Trainer:
     def close(self) -> None:
         if self.watchdog is not None:
             self.watchdog.stop()
+        if self.device_type == "cuda":
+            from ..ops import cuda_ops
+            cuda_ops.check_status()               # the per-step check is deferred by one step: surface the last one now
         du.barrier()
         if self.ep_size > 1 and self.device_type == "cuda":
             from ..parallel.ep_fused import release_workspaces

@@ -279,3 +279,27 @@ def test_attention_kernels_wide_query_key_heads(ops, t, window, hq, hk):
     assert rel(out, want) < 1e-2
     for name, got, exp in (("dq", q.grad, rq.grad), ("dk", k.grad, rk.grad), ("dv", v.grad, rv.grad)):
         assert rel(got, exp) < 2e-2, name
+
+
+def test_kernels_are_bitwise_deterministic(ops):
+    """No atomics decide a result: the same launch twice gives the same bits (GEMM, grouped GEMM, routing, norms, CE)."""
+    torch.manual_seed(12)
+    c = ops.ext()
+    a = torch.randn(1000, 768, device="cuda").bfloat16(); b = torch.randn(776, 768, device="cuda").bfloat16()
+    outs = []
+    for _ in range(2):
+        d = torch.empty(1000, 776, device="cuda", dtype=torch.bfloat16)
+        c.gemm_bf16(a, b, d)
+        idx = torch.randint(0, 8, (4096, 2), device="cuda", generator=torch.Generator("cuda").manual_seed(5))
+        route = c.route(idx, 8)
+        x = torch.randn(4096, 768, device="cuda", generator=torch.Generator("cuda").manual_seed(1))
+        dy = torch.randn(4096, 768, device="cuda", generator=torch.Generator("cuda").manual_seed(2)).bfloat16()
+        w = torch.ones(768, device="cuda")
+        y, rstd, _ = c.rmsnorm_fwd(x, w, 1e-6)
+        dx, dwn = c.rmsnorm_bwd(dy, x, w, rstd, None)
+        logits = torch.randn(512, 50304, device="cuda", generator=torch.Generator("cuda").manual_seed(3)).bfloat16()
+        tg = torch.randint(0, 50304, (512,), device="cuda", generator=torch.Generator("cuda").manual_seed(4))
+        loss = c.ce_fwd_bwd(logits, tg, torch.ones(1, device="cuda"), -100, True)
+        outs.append([d, route[0], route[1], y, dx, dwn, logits] + [t for t in (loss if isinstance(loss, (list, tuple)) else [loss])])
+    for first, second in zip(*outs):
+        assert torch.equal(first, second)
