@@ -88,23 +88,29 @@ void rope_qknorm_fwd(const Tensor& x, Tensor& out, const OptTensor& cos_t, const
     const long long tokens = x.size(0);
     GM_CHECK(launch_rope_qknorm(false, head_dim, x.data_ptr(), nullptr, out.data_ptr(), fptr(cos_t), fptr(sin_t), fptr(q_scale),
                                 fptr(k_scale), nullptr, tokens, seq_len, q_heads, k_heads, x.stride(0), out.stride(0),
-                                static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), copy_cols, stream()),
+                                static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), copy_cols, nullptr, 0, stream()),
              "unsupported head size for rope_qknorm");
 }
 
 // backward: dx written into `dx` (layout of x) for the q and k heads; returns dscale [q_heads + k_heads] (fp32)
+// `dq32` (optional, fp32 [tokens, q_heads * head_dim]): gradients of the query heads in full precision; when given, the query
+// columns of `dy` are not read.
 Tensor rope_qknorm_bwd(const Tensor& x, const Tensor& dy, Tensor& dx, const OptTensor& cos_t, const OptTensor& sin_t,
                        const OptTensor& q_scale, const OptTensor& k_scale, int64_t seq_len, int64_t q_heads, int64_t k_heads,
-                       int64_t head_dim, double eps, bool rms, double smin, double smax) {
+                       int64_t head_dim, double eps, bool rms, double smin, double smax, const OptTensor& dq32) {
     c10::cuda::CUDAGuard guard(x.device());
     const long long tokens = x.size(0);
     const int heads = q_heads + k_heads;
     const int blocks = rope_blocks(tokens, heads);
     Tensor partial = torch::empty({blocks, heads}, x.options().dtype(torch::kFloat32));
     GM_CHECK(x.stride(0) == dx.stride(0), "dx must share x's row stride");
+    if (dq32.has_value())
+        GM_CHECK(dq32->scalar_type() == torch::kFloat32 && dq32->is_contiguous() && dq32->numel() == tokens * q_heads * head_dim,
+                 "dq32 must be a contiguous fp32 [tokens, q_heads * head_dim] tensor");
     GM_CHECK(launch_rope_qknorm(true, head_dim, x.data_ptr(), dy.data_ptr(), dx.data_ptr(), fptr(cos_t), fptr(sin_t), fptr(q_scale),
                                 fptr(k_scale), partial.data_ptr<float>(), tokens, seq_len, q_heads, k_heads, x.stride(0),
-                                dy.stride(0), static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), 0, stream()),
+                                dy.stride(0), static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), 0,
+                                dq32.has_value() ? dq32->data_ptr<float>() : nullptr, dq32.has_value() ? q_heads * head_dim : 0, stream()),
              "unsupported head size for rope_qknorm");
     Tensor dscale = torch::empty({heads}, partial.options());
     launch_column_sum(partial.data_ptr<float>(), dscale.data_ptr<float>(), blocks, heads, 0, stream());
@@ -401,7 +407,9 @@ void register_kernels(pybind11::module_& m) {
     m.def("rope_qknorm_fwd", &rope_qknorm_fwd, py::arg("x"), py::arg("out"), py::arg("cos"), py::arg("sin"), py::arg("q_scale"), py::arg("k_scale"),
           py::arg("seq_len"), py::arg("q_heads"), py::arg("k_heads"), py::arg("head_dim"), py::arg("eps"), py::arg("rms"), py::arg("smin"),
           py::arg("smax"), py::arg("copy_cols") = 0);
-    m.def("rope_qknorm_bwd", &rope_qknorm_bwd);
+    m.def("rope_qknorm_bwd", &rope_qknorm_bwd, py::arg("x"), py::arg("dy"), py::arg("dx"), py::arg("cos"), py::arg("sin"), py::arg("q_scale"),
+          py::arg("k_scale"), py::arg("seq_len"), py::arg("q_heads"), py::arg("k_heads"), py::arg("head_dim"), py::arg("eps"), py::arg("rms"),
+          py::arg("smin"), py::arg("smax"), py::arg("dq32") = py::none());
     m.def("route", &route);
     m.def("gather_rows", &gather_rows);
     m.def("combine_fwd", &combine_fwd);

@@ -287,7 +287,7 @@ rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* dy,
                    const float* __restrict__ cos_t, const float* __restrict__ sin_t, const float* __restrict__ q_scale,
                    const float* __restrict__ k_scale, float* __restrict__ dscale_partial, long long tokens, int seq_len,
                    int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin, float smax,
-                   int copy_cols) {
+                   int copy_cols, const float* __restrict__ dq32, long long dq_stride) {
     constexpr int PAIRS = D / 2;
     constexpr int LANES = D / 8;                 // lanes per head
     constexpr int HEADS_PER_WARP = 32 / LANES;
@@ -317,12 +317,20 @@ rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* dy,
         uint4 xraw = make_uint4(0, 0, 0, 0), graw = make_uint4(0, 0, 0, 0);
         if (live) {
             xraw = *reinterpret_cast<const uint4*>(x + t * x_stride + h * D + li * 8);
-            if (BWD) graw = *reinterpret_cast<const uint4*>(dy + t * o_stride + h * D + li * 8);
+            if (BWD && !(dq32 != nullptr && h < q_heads)) graw = *reinterpret_cast<const uint4*>(dy + t * o_stride + h * D + li * 8);
         }
         const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xraw);
         const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&graw);
         float r1[4], r2[4], g1[4], g2[4];
         float ss = 0.f, dot = 0.f;
+        // backward: query-head gradients may arrive as fp32 (the attention backward's dQ accumulator) instead of bf16 rows
+        const bool g_fp32 = BWD && dq32 != nullptr && live && h < q_heads;
+        float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), gb = ga;
+        if (g_fp32) {
+            ga = *reinterpret_cast<const float4*>(dq32 + t * dq_stride + h * D + li * 8);
+            gb = *reinterpret_cast<const float4*>(dq32 + t * dq_stride + h * D + li * 8 + 4);
+        }
+        const float gq[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float2 xf = __bfloat1622float2(xp[i]);
@@ -331,7 +339,8 @@ rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* dy,
             ss += r1[i] * r1[i] + r2[i] * r2[i];
             if (BWD) {
                 const float2 gf = __bfloat1622float2(gp[i]);
-                g1[i] = gf.x; g2[i] = gf.y;
+                g1[i] = g_fp32 ? gq[2 * i] : gf.x;
+                g2[i] = g_fp32 ? gq[2 * i + 1] : gf.y;
                 dot += g1[i] * r1[i] + g2[i] * r2[i];
             }
         }
@@ -389,18 +398,18 @@ int rope_blocks(long long tokens, int heads) {
 bool launch_rope_qknorm(bool bwd, int D, const void* x, const void* dy, void* out, const float* cos_t, const float* sin_t,
                         const float* q_scale, const float* k_scale, float* dscale_partial, long long tokens, int seq_len,
                         int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin,
-                        float smax, int copy_cols, cudaStream_t s) {
+                        float smax, int copy_cols, const float* dq32, long long dq_stride, cudaStream_t s) {
     if (q_heads + k_heads > 64) return false;
     const int blocks = rope_blocks(tokens, q_heads + k_heads);
 #define GM_ROPE(DD)                                                                                                            \
     if (bwd)                                                                                                                   \
         rope_qknorm_kernel<DD, true><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), \
             static_cast<__nv_bfloat16*>(out), cos_t, sin_t, q_scale, k_scale, dscale_partial, tokens, seq_len, q_heads, k_heads,  \
-            x_stride, o_stride, eps, rms, smin, smax, 0);                                                                      \
+            x_stride, o_stride, eps, rms, smin, smax, 0, dq32, dq_stride);                                                     \
     else                                                                                                                       \
         rope_qknorm_kernel<DD, false><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), nullptr,                     \
             static_cast<__nv_bfloat16*>(out), cos_t, sin_t, q_scale, k_scale, nullptr, tokens, seq_len, q_heads, k_heads,        \
-            x_stride, o_stride, eps, rms, smin, smax, copy_cols);
+            x_stride, o_stride, eps, rms, smin, smax, copy_cols, nullptr, 0);
     switch (D) {
         case 32: GM_ROPE(32); break;
         case 64: GM_ROPE(64); break;

@@ -20,7 +20,7 @@ int rope_blocks(long long tokens, int heads);
 bool launch_rope_qknorm(bool bwd, int D, const void* x, const void* dy, void* out, const float* cos_t, const float* sin_t,
                         const float* q_scale, const float* k_scale, float* dscale_partial, long long tokens, int seq_len,
                         int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin,
-                        float smax, int copy_cols, cudaStream_t s);
+                        float smax, int copy_cols, const float* dq32, long long dq_stride, cudaStream_t s);
 
 // fused/moe.cu
 bool launch_route(const long long* idx, int slots, int experts, int* chunk_hist, int* chunk_start, int* counts, int* seg_ends,

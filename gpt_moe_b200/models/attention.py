@@ -109,8 +109,30 @@ class SelfAttention(nn.Module):
             self.qk_eps, self.qk_norm_type == "rms", self.qk_scale_min, self.qk_scale_max)
         return q, k, v
 
+    def _fused_rope_attention(self, x: Tensor, ctx: AttentionContext) -> Optional[Tensor]:
+        """One QKV GEMM, then RoPE + QK-norm + causal / sliding-window attention as a single autograd node (CUDA, 64-wide heads,
+        no soft-capping, masks or document ids).  Returns None when the shapes or options call for the general path."""
+        b, t, _ = x.shape
+        d, hq, hk = self.head_size, self.n_heads, self.n_kv_heads
+        if not (x.is_cuda and self.q_proj.bias is None and d == 64 and hq + hk <= 64 and hq % hk == 0 and t % 128 == 0
+                and self.is_causal and self.softcap == 0.0 and ctx.attn_mask is None and ctx.document_ids is None):
+            return None
+        from ..ops import cuda_ops
+        from ..ops.attention_cuda import _window_int
+        qkv = cuda_ops.linear_multi(x, (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight), self.q_proj.precision)
+        cos = sin = None
+        if self.rotary is not None:
+            cos, sin = self.rotary.cos_cached[:t], self.rotary.sin_cached[:t]
+        window = None if (self.is_full_attention or not self.use_flex_attention) else _window_int(ctx.window)
+        return cuda_ops.rope_attention_packed(
+            qkv.view(b * t, -1), cos, sin, self.q_scale if self.use_qk_norm else None, self.k_scale if self.use_qk_norm else None,
+            b, t, hq, hk, d, self.qk_eps, self.qk_norm_type == "rms", self.qk_scale_min, self.qk_scale_max, window, None)
+
     def forward(self, x: Tensor, ctx: AttentionContext) -> Tensor:
         b, t, _ = x.shape
+        y = self._fused_rope_attention(x, ctx)
+        if y is not None:
+            return self.out_proj(y.reshape(b, t, self.attn_dim))
         q, k, v = self.project_qkv(x)
         y = api.attention(
             q, k, v, causal=self.is_causal,

@@ -223,7 +223,10 @@ def router_gates(logits: Tensor, top_k: int, full_softmax: bool) -> Tuple[Tensor
     otherwise softmax renormalised over the selected logits (reference `model/feedforward/moe.py:59-76`).
     """
     logits = logits.float()
-    top_logits, top_idx = torch.topk(logits, top_k, dim=-1)
+    if top_k == 1:
+        top_logits, top_idx = logits.max(dim=-1, keepdim=True)          # same choice as topk, one small reduction instead of a sort
+    else:
+        top_logits, top_idx = torch.topk(logits, top_k, dim=-1)
     probs = F.softmax(logits, dim=-1)
     if top_k == 1 or full_softmax:
         gates = probs.gather(-1, top_idx)

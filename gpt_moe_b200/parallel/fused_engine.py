@@ -327,6 +327,15 @@ class FusedEngine:
             lr, momentum, nesterov = g["lr"], g["momentum"], g["nesterov"]
             if g["backend"] != "polarexpress":
                 raise NotImplementedError("the fused engine implements the Polar Express backend")
+            remaining = self.owned_shared
+            if self._early_layers:
+                # blocks whose update already ran beside the backward pass: join that stream, then do what is left
+                torch.cuda.current_stream().wait_stream(self.comm_stream)
+                remaining = [(n, p) for layer, items in self.layer_items.items() if layer not in self._early_layers for n, p in items]
+                self._early_layers = set()
+            self._muon_update(remaining, self.grad_muon.deltas, self.compute.deltas, lr, momentum, nesterov)
+            self._muon_update(self.owned_local, [0], [0], lr, momentum, nesterov)
+            # (issued after the large batches: its many tiny launches are host-bound and hide behind the queued GEMMs)
             # tiny matrices (routers): every rank averages them out of all buffers and repeats the small update
             if self.small:
                 lo, hi = self.small_range
@@ -355,14 +364,6 @@ class FusedEngine:
                         p = self.small[i][1]
                         p.data.add_(oi.to(p.dtype), alpha=-lr * max(shape) ** 0.5)
                         p.compute.copy_(p.data)
-            remaining = self.owned_shared
-            if self._early_layers:
-                # blocks whose update already ran beside the backward pass: join that stream, then do what is left
-                torch.cuda.current_stream().wait_stream(self.comm_stream)
-                remaining = [(n, p) for layer, items in self.layer_items.items() if layer not in self._early_layers for n, p in items]
-                self._early_layers = set()
-            self._muon_update(remaining, self.grad_muon.deltas, self.compute.deltas, lr, momentum, nesterov)
-            self._muon_update(self.owned_local, [0], [0], lr, momentum, nesterov)
         g0 = adamw.param_groups[0]
         self.adamw_step += 1
         c.adamw_sharded(self.adamw_param.tensor, self.adamw_grad.tensor, self.adamw_m, self.adamw_v, self.adamw_decay,
