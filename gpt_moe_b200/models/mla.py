@@ -124,10 +124,50 @@ class MLAttention(nn.Module):
             attn_mask=ctx.attn_mask, document_ids=ctx.document_ids)
         return out, key_gain
 
+    def _fused_forward(self, x: Tensor, ctx: AttentionContext) -> Optional[Tensor]:
+        """CUDA training path: the rotary rotation of the rope parts, the per-head QK-norm over the whole 128-wide head and the
+        learned clamped scales run as ONE kernel over the packed [query heads | key heads] rows - the same kernel as for
+        ordinary attention, given cos/sin tables that are the identity rotation on the content half of a head - followed by
+        the 128/64-wide tcgen05 attention kernels.  Returns None when shapes or options need the general path."""
+        b, t, _ = x.shape
+        h, hk, d = self.n_heads, self.n_kv_heads, self.head_size
+        if not (x.is_cuda and d == 128 and self.value_dim == 64 and self.rope_dim > 0 and self.rotary is not None and h + hk <= 64
+                and t % 128 == 0 and self.is_causal and self.softcap == 0.0 and ctx.attn_mask is None and ctx.document_ids is None
+                and self.q_proj.bias is None):
+            return None
+        from ..ops import cuda_ops
+        query = x
+        if self.q_rank:
+            query = api.rms_norm(self.q_down_proj(query), self.q_norm.weight, self.q_norm.eps)
+        query = self.q_proj(query).view(b, t, h, d)
+        compressed = self.kv_down_proj(x)
+        latent, rope = compressed.split((self.kv_rank, self.rope_dim), dim=-1)
+        latent = api.rms_norm(latent.contiguous(), self.kv_norm.weight, self.kv_norm.eps).to(compressed.dtype)
+        kv = self.kv_up_proj(latent).view(b, t, hk, self.content_dim + self.value_dim)
+        k_content, value = kv.split((self.content_dim, self.value_dim), dim=-1)
+        key = torch.cat((k_content, rope.reshape(b, t, 1, self.rope_dim).expand(-1, -1, hk, -1)), dim=-1)
+        packed = torch.cat((query, key.to(query.dtype)), dim=2).to(torch.bfloat16)          # [B, T, H + Hkv, 128]: rows of heads
+        if getattr(self, "_cos_padded", None) is None or self._cos_padded.device != x.device:
+            # identity rotation (cos 1, sin 0) on the content pairs, the rotary tables on the rope pairs
+            cos, sin = self.rotary.cos_cached.float(), self.rotary.sin_cached.float()
+            pad = self.content_dim // 2
+            self._cos_padded = torch.cat((torch.ones(cos.shape[0], pad, device=cos.device), cos), dim=1).contiguous()
+            self._sin_padded = torch.cat((torch.zeros(sin.shape[0], pad, device=sin.device), sin), dim=1).contiguous()
+        rotated = cuda_ops.rope_qk_norm_packed(
+            packed.view(b * t, -1), self._cos_padded[:t], self._sin_padded[:t], self.q_scale if self.use_qk_norm else None,
+            self.k_scale if self.use_qk_norm else None, t, h, hk, d, self.qk_eps, self.qk_norm_type == "rms",
+            self.qk_scale_min, self.qk_scale_max).view(b, t, h + hk, d)
+        out = api.attention(
+            rotated[:, :, :h], rotated[:, :, h:], value.contiguous(), causal=True,
+            window=None if (self.is_full_attention or not self.use_flex_attention) else ctx.window, scale=self.softmax_scale)
+        return out
+
     def forward(self, x: Tensor, ctx: AttentionContext) -> Tensor:
         b, t, _ = x.shape
-        query, latent, rope = self._project(x)
-        out, _ = self._expand(query, latent, rope, ctx)
+        out = self._fused_forward(x, ctx)
+        if out is None:
+            query, latent, rope = self._project(x)
+            out, _ = self._expand(query, latent, rope, ctx)
         return self.out_proj(out.reshape(b, t, self.attn_dim))
 
     # ---- cached generation ---------------------------------------------------------------------
