@@ -304,3 +304,25 @@ def test_kernels_are_bitwise_deterministic(ops):
         outs.append([d, route[0], route[1][:used], route[2], route[4][: used // 128], y, dx, dwn, logits] + [t for t in (loss if isinstance(loss, (list, tuple)) else [loss])])
     for first, second in zip(*outs):
         assert torch.equal(first, second)
+
+
+def test_bounded_wait_gives_up_and_reports(ops):
+    """A wait on a flag that nothing sets runs out of its budget (about a second), records its code in the status word
+    and returns: the context stays usable and the host sees the failure."""
+    c = ops.ext()
+    c.reset_status()
+    flags = torch.zeros(4, dtype=torch.int32, device="cuda")
+    c.flag_signal(flags, [0], 1, 7)                       # slot 1 is published, slot 0 never is
+    c.flag_wait(flags, 1, 1, 7)                           # satisfied at once
+    torch.cuda.synchronize()
+    assert c.read_status() == 0 and flags.tolist() == [0, 7, 0, 0]
+    c.flag_wait(flags, 0, 1, 7)                           # nobody writes flags[0]
+    torch.cuda.synchronize()
+    assert c.read_status() == 601
+    with pytest.raises(RuntimeError):
+        ops.check_status()
+    assert c.read_status() == 0                           # check_status clears the word
+    a = torch.randn(128, 64, device="cuda").bfloat16()
+    d = torch.empty(128, 128, device="cuda", dtype=torch.bfloat16)
+    c.gemm_bf16(a, a, d)                                  # kernels still run afterwards
+    assert rel(d, a.float() @ a.float().t()) < BF16_TOL
