@@ -15,6 +15,7 @@ struct AttnParams {
     const int* window_ptr;          // optional device-resident window (overrides `window`)
     float scale_log2e;              // softmax scale * log2(e)
     float scale;                    // softmax scale
+    float softcap;                  // > 0: logits are soft-capped, z = softcap * tanh(scale * s / softcap), before the softmax
     void* out;                      // forward: O [tokens, heads*64] bf16
     long long out_stride;
     float* lse;                     // [batch, heads, seq] natural-log LSE of the scaled scores

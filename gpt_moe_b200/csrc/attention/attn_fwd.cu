@@ -45,6 +45,12 @@ __device__ __forceinline__ float exp2_poly(float x) {
     return __int_as_float(__float_as_int(pl) + (__float_as_int(shifted) << 23));
 }
 
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ void tma_load_2d_as3d(void* dst, const void* tmap, uint64_t* bar, int col, int row) {
     tma_load_3d(dst, tmap, bar, col, row, 0);
 }
@@ -53,10 +59,12 @@ __device__ __forceinline__ void tma_load_2d_as3d(void* dst, const void* tmap, ui
 // Pass 1 finds the row maximum (combined with the other half of the row through shared memory); pass 2 forms the
 // exponentials, packs them to bf16 pairs and writes them to the P columns of TMEM.  MASK selects the token-exact
 // causal/window test; it is a template parameter so interior tiles carry no per-element compare or branch.
-template <bool MASK>
+// CAP: logit soft-capping.  The raw score s becomes cap_a * tanh(s * cap_b) with cap_b = scale / softcap and cap_a = softcap / scale,
+// so that multiplying by c = scale * log2(e) afterwards gives the capped logit in the base-2 domain.
+template <bool MASK, bool CAP>
 __device__ __forceinline__ void softmax_tile(uint32_t s_addr, uint32_t p_addr, int kv0, int qpos, int window, float c, float m,
                                              float* row_stat, int half, int r, int bar_id, float& tile_max, float& alpha,
-                                             float& base, float& row_sum) {
+                                             float& base, float& row_sum, float cap_a, float cap_b) {
     float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
@@ -66,6 +74,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_addr, uint32_t p_addr, i
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             float v = __uint_as_float(sreg[i]);
+            if (CAP) v = cap_a * tanh_approx(v * cap_b);
             if (MASK) {
                 const int kpos = kv0 + cc * 32 + i;
                 v = (kpos > qpos || qpos - kpos > window) ? -INFINITY : v;
@@ -93,6 +102,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_addr, uint32_t p_addr, i
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
                 float v = __uint_as_float(sreg[i + u]);
+                if (CAP) v = cap_a * tanh_approx(v * cap_b);
                 if (MASK) {
                     const int kpos = kv0 + cc * 32 + i + u;
                     v = (kpos > qpos || qpos - kpos > window) ? -INFINITY : v;
@@ -108,7 +118,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_addr, uint32_t p_addr, i
     row_sum = (sum[0] + sum[1]) + (sum[2] + sum[3]);
 }
 
-template <int DQK>
+template <int DQK, bool CAPPED>
 __global__ void __launch_bounds__(AT_THREADS, DQK == 64 ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
@@ -217,6 +227,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int qpos = q0 + r;
         const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
         const float c = p.scale_log2e;
+        constexpr bool capped = CAPPED;
+        const float cap_a = capped ? p.softcap / p.scale : 0.f, cap_b = capped ? p.scale / p.softcap : 0.f;
         float m = -INFINITY, l = 0.f;
         float o[AT_D / 2];
 #pragma unroll
@@ -231,10 +243,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const int tile0 = kv_lo + j * AT_BN;
             const bool need_mask = (tile0 + AT_BN - 1 > q0) || (q0 + AT_BM - 1 - tile0 > window);
             float tile_max, alpha, base, row_sum;
-            if (need_mask) softmax_tile<true>(tmem_s + lane_off + half * 64, tmem_p + lane_off + half * 32, kv0, qpos, window, c, m,
-                                              row_stat, half, r, bar_id, tile_max, alpha, base, row_sum);
-            else softmax_tile<false>(tmem_s + lane_off + half * 64, tmem_p + lane_off + half * 32, kv0, qpos, window, c, m,
-                                     row_stat, half, r, bar_id, tile_max, alpha, base, row_sum);
+            const uint32_t sa = tmem_s + lane_off + half * 64, pa = tmem_p + lane_off + half * 32;
+            if (capped) {
+                if (need_mask) softmax_tile<true, true>(sa, pa, kv0, qpos, window, c, m, row_stat, half, r, bar_id, tile_max, alpha, base, row_sum, cap_a, cap_b);
+                else softmax_tile<false, true>(sa, pa, kv0, qpos, window, c, m, row_stat, half, r, bar_id, tile_max, alpha, base, row_sum, cap_a, cap_b);
+            } else {
+                if (need_mask) softmax_tile<true, false>(sa, pa, kv0, qpos, window, c, m, row_stat, half, r, bar_id, tile_max, alpha, base, row_sum, 0.f, 0.f);
+                else softmax_tile<false, false>(sa, pa, kv0, qpos, window, c, m, row_stat, half, r, bar_id, tile_max, alpha, base, row_sum, 0.f, 0.f);
+            }
             const float m_new = fmaxf(m, tile_max * c);
             tmem_st_wait();
             l = l * alpha + row_sum;
@@ -286,10 +302,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
 }
 
-template <int DQK>
+template <int DQK, bool CAPPED>
 static cudaError_t launch_fwd_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t stream) {
     constexpr int smem = (DQK / 64) * SLAB_BYTES * (1 + KV_STAGES) + KV_STAGES * V_BYTES + 1024 + 128 + 2 * AT_BM * 4;
-    auto kernel = attn_fwd_kernel<DQK>;
+    auto kernel = attn_fwd_kernel<DQK, CAPPED>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -304,8 +320,9 @@ static cudaError_t launch_fwd_variant(const CUtensorMap& tq, const CUtensorMap& 
 }
 
 cudaError_t launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t stream) {
-    if (p.qk_dim == 128) return launch_fwd_variant<128>(tq, tk, tv, p, stream);
-    return launch_fwd_variant<64>(tq, tk, tv, p, stream);
+    const bool capped = p.softcap > 0.f;
+    if (p.qk_dim == 128) return capped ? launch_fwd_variant<128, true>(tq, tk, tv, p, stream) : launch_fwd_variant<128, false>(tq, tk, tv, p, stream);
+    return capped ? launch_fwd_variant<64, true>(tq, tk, tv, p, stream) : launch_fwd_variant<64, false>(tq, tk, tv, p, stream);
 }
 
 }  // namespace gm

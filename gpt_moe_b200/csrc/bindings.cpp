@@ -235,7 +235,8 @@ const CUtensorMap& head_map(const torch::Tensor& t, int box_rows) {
 }
 
 // Returns (out [B,T,H,64] bf16, lse [B,H,T] fp32).
-std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, int64_t window, double scale) {
+std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, int64_t window, double scale,
+                                    double softcap) {
     c10::cuda::CUDAGuard guard(q.device());
     const int B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
     GM_CHECK((D == 64 || D == 128) && k.size(3) == D && v.size(3) == 64 && T % 128 == 0 && H % Hkv == 0,
@@ -246,6 +247,7 @@ std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor&
     p.window = static_cast<int>(std::min<int64_t>(window, T));
     p.scale = static_cast<float>(scale);
     p.scale_log2e = static_cast<float>(scale * 1.4426950408889634);
+    p.softcap = static_cast<float>(softcap);
     auto out = torch::empty({B, T, H, 64}, q.options());
     auto lse = torch::empty({B, H, T}, q.options().dtype(torch::kFloat32));
     p.out = out.data_ptr(); p.out_stride = H * 64; p.lse = lse.data_ptr<float>();
@@ -259,7 +261,7 @@ std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor&
 // (they may be column slices of a packed gradient buffer).  Returns dq as fp32 [B,T,H,64].
 torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, const torch::Tensor& out,
                        const torch::Tensor& d_out, const torch::Tensor& lse, torch::Tensor& dk, torch::Tensor& dv, int64_t window,
-                       double scale) {
+                       double scale, double softcap) {
     c10::cuda::CUDAGuard guard(q.device());
     const int B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
     GM_CHECK((D == 64 || D == 128) && k.size(3) == D && v.size(3) == 64 && T % 128 == 0 && H % Hkv == 0,
@@ -273,6 +275,7 @@ torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const tor
     p.window = static_cast<int>(std::min<int64_t>(window, T));
     p.scale = static_cast<float>(scale);
     p.scale_log2e = static_cast<float>(scale * 1.4426950408889634);
+    p.softcap = static_cast<float>(softcap);
     p.lse = const_cast<float*>(lse.data_ptr<float>());
     auto delta = torch::empty({B, H, T}, lse.options());
     auto dq = torch::zeros({B, T, H, D}, lse.options());
@@ -307,7 +310,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("mxfp8_quantize_transposed", &mxfp8_quantize_transposed);
     m.def("gemm_mxfp8", &gemm_mxfp8, py::arg("a"), py::arg("sfa"), py::arg("b"), py::arg("sfb"), py::arg("d"), py::arg("alpha") = 1.0,
           py::arg("tile_expert") = py::none(), py::arg("num_m_tiles") = py::none());
-    m.def("attn_fwd", &attn_fwd);
-    m.def("attn_bwd", &attn_bwd);
+    m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0);
+    m.def("attn_bwd", &attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("d_out"), py::arg("lse"), py::arg("dk"),
+          py::arg("dv"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0);
     gm::register_kernels(m);
 }

@@ -101,10 +101,26 @@ muon_apply_push_kernel(float* const* __restrict__ weights, __nv_bfloat16* const*
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int c0 = blockIdx.x * 128, r0 = blockIdx.y * 32;
     if (transpose) {                                                 // update is [cols][rows]: stage the 128 x 32 block
+        if ((rows & 3) == 0) {                                       // 8-byte loads: four consecutive rows of one column
+            const int r4 = (threadIdx.x & 7) * 4, cl0 = threadIdx.x >> 3;          // 8 threads cover 32 rows; 32 columns per pass
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const int c = c0 + ty + 8 * i, r = r0 + tx;
-            tile[ty + 8 * i][tx] = (r < rows && c < cols) ? __bfloat162float(o[static_cast<long long>(c) * rows + r]) : 0.f;
+            for (int i = 0; i < 4; ++i) {
+                const int cl = cl0 + 32 * i, c = c0 + cl, r = r0 + r4;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (c < cols && r < rows) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(o + static_cast<long long>(c) * rows + r);
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                    v = make_float4(a.x, a.y, b.x, b.y);
+                }
+                tile[cl][r4] = v.x; tile[cl][r4 + 1] = v.y; tile[cl][r4 + 2] = v.z; tile[cl][r4 + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int c = c0 + ty + 8 * i, r = r0 + tx;
+                tile[ty + 8 * i][tx] = (r < rows && c < cols) ? __bfloat162float(o[static_cast<long long>(c) * rows + r]) : 0.f;
+            }
         }
         __syncthreads();
     }

@@ -111,11 +111,11 @@ class SelfAttention(nn.Module):
 
     def _fused_rope_attention(self, x: Tensor, ctx: AttentionContext) -> Optional[Tensor]:
         """One QKV GEMM, then RoPE + QK-norm + causal / sliding-window attention as a single autograd node (CUDA, 64-wide heads,
-        no soft-capping, masks or document ids).  Returns None when the shapes or options call for the general path."""
+        optional logit soft-capping, no masks or document ids).  Returns None when the shapes or options call for the general path."""
         b, t, _ = x.shape
         d, hq, hk = self.head_size, self.n_heads, self.n_kv_heads
         if not (x.is_cuda and self.q_proj.bias is None and d == 64 and hq + hk <= 64 and hq % hk == 0 and t % 128 == 0
-                and self.is_causal and self.softcap == 0.0 and ctx.attn_mask is None and ctx.document_ids is None):
+                and self.is_causal and ctx.attn_mask is None and ctx.document_ids is None):
             return None
         from ..ops import cuda_ops
         from ..ops.attention_cuda import _window_int
@@ -126,7 +126,7 @@ class SelfAttention(nn.Module):
         window = None if (self.is_full_attention or not self.use_flex_attention) else _window_int(ctx.window)
         return cuda_ops.rope_attention_packed(
             qkv.view(b * t, -1), cos, sin, self.q_scale if self.use_qk_norm else None, self.k_scale if self.use_qk_norm else None,
-            b, t, hq, hk, d, self.qk_eps, self.qk_norm_type == "rms", self.qk_scale_min, self.qk_scale_max, window, None)
+            b, t, hq, hk, d, self.qk_eps, self.qk_norm_type == "rms", self.qk_scale_min, self.qk_scale_max, window, None, self.softcap)
 
     def forward(self, x: Tensor, ctx: AttentionContext) -> Tensor:
         b, t, _ = x.shape

@@ -3,10 +3,10 @@
 `attention()` takes token-major tensors q[B,T,H,Dk], k[B,T,Hkv,Dk], v[B,T,Hkv,Dv] (views into the
 packed projection output are fine: only the last dimension must be contiguous).
 
-Causal / sliding-window attention without padding, document masks or soft-capping goes to the
-tcgen05 kernel in `csrc/attention` when it is built for the head size; everything else — and any
-shape the kernel does not cover — runs through torch's fused SDPA with an explicit boolean mask,
-which is the slow but general path.
+Causal / sliding-window attention without padding or document masks (with or without logit
+soft-capping) goes to the tcgen05 kernel in `csrc/attention` when it is built for the head size;
+everything else — and any shape the kernel does not cover — runs through the flash-attn library
+kernel or torch's fused SDPA with an explicit boolean mask, which is the slow but general path.
 """
 from __future__ import annotations
 
@@ -54,7 +54,7 @@ def attention(q: Tensor, k: Tensor, v: Tensor, *, causal: bool = True, window=No
     if plain and causal:
         from . import attention_tc
         if attention_tc.supported(q, k, v, softcap_value):
-            return attention_tc.attention(q, k, v, window=w, scale=scale)
+            return attention_tc.attention(q, k, v, window=w, scale=scale, softcap=softcap_value)
         flash = _flash_attn()
         dv = v.shape[-1]
         if flash and q.dtype == torch.bfloat16 and dv <= dk and dk <= 256 and softcap_value == 0.0:

@@ -11,42 +11,43 @@ from torch import Tensor
 def supported(q: Tensor, k: Tensor, v: Tensor, softcap_value: float) -> bool:
     b, t, h, d = q.shape
     return (q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16 and d in (64, 128) and k.shape[-1] == d
-            and v.shape[-1] == 64 and t % 128 == 0 and softcap_value == 0.0 and h % k.shape[2] == 0
+            and v.shape[-1] == 64 and t % 128 == 0 and softcap_value >= 0.0 and h % k.shape[2] == 0
             and all(x.stride(3) == 1 and x.stride(2) == x.shape[3] and x.stride(0) == t * x.stride(1) and x.stride(1) % 8 == 0 for x in (q, k, v)))
 
 
 class _AttentionFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q: Tensor, k: Tensor, v: Tensor, window: int, scale: float) -> Tensor:
+    def forward(ctx, q: Tensor, k: Tensor, v: Tensor, window: int, scale: float, softcap: float) -> Tensor:
         from .cuda_ops import ext
-        out, lse = ext().attn_fwd(q, k, v, window, scale)
+        out, lse = ext().attn_fwd(q, k, v, window, scale, softcap)
         ctx.save_for_backward(q, k, v, out, lse)
-        ctx.cfg = (window, scale)
+        ctx.cfg = (window, scale, softcap)
         return out
 
     @staticmethod
     def backward(ctx, d_out: Tensor):
         from .cuda_ops import ext
         q, k, v, out, lse = ctx.saved_tensors
-        window, scale = ctx.cfg
+        window, scale, softcap = ctx.cfg
         b, t, h, d = q.shape
         hk = k.shape[2]
         d_out = d_out if (d_out.stride(3) == 1 and d_out.stride(2) == 64 and d_out.stride(0) == t * d_out.stride(1)) else d_out.contiguous()
         if d != 64:                   # wide query / key heads: separate gradient tensors
             dk = torch.empty((b, t, hk, d), dtype=q.dtype, device=q.device)
             dv = torch.empty((b, t, hk, 64), dtype=q.dtype, device=q.device)
-            dq32 = ext().attn_bwd(q, k, v, out, d_out, lse, dk, dv, window, scale)
-            return dq32.to(q.dtype), dk, dv, None, None
+            dq32 = ext().attn_bwd(q, k, v, out, d_out, lse, dk, dv, window, scale, softcap)
+            return dq32.to(q.dtype), dk, dv, None, None, None
         # one packed gradient buffer [B, T, (H + 2 Hkv) * 64]: dk and dv are written in place by the kernel, dq is converted into it
         packed = torch.empty((b, t, (h + 2 * hk) * d), dtype=q.dtype, device=q.device)
         dk = packed[..., h * d: (h + hk) * d].unflatten(-1, (hk, d))
         dv = packed[..., (h + hk) * d:].unflatten(-1, (hk, d))
-        dq32 = ext().attn_bwd(q, k, v, out, d_out, lse, dk, dv, window, scale)
+        dq32 = ext().attn_bwd(q, k, v, out, d_out, lse, dk, dv, window, scale, softcap)
         dq = packed[..., : h * d].unflatten(-1, (h, d))
         dq.copy_(dq32)
-        return dq, dk, dv, None, None
+        return dq, dk, dv, None, None, None
 
 
-def attention(q: Tensor, k: Tensor, v: Tensor, *, window: Optional[int], scale: Optional[float]) -> Tensor:
+def attention(q: Tensor, k: Tensor, v: Tensor, *, window: Optional[int], scale: Optional[float], softcap: float = 0.0) -> Tensor:
+    """`softcap` > 0 caps the scaled logits with softcap * tanh(logit / softcap) (hardware `tanh.approx`) before the softmax."""
     t, d = q.shape[1], q.shape[3]
-    return _AttentionFn.apply(q, k, v, t if window is None else int(window), d ** -0.5 if scale is None else float(scale))
+    return _AttentionFn.apply(q, k, v, t if window is None else int(window), d ** -0.5 if scale is None else float(scale), float(softcap))

@@ -326,3 +326,26 @@ def test_bounded_wait_gives_up_and_reports(ops):
     d = torch.empty(128, 128, device="cuda", dtype=torch.bfloat16)
     c.gemm_bf16(a, a, d)                                  # kernels still run afterwards
     assert rel(d, a.float() @ a.float().t()) < BF16_TOL
+
+
+@pytest.mark.parametrize("dqk,window", [(64, 200), (128, 2000)])
+def test_attention_kernels_with_logit_softcapping(ops, dqk, window):
+    """softcap * tanh(scale * s / softcap) before the softmax, forward and backward (hardware tanh.approx)."""
+    from gpt_moe_b200.ops import attention_tc
+    torch.manual_seed(13)
+    b, t, hq, hk, cap = 2, 512, 4, 2, 15.0
+    q = torch.randn(b, t, hq, dqk, device="cuda").mul_(2.0).bfloat16().requires_grad_()      # large logits so the cap matters
+    k = torch.randn(b, t, hk, dqk, device="cuda").mul_(2.0).bfloat16().requires_grad_()
+    v = torch.randn(b, t, hk, 64, device="cuda").bfloat16().requires_grad_()
+    assert attention_tc.supported(q, k, v, cap)
+    out = attention_tc.attention(q, k, v, window=window, scale=None, softcap=cap)
+    g = torch.randn_like(out)
+    out.backward(g)
+    rq, rk, rv = (x.detach().float().requires_grad_() for x in (q, k, v))
+    want = ref.attention(rq, rk, rv, causal=True, window=window, softcap_value=cap, tanh_backend="exact")
+    want.backward(g.float())
+    plain = ref.attention(rq.detach(), rk.detach(), rv.detach(), causal=True, window=window)
+    assert rel(plain, want) > 5e-2                        # the cap changes the result on this input
+    assert rel(out, want) < 1.5e-2
+    for name, got, exp in (("dq", q.grad, rq.grad), ("dk", k.grad, rk.grad), ("dv", v.grad, rv.grad)):
+        assert rel(got, exp) < 3e-2, name
