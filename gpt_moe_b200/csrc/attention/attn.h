@@ -13,6 +13,8 @@ struct AttnParams {
     int q_col0, k_col0, v_col0;     // first column of head 0 inside each tensor map
     int window;                     // inclusive look-back W (a query sees keys q-W..q); >= seq_len means plain causal
     const int* window_ptr;          // optional device-resident window (overrides `window`)
+    const int* doc_start;           // optional [batch * seq]: position (inside its sequence) of the first token of each token's document;
+                                    // a query then sees keys max(q - W, doc_start[q]) .. q (documents are contiguous runs of tokens)
     float scale_log2e;              // softmax scale * log2(e)
     float scale;                    // softmax scale
     float softcap;                  // > 0: logits are soft-capped, z = softcap * tanh(scale * s / softcap), before the softmax

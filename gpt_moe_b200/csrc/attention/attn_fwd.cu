@@ -143,12 +143,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int q_tile = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
     const int q0 = q_tile * AT_BM;
     const int window = p.window_ptr ? *p.window_ptr : p.window;
-    int kv_lo = q0 - window;
+    const int row0 = batch * p.seq_len;
+    // document masking narrows a row's look-back to the start of its document; look-backs shrink monotonically towards
+    // later rows of a document, so the first row bounds the tiles to visit and the last row decides whether a tile needs masking
+    int w_first = window, w_last = window;
+    if (p.doc_start) {
+        w_first = min(window, q0 - p.doc_start[row0 + q0]);
+        w_last = min(window, q0 + AT_BM - 1 - p.doc_start[row0 + q0 + AT_BM - 1]);
+    }
+    int kv_lo = q0 - w_first;
     if (kv_lo < 0) kv_lo = 0;
     kv_lo &= ~(AT_BN - 1);
     const int n_tiles = (q0 + AT_BM - kv_lo) / AT_BN;
     const int kv_head = head / p.group;                       // grouped-query attention: several q heads share a kv head
-    const int row0 = batch * p.seq_len;
     const int q_col = p.q_col0 + head * DQK, k_col = p.k_col0 + kv_head * DQK, v_col = p.v_col0 + kv_head * AT_D;
 
     if (threadIdx.x == 0) {
@@ -225,6 +232,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int quad = warp & 3, half = warp >> 2;         // TMEM lanes 32*quad..+31; key / output columns of this half
         const int r = quad * 32 + lane;
         const int qpos = q0 + r;
+        const int w_row = p.doc_start ? min(window, qpos - p.doc_start[row0 + qpos]) : window;     // this row's look-back
         const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
         const float c = p.scale_log2e;
         constexpr bool capped = CAPPED;
@@ -241,15 +249,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             tc_fence_after();
             // tiles strictly inside the band need no mask; the diagonal tile and the tile(s) at the window edge do
             const int tile0 = kv_lo + j * AT_BN;
-            const bool need_mask = (tile0 + AT_BN - 1 > q0) || (q0 + AT_BM - 1 - tile0 > window);
+            const bool need_mask = (tile0 + AT_BN - 1 > q0) || (q0 + AT_BM - 1 - tile0 > w_last);
             float tile_max, alpha, base, row_sum;
             const uint32_t sa = tmem_s + lane_off + half * 64, pa = tmem_p + lane_off + half * 32;
             if (capped) {
-                if (need_mask) softmax_tile<true, true>(sa, pa, kv0, qpos, window, c, m, row_stat, half, r, bar_id, tile_max, alpha, base, row_sum, cap_a, cap_b);
-                else softmax_tile<false, true>(sa, pa, kv0, qpos, window, c, m, row_stat, half, r, bar_id, tile_max, alpha, base, row_sum, cap_a, cap_b);
+                if (need_mask) softmax_tile<true, true>(sa, pa, kv0, qpos, w_row, c, m, row_stat, half, r, bar_id, tile_max, alpha, base, row_sum, cap_a, cap_b);
+                else softmax_tile<false, true>(sa, pa, kv0, qpos, w_row, c, m, row_stat, half, r, bar_id, tile_max, alpha, base, row_sum, cap_a, cap_b);
             } else {
-                if (need_mask) softmax_tile<true, false>(sa, pa, kv0, qpos, window, c, m, row_stat, half, r, bar_id, tile_max, alpha, base, row_sum, 0.f, 0.f);
-                else softmax_tile<false, false>(sa, pa, kv0, qpos, window, c, m, row_stat, half, r, bar_id, tile_max, alpha, base, row_sum, 0.f, 0.f);
+                if (need_mask) softmax_tile<true, false>(sa, pa, kv0, qpos, w_row, c, m, row_stat, half, r, bar_id, tile_max, alpha, base, row_sum, 0.f, 0.f);
+                else softmax_tile<false, false>(sa, pa, kv0, qpos, w_row, c, m, row_stat, half, r, bar_id, tile_max, alpha, base, row_sum, 0.f, 0.f);
             }
             const float m_new = fmaxf(m, tile_max * c);
             tmem_st_wait();

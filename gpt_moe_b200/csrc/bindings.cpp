@@ -235,8 +235,15 @@ const CUtensorMap& head_map(const torch::Tensor& t, int box_rows) {
 }
 
 // Returns (out [B,T,H,64] bf16, lse [B,H,T] fp32).
+const int* doc_start_ptr(const c10::optional<torch::Tensor>& doc_start, int64_t tokens) {
+    if (!doc_start.has_value()) return nullptr;
+    GM_CHECK(doc_start->is_cuda() && doc_start->scalar_type() == torch::kInt32 && doc_start->is_contiguous() && doc_start->numel() == tokens,
+             "doc_start must be a contiguous int32 CUDA tensor with one entry per token");
+    return doc_start->data_ptr<int>();
+}
+
 std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, int64_t window, double scale,
-                                    double softcap) {
+                                    double softcap, const c10::optional<torch::Tensor>& doc_start) {
     c10::cuda::CUDAGuard guard(q.device());
     const int B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
     GM_CHECK((D == 64 || D == 128) && k.size(3) == D && v.size(3) == 64 && T % 128 == 0 && H % Hkv == 0,
@@ -248,6 +255,7 @@ std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor&
     p.scale = static_cast<float>(scale);
     p.scale_log2e = static_cast<float>(scale * 1.4426950408889634);
     p.softcap = static_cast<float>(softcap);
+    p.doc_start = doc_start_ptr(doc_start, static_cast<int64_t>(B) * T);
     auto out = torch::empty({B, T, H, 64}, q.options());
     auto lse = torch::empty({B, H, T}, q.options().dtype(torch::kFloat32));
     p.out = out.data_ptr(); p.out_stride = H * 64; p.lse = lse.data_ptr<float>();
@@ -261,7 +269,7 @@ std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor&
 // (they may be column slices of a packed gradient buffer).  Returns dq as fp32 [B,T,H,64].
 torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, const torch::Tensor& out,
                        const torch::Tensor& d_out, const torch::Tensor& lse, torch::Tensor& dk, torch::Tensor& dv, int64_t window,
-                       double scale, double softcap) {
+                       double scale, double softcap, const c10::optional<torch::Tensor>& doc_start) {
     c10::cuda::CUDAGuard guard(q.device());
     const int B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
     GM_CHECK((D == 64 || D == 128) && k.size(3) == D && v.size(3) == 64 && T % 128 == 0 && H % Hkv == 0,
@@ -276,6 +284,7 @@ torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const tor
     p.scale = static_cast<float>(scale);
     p.scale_log2e = static_cast<float>(scale * 1.4426950408889634);
     p.softcap = static_cast<float>(softcap);
+    p.doc_start = doc_start_ptr(doc_start, static_cast<int64_t>(B) * T);
     p.lse = const_cast<float*>(lse.data_ptr<float>());
     auto delta = torch::empty({B, H, T}, lse.options());
     auto dq = torch::zeros({B, T, H, D}, lse.options());
@@ -310,8 +319,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("mxfp8_quantize_transposed", &mxfp8_quantize_transposed);
     m.def("gemm_mxfp8", &gemm_mxfp8, py::arg("a"), py::arg("sfa"), py::arg("b"), py::arg("sfb"), py::arg("d"), py::arg("alpha") = 1.0,
           py::arg("tile_expert") = py::none(), py::arg("num_m_tiles") = py::none());
-    m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0);
+    m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0,
+          py::arg("doc_start") = py::none());
     m.def("attn_bwd", &attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("d_out"), py::arg("lse"), py::arg("dk"),
-          py::arg("dv"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0);
+          py::arg("dv"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0, py::arg("doc_start") = py::none());
     gm::register_kernels(m);
 }

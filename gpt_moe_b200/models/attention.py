@@ -41,10 +41,11 @@ class AttentionContext:
     window: 0-dim int32 tensor (device resident, so a window-schedule change is a `fill_`, not a
     new launch configuration) or None for full attention.
     """
-    __slots__ = ("window", "attn_mask", "document_ids")
+    __slots__ = ("window", "attn_mask", "document_ids", "doc_start")
 
     def __init__(self, window: Optional[Tensor], attn_mask: Optional[Tensor], document_ids: Optional[Tensor]):
         self.window, self.attn_mask, self.document_ids = window, attn_mask, document_ids
+        self.doc_start = None           # per-token start of its document, derived from document_ids on first use
 
 
 class SelfAttention(nn.Module):
@@ -111,11 +112,11 @@ class SelfAttention(nn.Module):
 
     def _fused_rope_attention(self, x: Tensor, ctx: AttentionContext) -> Optional[Tensor]:
         """One QKV GEMM, then RoPE + QK-norm + causal / sliding-window attention as a single autograd node (CUDA, 64-wide heads,
-        optional logit soft-capping, no masks or document ids).  Returns None when the shapes or options call for the general path."""
+        optional logit soft-capping and document masking, no padding mask).  Returns None when the shapes or options call for the general path."""
         b, t, _ = x.shape
         d, hq, hk = self.head_size, self.n_heads, self.n_kv_heads
         if not (x.is_cuda and self.q_proj.bias is None and d == 64 and hq + hk <= 64 and hq % hk == 0 and t % 128 == 0
-                and self.is_causal and ctx.attn_mask is None and ctx.document_ids is None):
+                and self.is_causal and ctx.attn_mask is None):
             return None
         from ..ops import cuda_ops
         from ..ops.attention_cuda import _window_int
@@ -124,9 +125,15 @@ class SelfAttention(nn.Module):
         if self.rotary is not None:
             cos, sin = self.rotary.cos_cached[:t], self.rotary.sin_cached[:t]
         window = None if (self.is_full_attention or not self.use_flex_attention) else _window_int(ctx.window)
+        doc_start = None
+        if ctx.document_ids is not None:
+            if getattr(ctx, "doc_start", None) is None:          # computed once per forward pass, shared by all layers
+                from ..ops.attention_tc import document_starts
+                ctx.doc_start = document_starts(ctx.document_ids)
+            doc_start = ctx.doc_start
         return cuda_ops.rope_attention_packed(
             qkv.view(b * t, -1), cos, sin, self.q_scale if self.use_qk_norm else None, self.k_scale if self.use_qk_norm else None,
-            b, t, hq, hk, d, self.qk_eps, self.qk_norm_type == "rms", self.qk_scale_min, self.qk_scale_max, window, None, self.softcap)
+            b, t, hq, hk, d, self.qk_eps, self.qk_norm_type == "rms", self.qk_scale_min, self.qk_scale_max, window, None, self.softcap, doc_start)
 
     def forward(self, x: Tensor, ctx: AttentionContext) -> Tensor:
         b, t, _ = x.shape

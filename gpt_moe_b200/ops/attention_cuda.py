@@ -3,8 +3,8 @@
 `attention()` takes token-major tensors q[B,T,H,Dk], k[B,T,Hkv,Dk], v[B,T,Hkv,Dv] (views into the
 packed projection output are fine: only the last dimension must be contiguous).
 
-Causal / sliding-window attention without padding or document masks (with or without logit
-soft-capping) goes to the tcgen05 kernel in `csrc/attention` when it is built for the head size;
+Causal / sliding-window attention without a padding mask (with or without logit soft-capping and
+document masking) goes to the tcgen05 kernel in `csrc/attention` when it is built for the head size;
 everything else — and any shape the kernel does not cover — runs through the flash-attn library
 kernel or torch's fused SDPA with an explicit boolean mask, which is the slow but general path.
 """
@@ -50,14 +50,13 @@ def attention(q: Tensor, k: Tensor, v: Tensor, *, causal: bool = True, window=No
     w = _window_int(window)
     if w is not None and w >= t - 1 and causal:
         w = None
-    plain = attn_mask is None and document_ids is None
-    if plain and causal:
+    if attn_mask is None and causal:
         from . import attention_tc
         if attention_tc.supported(q, k, v, softcap_value):
-            return attention_tc.attention(q, k, v, window=w, scale=scale, softcap=softcap_value)
+            return attention_tc.attention(q, k, v, window=w, scale=scale, softcap=softcap_value, document_ids=document_ids)
         flash = _flash_attn()
         dv = v.shape[-1]
-        if flash and q.dtype == torch.bfloat16 and dv <= dk and dk <= 256 and softcap_value == 0.0:
+        if document_ids is None and flash and q.dtype == torch.bfloat16 and dv <= dk and dk <= 256 and softcap_value == 0.0:
             # head sizes the tcgen05 kernel is not built for (e.g. MLA: 128-wide keys, 64-wide values) go to the library kernel;
             # it wants equal widths, so narrower values are zero-padded and the padding columns of the result dropped
             vp = v if dv == dk else F.pad(v, (0, dk - dv))

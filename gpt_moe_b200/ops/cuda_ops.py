@@ -416,7 +416,7 @@ class _RopeAttentionFn(torch.autograd.Function):
     directly by the rope backward kernel (no bf16 round trip of dQ), working in place on the packed gradient rows."""
 
     @staticmethod
-    def forward(ctx, qkv: Tensor, cos, sin, q_scale, k_scale, batch, seq_len, hq, hk, d, eps, rms, smin, smax, window, scale, softcap):
+    def forward(ctx, qkv: Tensor, cos, sin, q_scale, k_scale, batch, seq_len, hq, hk, d, eps, rms, smin, smax, window, scale, softcap, doc_start):
         c = ext()
         out = torch.empty_like(qkv)
         qs = None if q_scale is None else q_scale.detach().float().reshape(-1).contiguous()
@@ -426,7 +426,8 @@ class _RopeAttentionFn(torch.autograd.Function):
         q = packed[..., : hq * d].unflatten(-1, (hq, d))
         k = packed[..., hq * d: (hq + hk) * d].unflatten(-1, (hk, d))
         v = packed[..., (hq + hk) * d:].unflatten(-1, (hk, d))
-        o, lse = c.attn_fwd(q, k, v, window, scale, softcap)
+        o, lse = c.attn_fwd(q, k, v, window, scale, softcap, doc_start)
+        ctx.doc_start = doc_start
         empty = qkv.new_empty(0)
         ctx.save_for_backward(qkv, out, o, lse, cos if cos is not None else empty, sin if sin is not None else empty,
                               qs if qs is not None else empty, ks if ks is not None else empty)
@@ -448,7 +449,7 @@ class _RopeAttentionFn(torch.autograd.Function):
         grad = torch.empty_like(packed)                               # dq columns are produced by the rope backward from the fp32 dQ
         dk = grad[..., hq * d: (hq + hk) * d].unflatten(-1, (hk, d))
         dv = grad[..., (hq + hk) * d:].unflatten(-1, (hk, d))
-        dq32 = c.attn_bwd(q, k, v, o, d_out, lse, dk, dv, window, scale, softcap)
+        dq32 = c.attn_bwd(q, k, v, o, d_out, lse, dk, dv, window, scale, softcap, ctx.doc_start)
         g2 = grad.view(batch * seq_len, -1)
         dscale = c.rope_qknorm_bwd(qkv, g2, g2, cos if has_rope else None, sin if has_rope else None, qs if has_norm else None,
                                    ks if has_norm else None, seq_len, hq, hk, d, eps, rms, smin, smax, dq32.view(batch * seq_len, -1))
@@ -456,17 +457,18 @@ class _RopeAttentionFn(torch.autograd.Function):
         if has_norm:
             (qshape, qdt), (kshape, kdt) = ctx.scale_shapes
             dqs, dks = dscale[:hq].reshape(qshape).to(qdt), dscale[hq:].reshape(kshape).to(kdt)
-        return (g2, None, None, dqs, dks) + (None,) * 12
+        return (g2, None, None, dqs, dks) + (None,) * 13
 
 
 def rope_attention_packed(qkv: Tensor, cos, sin, q_scale, k_scale, batch: int, seq_len: int, hq: int, hk: int, d: int, eps: float,
-                          rms: bool, smin: float, smax: float, window: Optional[int], scale: Optional[float], softcap: float = 0.0) -> Tensor:
+                          rms: bool, smin: float, smax: float, window: Optional[int], scale: Optional[float], softcap: float = 0.0,
+                          doc_start: Optional[Tensor] = None) -> Tensor:
     """qkv [batch * seq_len, (hq + 2 hk) * 64] bf16 -> attention output [batch, seq_len, hq, 64]."""
     smin = max(smin, -3.0e38)
     smax = min(smax, 3.0e38)
     w = seq_len if window is None else int(window)
     return _RopeAttentionFn.apply(qkv, cos, sin, q_scale, k_scale, batch, seq_len, hq, hk, d, eps, rms, smin, smax, w,
-                                  d ** -0.5 if scale is None else float(scale), float(softcap))
+                                  d ** -0.5 if scale is None else float(scale), float(softcap), doc_start)
 
 
 def rope_qk_norm(q, k, cos, sin, q_scale, k_scale, eps, rms, scale_min, scale_max):

@@ -349,3 +349,28 @@ def test_attention_kernels_with_logit_softcapping(ops, dqk, window):
     assert rel(out, want) < 1.5e-2
     for name, got, exp in (("dq", q.grad, rq.grad), ("dk", k.grad, rk.grad), ("dv", v.grad, rv.grad)):
         assert rel(got, exp) < 3e-2, name
+
+
+@pytest.mark.parametrize("dqk,window", [(64, 300), (64, 5000), (128, 5000)])
+def test_attention_kernels_with_document_masking(ops, dqk, window):
+    """Queries see only keys of their own document (documents = contiguous runs), combined with the causal window."""
+    from gpt_moe_b200.ops import attention_tc
+    torch.manual_seed(14)
+    b, t, hq, hk = 2, 640, 2, 1
+    q = torch.randn(b, t, hq, dqk, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(b, t, hk, dqk, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(b, t, hk, 64, device="cuda").bfloat16().requires_grad_()
+    ends = torch.zeros(b, t, dtype=torch.long, device="cuda")
+    for row, cuts in enumerate(([5, 130, 131, 400], [127, 128, 500, 639])):      # documents of very different lengths, cuts at tile edges too
+        ends[row, cuts] = 1
+    docs = ends.cumsum(dim=1) - ends                                               # the end-of-sequence token belongs to its document
+    assert attention_tc.document_starts(docs)[0, 131].item() == 131 and attention_tc.document_starts(docs)[0, 399].item() == 132
+    out = attention_tc.attention(q, k, v, window=window, scale=None, document_ids=docs)
+    g = torch.randn_like(out)
+    out.backward(g)
+    rq, rk, rv = (x.detach().float().requires_grad_() for x in (q, k, v))
+    want = ref.attention(rq, rk, rv, causal=True, window=window, document_ids=docs)
+    want.backward(g.float())
+    assert rel(out, want) < 1e-2
+    for name, got, exp in (("dq", q.grad, rq.grad), ("dk", k.grad, rk.grad), ("dv", v.grad, rv.grad)):
+        assert rel(got, exp) < 2e-2, name
