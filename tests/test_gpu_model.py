@@ -205,3 +205,30 @@ def test_activation_memory_options_train_on_gpu(option):
     batch = [(ids[:, :-1].contiguous(), ids[:, 1:].contiguous(), None)]
     losses = [trainer.train_step(batch)["loss"] for _ in range(6)]
     assert losses[-1] < losses[0] - 0.3, losses
+
+
+def test_document_masking_and_softcapping_model_against_cpu():
+    """The attention options that ride inside the tcgen05 kernels (document masking, logit soft-capping) give the CPU oracle's loss."""
+    from gpt_moe_b200.models.gpt import GPT
+    torch.manual_seed(2)
+    gc, tc = _tiny()
+    gc.use_doc_masking, gc.use_attn_logit_softcapping, gc.attn_logit_softcap, gc.tanh_backend = True, True, 15.0, "exact"
+    cpu = GPT(gc, tc)
+    with torch.no_grad():
+        for block in cpu.transformer.h:
+            block.mlp.router.weight.mul_(40.0)
+    gpu = copy.deepcopy(cpu).cuda()
+    cpu.set_sliding_window(128); gpu.set_sliding_window(128)
+    ids = torch.randint(0, gc.vocab_size, (2, 257))
+    x, y = ids[:, :-1], ids[:, 1:]
+    ends = torch.zeros(2, 256, dtype=torch.long)
+    ends[0, [40, 127, 200]] = 1
+    ends[1, [128, 129]] = 1
+    docs = ends.cumsum(dim=1) - ends
+    loss_g = gpu(x.cuda(), y.cuda(), document_ids=docs.cuda())[0]
+    loss_g.backward()
+    loss_c = cpu(x, y, document_ids=docs)[0]
+    loss_plain = cpu(x, y)[0]
+    assert abs(loss_c.item() - loss_g.item()) < 3e-2
+    assert all(torch.isfinite(p.grad).all() for p in gpu.parameters() if p.grad is not None)
+    assert loss_plain.item() != loss_c.item()
