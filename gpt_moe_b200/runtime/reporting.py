@@ -48,14 +48,18 @@ def log_source_code(log_buffer: List[str], include_sources: bool = True) -> None
     if not include_sources:
         return
     for folder, _, files in os.walk(root):
-        if any(part.startswith((".", "_")) and part not in (".",) for part in os.path.relpath(folder, root).split(os.sep)) \
-                or "gpurun_out" in folder or "baseline/_ref" in folder:
+        parts = os.path.relpath(folder, root).split(os.sep)
+        # hidden / private folders, run outputs and vendored trees are not part of the program being logged
+        if any((part.startswith((".", "_")) and part != ".") or part.endswith("_out") for part in parts) or parts[0] in SKIPPED_TOP_LEVEL:
             continue
         for name in sorted(files):
             if name.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
                 path = os.path.join(folder, name)
                 with open(path, errors="replace") as f:
                     log_buffer.append(f"{'=' * 20} {os.path.relpath(path, root)} {'=' * 20}\n{f.read()}")
+
+
+SKIPPED_TOP_LEVEL = ("baseline", "configs_and_logs", "checkpoints", "model_exports", "profiles")
 
 
 def save_config_info(run, training_config, gpt_config) -> None:
