@@ -250,7 +250,8 @@ class Trainer:
         accum = cfg.grad_accum_mini_steps
         if self.watchdog is not None:
             self.watchdog.arm()
-        model.train()
+        if not model.training:                # walking ~1300 modules every step costs milliseconds of host time
+            model.train()
         raw.set_precision_phase("training")
         self.engine.zero_grad()
         if accum > 1:
@@ -299,15 +300,22 @@ class Trainer:
             self.next_swa_update_tokens = get_next_update_tokens(cfg.swa_schedule_keys, self.swa_schedule_idx, cfg.max_tokens)
         raw.set_sliding_window(self.current_window_size)
         raw.clear_fp8_weights()
+        loss_ready = None
+        if read_losses and self.device_type == "cuda":
+            # the losses are final once the backward pass is issued: their copy to pinned host memory is queued BEFORE the
+            # optimizer kernels, so the host gets the numbers (and starts issuing the next step) while the optimizer still runs
+            if self._loss_host is None:
+                self._loss_host = torch.empty(3, dtype=torch.float32, pin_memory=True)
+            self._loss_host.copy_(train_losses, non_blocking=True)
+            loss_ready = torch.cuda.Event()
+            loss_ready.record()
         with self._nvtx("optimizer_step"):
             self.engine.step()
 
         out = {"adamw_lr": adamw_lr, "tokens": bs * cfg.seq_len_train * self.effective_world_size * accum}
         if read_losses:
-            if self.device_type == "cuda":
-                if self._loss_host is None:
-                    self._loss_host = torch.empty(3, dtype=torch.float32, pin_memory=True)
-                self._loss_host.copy_(train_losses, non_blocking=False)
+            if loss_ready is not None:
+                loss_ready.synchronize()
                 vals = self._loss_host.tolist()
             else:
                 vals = train_losses.tolist()
