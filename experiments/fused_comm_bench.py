@@ -101,7 +101,7 @@ def bench_rs_ag(args, results):
             c.muon_apply_push(mp, lp, packed, rows, cols, cols, cols, -0.01, False, [0])
             dist.all_gather_into_tensor(gathered, local_bf16)
 
-        link_rs = numel * 4 * (world - 1) / world / world            # bytes this GPU pulls from peers: its shard from every other rank
+        link_rs = numel * 4 / world * (world - 1)                    # bytes this GPU pulls from peers: its shard (1/world of the bucket) from every other rank
         link_ag = mine * per_mat * 2 * (world - 1)                   # bytes this GPU pushes: its shard to every other rank
         for name, fused, nccl, link in (("rs", rs_fused, rs_nccl, link_rs), ("ag", ag_fused, ag_nccl, link_ag)):
             if args.part not in (name, "all"):
