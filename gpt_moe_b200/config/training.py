@@ -198,6 +198,7 @@ class TrainingConfig:
     grad_reduce_dtype: str = "bf16"   # wire dtype of the gradient reduce-scatter ("bf16" | "fp32")
     grad_bucket_mb: int = 64          # flat gradient bucket size
     use_fused_collectives: bool = True  # peer-memory kernels; False = NCCL calls (the measured baseline)
+    use_cuda_graphs: bool = True        # fused engine: forward+backward of a training step is captured once per (shape, window) and replayed
     nvtx_ranges: bool = False           # NVTX ranges around the phases of a training step (forward+backward per micro-step, optimizer)
     overlap_grad_reduce: bool = False   # fused engine: a block's Muon reduce / update / push runs beside the backward of earlier blocks
                                         # (measured slightly slower at 2 GPUs, where the per-block batches are small: 67.9 vs 66.3 ms/step)

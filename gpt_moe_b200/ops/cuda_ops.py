@@ -63,6 +63,11 @@ def launch_count() -> int:
     return ext().calls
 
 
+def add_launches(count: int) -> None:
+    """Account for kernels that ran without a Python call (a replayed CUDA graph): `count` = bindings recorded at capture."""
+    ext().calls += int(count)
+
+
 def check_status() -> None:
     code = ext().read_status()
     if code != 0:

@@ -176,6 +176,9 @@ class FusedEngine:
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.overlap else None
         self.step_counter = 0
         self._early_layers: set = set()
+        # ---- CUDA graphs: forward + backward of one micro-step, captured per (input shape, window, loss scale) ----------------
+        self.use_graphs = bool(getattr(training_config, "use_cuda_graphs", True) and self.device.type == "cuda")
+        self._graphs: Dict[tuple, dict] = {}
         self._barrier()
 
     # ---- layout helpers ---------------------------------------------------------------------------------------------------
@@ -248,9 +251,57 @@ class FusedEngine:
             p.grad_ready = False
             p.grad = None
 
+    def _graph_eligible(self, model, x, document_ids) -> bool:
+        """Graph replay needs a step whose launches do not depend on host-side state: one micro-step per step (the
+        first-write / accumulate choice of the weight-gradient GEMMs is then fixed), no expert-parallel exchange (its barriers
+        and peer stores stay eager), no document ids, the plain chain of blocks (no activation checkpointing or offloading)."""
+        raw = self.model
+        return (self.use_graphs and x.is_cuda and document_ids is None and self.cfg.grad_accum_mini_steps == 1 and self.ep_size == 1
+                and not self.overlap and raw.training and torch.is_grad_enabled()
+                and not getattr(raw, "use_activation_checkpointing", False) and getattr(raw, "activation_offloader", None) is None)
+
+    def _graphed_forward_backward(self, model, x, y, loss_scale: float):
+        """Third and later calls with the same key replay a captured graph of forward + backward (inputs are copied into the
+        graph's static tensors; losses come back in static tensors); the first two run eagerly (they also warm every cache)."""
+        from ..ops import cuda_ops
+        window = getattr(getattr(self.model, "sliding_window_size", None), "host_value", None)
+        key = (tuple(x.shape), tuple(y.shape), window, float(loss_scale), x.dtype)
+        entry = self._graphs.setdefault(key, {"calls": 0})
+        entry["calls"] += 1
+        if "graph" not in entry:
+            if entry["calls"] <= 2:
+                return None
+            torch.cuda.synchronize()
+            sx, sy = x.clone(), y.clone()
+            graph = torch.cuda.CUDAGraph()
+            before = cuda_ops.launch_count()
+            try:
+                with torch.cuda.graph(graph):
+                    loss, token_loss, balance = model(sx, sy, document_ids=None)
+                    (loss * loss_scale).backward()
+            except Exception as exc:              # capture refused (an op that cannot be captured): stay eager from now on
+                self.use_graphs = False
+                self._graphs.clear()
+                torch.cuda.synchronize()
+                print(f"CUDA graph capture of the training step failed ({type(exc).__name__}: {exc}); continuing without graphs")
+                return None
+            entry.update(graph=graph, x=sx, y=sy, outs=(loss.detach(), token_loss.detach(), balance.detach()),
+                         launches=cuda_ops.launch_count() - before)
+            # the capture only recorded the launches: the replay below is what computes this step
+        else:
+            entry["x"].copy_(x, non_blocking=True)
+            entry["y"].copy_(y, non_blocking=True)
+        entry["graph"].replay()
+        cuda_ops.add_launches(entry["launches"])
+        return entry["outs"]
+
     def forward_backward(self, model, x, y, document_ids, loss_scale: float, last_micro_step: bool):
         from ..ops import cuda_ops
         cuda_ops.set_loss_scale(loss_scale)
+        if self._graph_eligible(model, x, document_ids):
+            outs = self._graphed_forward_backward(model, x, y, loss_scale)
+            if outs is not None:
+                return outs
         early = self.overlap and last_micro_step and self.optimizers.get("muon") is not None
         if early:
             self.step_counter += 1
