@@ -287,6 +287,11 @@ class FusedEngine:
                 return None
             entry.update(graph=graph, x=sx, y=sy, outs=(loss.detach(), token_loss.detach(), balance.detach()),
                          launches=cuda_ops.launch_count() - before)
+            # a captured step keeps its activations alive in the graph's memory pool: when a schedule moves on (new window,
+            # new batch size) only the two most recent graphs are kept
+            captured = [k for k, e in self._graphs.items() if "graph" in e]
+            for stale in captured[:-2]:
+                del self._graphs[stale]
             # the capture only recorded the launches: the replay below is what computes this step
         else:
             entry["x"].copy_(x, non_blocking=True)

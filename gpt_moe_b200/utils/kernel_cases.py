@@ -25,7 +25,7 @@ def _timed(fn, iters):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_mxfp8", "quantize", "gemm_wgrad", "grouped", "attn_fwd", "attn_bwd", "rs_muon", "ce", "rmsnorm", "rope", "rope_bwd", "ep_dispatch", "ep_combine", "rmsnorm_bwd"])
+    ap.add_argument("case", choices=["gemm", "gemm_mxfp8", "quantize", "gemm_wgrad", "grouped", "attn_fwd", "attn_bwd", "rs_muon", "ce", "rmsnorm", "rope", "rope_bwd", "ep_dispatch", "ep_combine", "rmsnorm_bwd", "attn_fwd_mla", "attn_bwd_mla"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     from gpt_moe_b200.ops import attention_tc, cuda_ops
@@ -75,6 +75,20 @@ def main() -> None:
             g = torch.randn_like(out)
             fn = lambda: torch.autograd.grad(out, packed, g, retain_graph=True)
             flops = 10 * d * keys * b_ * h
+    elif args.case in ("attn_fwd_mla", "attn_bwd_mla"):   # multi-head latent attention shape: 128-wide query/key heads, 64-wide values, causal 4096
+        b_, t, h = 2, 4096, 16
+        q = torch.randn(b_, t, h, 128, device=dev).mul_(0.5).bfloat16().requires_grad_()
+        k = torch.randn(b_, t, h, 128, device=dev).mul_(0.5).bfloat16().requires_grad_()
+        v = torch.randn(b_, t, h, 64, device=dev).bfloat16().requires_grad_()
+        pairs = t * (t + 1) // 2 * b_ * h
+        if args.case == "attn_fwd_mla":
+            fn = lambda: c.attn_fwd(q.detach(), k.detach(), v.detach(), t, 128 ** -0.5)
+            flops = 2 * (128 + 64) * pairs
+        else:
+            out = attention_tc.attention(q, k, v, window=None, scale=None)
+            g = torch.randn_like(out)
+            fn = lambda: torch.autograd.grad(out, (q, k, v), g, retain_graph=True)
+            flops = 2 * (128 + 64 + 64 + 128 + 128) * pairs
     elif args.case == "rs_muon":                 # reduce + momentum + pack for 16 matrices of 6144 x 768 (world of one)
         grads = [torch.randn(6144, 768, device=dev) for _ in range(16)]
         bufs = [torch.zeros(6144, 768, device=dev) for _ in range(16)]
