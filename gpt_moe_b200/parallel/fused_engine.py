@@ -283,7 +283,9 @@ class FusedEngine:
                 self.use_graphs = False
                 self._graphs.clear()
                 torch.cuda.synchronize()
-                print(f"CUDA graph capture of the training step failed ({type(exc).__name__}: {exc}); continuing without graphs")
+                import sys
+                print(f"CUDA graph capture of the training step failed ({type(exc).__name__}: {exc}); continuing without graphs",
+                      file=sys.stderr)
                 return None
             entry.update(graph=graph, x=sx, y=sy, outs=(loss.detach(), token_loss.detach(), balance.detach()),
                          launches=cuda_ops.launch_count() - before)
@@ -498,5 +500,6 @@ def build_cuda_engine(model, training_config, optimizers, ep_size: int = 1, ep_g
             return FusedEngine(model, training_config, optimizers, dp_group=None, ep_size=ep_size, ep_group=ep_group)
         except Exception as exc:  # symmetric memory unavailable on this machine
             if du.get_rank() == 0:
-                print(f"fused engine unavailable ({type(exc).__name__}: {exc}); using NCCL collectives")
+                import sys
+                print(f"fused engine unavailable ({type(exc).__name__}: {exc}); using NCCL collectives", file=sys.stderr)
     return CudaHostEngine(model, training_config, optimizers, dp_group=None, ep_size=ep_size)
