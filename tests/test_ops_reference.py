@@ -127,3 +127,20 @@ def test_moe_experts_matches_dense_evaluation():
     assert torch.allclose(g1[:, 0], p1.max(-1).values)       # top-1 gate = full-softmax probability, not 1.0
     loss = ref.load_balance_loss(torch.full((m, e), 1 / e), torch.arange(m)[:, None] % e, e)
     assert abs(loss.item() - 1.0) < 0.05                     # perfectly balanced routing gives 1
+
+
+def test_document_starts_reproduce_the_document_mask():
+    """The GPU kernels fold document masking into a per-row look-back bound; that bound must describe the same mask as
+    comparing document ids pairwise (documents are contiguous runs of tokens)."""
+    from gpt_moe_b200.ops.attention_tc import document_starts
+    torch.manual_seed(0)
+    b, t, window = 3, 97, 20
+    ends = (torch.rand(b, t) < 0.08).long()
+    docs = ends.cumsum(dim=1) - ends
+    starts = document_starts(docs)
+    keep = ref.attention_mask(t, "cpu", True, window, None, docs)                  # [B, 1, T, T] or broadcastable
+    q = torch.arange(t)[None, :, None]
+    k = torch.arange(t)[None, None, :]
+    lo = torch.maximum(q - window, starts[:, :, None].long())
+    want = (k <= q) & (k >= lo)
+    assert torch.equal(keep.reshape(b, t, t) if keep.dim() == 4 else keep.expand(b, t, t), want)
