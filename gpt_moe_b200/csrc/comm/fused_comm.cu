@@ -26,6 +26,21 @@ __device__ __forceinline__ float4 ld_peer4(const float* p, long long delta) {
     return *reinterpret_cast<const float4*>(reinterpret_cast<const char*>(p) + delta);
 }
 
+// Sum of the same float4 on every rank, added in rank order.  The loads of up to eight ranks are issued before any of them
+// is consumed, so a thread keeps eight NVLink requests in flight instead of one.
+__device__ __forceinline__ float4 sum_peers4(const float* p, const PeerDeltas& peers, int world) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int base = 0; base < world; base += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            t[k] = (base + k < world) ? ld_peer4(p, peers.d[base + k]) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { s.x += t[k].x; s.y += t[k].y; s.z += t[k].z; s.w += t[k].w; }
+    }
+    return s;
+}
+
 // tile: 32 rows x 128 columns, 256 threads; thread (tx, ty) owns columns 4*tx..4*tx+3 of rows ty, ty+8, ty+16, ty+24
 __global__ void __launch_bounds__(256)
 rs_muon_prepare_kernel(const float* const* __restrict__ grads, float* const* __restrict__ bufs, __nv_bfloat16* __restrict__ packed,
@@ -46,11 +61,7 @@ rs_muon_prepare_kernel(const float* const* __restrict__ grads, float* const* __r
         float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
         if (r < rows && c < cols) {
             const float* gp = g + r * g_stride + c;
-            float4 s = ld_peer4(gp, peers.d[0]);
-            for (int k = 1; k < world; ++k) {
-                const float4 t = ld_peer4(gp, peers.d[k]);
-                s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
-            }
+            float4 s = sum_peers4(gp, peers, world);
             s.x *= inv_world; s.y *= inv_world; s.z *= inv_world; s.w *= inv_world;
             float4 b = *reinterpret_cast<const float4*>(buf + r * b_stride + c);
             b.x = b.x * momentum + s.x; b.y = b.y * momentum + s.y; b.z = b.z * momentum + s.z; b.w = b.w * momentum + s.w;
@@ -157,11 +168,7 @@ adamw_sharded_kernel(float* __restrict__ params, const float* __restrict__ grads
                      float bc1, float bc2_sqrt, PeerDeltas gpeers, PeerDeltas ppeers, int world, float inv_world) {
     for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 4; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
         const float* gp = grads + lo + i;
-        float4 g = ld_peer4(gp, gpeers.d[0]);
-        for (int k = 1; k < world; ++k) {
-            const float4 t = ld_peer4(gp, gpeers.d[k]);
-            g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
-        }
+        const float4 g = sum_peers4(gp, gpeers, world);
         const float gg[4] = {g.x * inv_world, g.y * inv_world, g.z * inv_world, g.w * inv_world};
         float4 pw = *reinterpret_cast<const float4*>(params + lo + i);
         float pp[4] = {pw.x, pw.y, pw.z, pw.w};

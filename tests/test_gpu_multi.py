@@ -16,3 +16,21 @@ def test_fused_engine_matches_nccl_engine_on_two_gpus():
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
                           "--master-port", "29611", worker], capture_output=True, text=True, timeout=900, env=env)
     assert "MULTI_GPU_ENGINE_OK" in out.stdout, out.stdout[-3000:] + out.stderr[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_stage_pipeline_trains_on_two_gpus():
+    """`parallel_mode="pp"`: two stages, 1F1B over NCCL send/recv, the CUDA kernels on both stages; the loss must fall."""
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29613", os.path.join(root, "train.py"), "--preset", "small", "--steps", "8",
+           "--set", "training.parallel_mode=pp", "--set", "model.n_layers=4", "--set", "model.hidden_size=256", "--set", "model.attn_dim=256",
+           "--set", "model.n_heads=4", "--set", "model.n_kv_heads=4", "--set", "model.mlp_hidden_dim=256", "--set", "model.num_experts=4",
+           "--set", "training.total_tokens_per_step_train=65536",          # two micro-batches of 16 x 2048 tokens per step
+           "--set", "training.kernel_warmup_train_steps=0"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=root)
+    losses = [float(m) for m in re.findall(r"train loss: ([0-9.]+)", out.stdout)]
+    assert len(losses) >= 8, out.stdout[-3000:] + out.stderr[-3000:]
+    assert losses[-1] < losses[0] - 0.5, losses
