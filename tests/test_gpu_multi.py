@@ -20,7 +20,9 @@ def test_fused_engine_matches_nccl_engine_on_two_gpus():
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_stage_pipeline_trains_on_two_gpus():
-    """`parallel_mode="pp"`: two stages, 1F1B over NCCL send/recv, the CUDA kernels on both stages; the loss must fall."""
+    """`parallel_mode="pp"`: two stages, 1F1B over NCCL send/recv, the CUDA kernels on both stages.  The synthetic tokens are
+    uniform over the vocabulary, so the loss can only hover around ln(vocab) = 10.83; equivalence with the single-process run
+    is checked on the CPU (`tests/test_distributed_cpu.py`), here every step must complete with a finite, sane loss."""
     import re
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
@@ -33,4 +35,5 @@ def test_two_stage_pipeline_trains_on_two_gpus():
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=root)
     losses = [float(m) for m in re.findall(r"train loss: ([0-9.]+)", out.stdout)]
     assert len(losses) >= 8, out.stdout[-3000:] + out.stderr[-3000:]
-    assert losses[-1] < losses[0] - 0.5, losses
+    assert all(10.0 < v < 11.5 for v in losses), losses
+    assert "val loss" in out.stdout                      # the forward-only path across stages ran too
