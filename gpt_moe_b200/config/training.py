@@ -195,7 +195,7 @@ class TrainingConfig:
     # ---- new capabilities ---------------------------------------------------------------------
     expert_parallel_size: int = 1     # experts are sharded over this many ranks (must divide world size and num_experts)
     shard_muon: bool = True           # each rank orthogonalises only the matrices it owns, then all-gathers
-    grad_reduce_dtype: str = "bf16"   # wire dtype of the gradient reduce-scatter ("bf16" | "fp32")
+    grad_reduce_dtype: str = "fp32"   # wire dtype of the gradient reduction; only "fp32" (the reference's DDP precision) is implemented
     grad_bucket_mb: int = 64          # flat gradient bucket size
     use_fused_collectives: bool = True  # peer-memory kernels; False = NCCL calls (the measured baseline)
     use_cuda_graphs: bool = True        # fused engine: forward+backward of a training step is captured once per (shape, window) and replayed

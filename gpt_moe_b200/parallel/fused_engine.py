@@ -99,6 +99,8 @@ class FusedEngine:
         self.world, self.rank = du.world_size(dp_group), du.get_rank(dp_group)
         self.ep_size, self.ep_group = ep_size, ep_group
         self.device = next(model.parameters()).device
+        if getattr(training_config, "grad_reduce_dtype", "fp32") != "fp32":
+            raise NotImplementedError("gradients are reduced in fp32 (grad_reduce_dtype must be 'fp32')")
         groups = model.optimizer_param_groups()
         named = dict(model.named_parameters())
         muon_names = [n for n, _ in groups["muon"]]
