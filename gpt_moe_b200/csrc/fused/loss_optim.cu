@@ -79,8 +79,108 @@ ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restric
         p[i] = __float2bfloat16((__expf(__bfloat162float(p[i]) - lse) - (i == tgt ? 1.f : 0.f)) * scale);
 }
 
+// Same computation for rows that fit in registers (vocab <= 512 * CE_MAXV * 8 and a multiple of 8): every thread keeps its
+// CE_MAXV 16-byte pieces of the row, so the row is read from memory once, the maximum is found without exponentials, and
+// the two exponentials per element (sum, gradient) carry no data-dependent branch.
+constexpr int CE_MAXV = 13;
+
+__global__ void __launch_bounds__(512)
+ce_fwd_bwd_reg_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets, float* __restrict__ loss,
+                      const float* __restrict__ grad_scale, int vocab, long long row_stride, long long ignore_index, int write_grad) {
+    __shared__ float red[16];
+    __shared__ float bcast;
+    const long long row = blockIdx.x;
+    uint4* p = reinterpret_cast<uint4*>(logits + row * row_stride);
+    const long long tgt = targets[row];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int vec = vocab / 8;
+    if (tgt == ignore_index) {
+        if (threadIdx.x == 0) loss[row] = 0.f;
+        if (write_grad)
+            for (int i = threadIdx.x; i < vec; i += 512) p[i] = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    uint4 raw[CE_MAXV];
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < CE_MAXV; ++j) {
+        const int i = threadIdx.x + j * 512;
+        raw[j] = make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);          // bf16 -inf pairs: neutral for max and sum
+        if (i < vec) raw[j] = p[i];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); m = fmaxf(m, fmaxf(f.x, f.y)); }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = red[0];
+#pragma unroll
+        for (int w = 1; w < 16; ++w) t = fmaxf(t, red[w]);
+        bcast = t;
+    }
+    __syncthreads();
+    const float gmax = bcast;
+    float s = 0.f;
+    constexpr float LOG2E = 1.4426950408889634f;
+    const float mb = gmax * LOG2E;
+#pragma unroll
+    for (int j = 0; j < CE_MAXV; ++j) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            s += exp2f(fmaf(f.x, LOG2E, -mb)) + exp2f(fmaf(f.y, LOG2E, -mb));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    __syncthreads();                                      // red / bcast are reused
+    if (lane == 0) red[warp] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 16; ++w) t += red[w];
+        bcast = t;
+    }
+    __syncthreads();
+    const float lse = gmax + __logf(bcast);
+    if (threadIdx.x == 0) loss[row] = lse - __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[tgt]);
+    if (!write_grad) return;
+    __syncthreads();                                      // the target logit has been read before the row is overwritten
+    const float scale = *grad_scale;
+    const float lb = lse * LOG2E;
+    const int tvec = static_cast<int>(tgt >> 3), tsub = static_cast<int>(tgt & 7);
+#pragma unroll
+    for (int j = 0; j < CE_MAXV; ++j) {
+        const int i = threadIdx.x + j * 512;
+        if (i >= vec) continue;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+        float g[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            g[2 * e] = exp2f(fmaf(f.x, LOG2E, -lb));
+            g[2 * e + 1] = exp2f(fmaf(f.y, LOG2E, -lb));
+        }
+        if (i == tvec) g[tsub] -= 1.f;
+        uint4 o;
+        o.x = pack_bf16x2(g[0] * scale, g[1] * scale); o.y = pack_bf16x2(g[2] * scale, g[3] * scale);
+        o.z = pack_bf16x2(g[4] * scale, g[5] * scale); o.w = pack_bf16x2(g[6] * scale, g[7] * scale);
+        p[i] = o;
+    }
+}
+
 void launch_ce_fwd_bwd(void* logits, const long long* targets, float* loss, const float* grad_scale, int rows, int vocab,
                        long long row_stride, long long ignore_index, int write_grad, cudaStream_t s) {
+    if (vocab % 8 == 0 && vocab / 8 <= 512 * CE_MAXV && row_stride % 8 == 0) {
+        ce_fwd_bwd_reg_kernel<<<rows, 512, 0, s>>>(static_cast<__nv_bfloat16*>(logits), targets, loss, grad_scale, vocab, row_stride,
+                                                   ignore_index, write_grad);
+        return;
+    }
     ce_fwd_bwd_kernel<<<rows, 512, 0, s>>>(static_cast<__nv_bfloat16*>(logits), targets, loss, grad_scale, vocab, row_stride,
                                            ignore_index, write_grad);
 }
