@@ -91,7 +91,8 @@ const CUtensorMap& operand_map(const torch::Tensor& t, bool mn_major, int tile_r
 void gemm_bf16(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& d, bool a_mn, bool b_mn, double alpha,
                double beta, const c10::optional<torch::Tensor>& c, bool accumulate, int64_t mode,
                const c10::optional<torch::Tensor>& tile_expert, const c10::optional<torch::Tensor>& num_m_tiles,
-               const c10::optional<torch::Tensor>& seg_ends) {
+               const c10::optional<torch::Tensor>& seg_ends, bool symmetric, const c10::optional<torch::Tensor>& batch_sumsq,
+               int64_t scale_mode) {
     c10::cuda::CUDAGuard guard(a.device());
     gm::GemmParams p;
     std::memset(&p, 0, sizeof(p));
@@ -135,6 +136,17 @@ void gemm_bf16(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& d,
         p.c_batch_stride = c->dim() == 3 ? c->stride(0) : 0;
     }
     GM_CHECK(p.ldd % 8 == 0 && (p.C == nullptr || p.ldc % 8 == 0), "output row pitch must be a multiple of 8 elements");
+    if (symmetric) {      // the caller vouches that alpha * A B^T + beta * C is symmetric; only the upper triangle of tiles is computed
+        GM_CHECK(mode == gm::GEMM_DENSE && p.M == p.N && !p.out_fp32 && !accumulate, "symmetric GEMM: dense, square, bf16 output");
+        p.symmetric = 1;
+    }
+    if (batch_sumsq.has_value()) {
+        GM_CHECK(mode == gm::GEMM_DENSE && batch_sumsq->is_cuda() && batch_sumsq->scalar_type() == torch::kFloat32 &&
+                 batch_sumsq->is_contiguous() && batch_sumsq->numel() == p.batch && (scale_mode == 1 || scale_mode == 2),
+                 "batch_sumsq: one fp32 value per batched problem of a dense GEMM, scale_mode 1 or 2");
+        p.batch_sumsq = batch_sumsq->data_ptr<float>();
+        p.scale_mode = static_cast<int>(scale_mode);
+    }
     p.status = status_tensor(a.device().index()).data_ptr<int>();
     // split-K: a long contraction with too few output tiles to fill the GPU (weight gradients) is shared by several CTAs per tile
     p.split_k = 1;
@@ -314,7 +326,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("a_mn") = false, py::arg("b_mn") = false,
           py::arg("alpha") = 1.0, py::arg("beta") = 0.0, py::arg("c") = py::none(), py::arg("accumulate") = false,
           py::arg("mode") = 0, py::arg("tile_expert") = py::none(), py::arg("num_m_tiles") = py::none(),
-          py::arg("seg_ends") = py::none());
+          py::arg("seg_ends") = py::none(), py::arg("symmetric") = false,
+          py::arg("batch_sumsq") = py::none(), py::arg("scale_mode") = 0);
     m.def("mxfp8_quantize", &mxfp8_quantize, py::arg("x"), py::arg("rows_limit") = py::none());
     m.def("mxfp8_quantize_transposed", &mxfp8_quantize_transposed);
     m.def("gemm_mxfp8", &gemm_mxfp8, py::arg("a"), py::arg("sfa"), py::arg("b"), py::arg("sfb"), py::arg("d"), py::arg("alpha") = 1.0,

@@ -257,7 +257,7 @@ std::vector<long long> to_deltas(const std::vector<int64_t>& deltas) { return st
 // grad_ptrs point into THIS rank's symmetric gradient buffer; peer_deltas[r] = (rank r's buffer base) - (this rank's base).
 void rs_muon_prepare(const Tensor& grad_ptrs, const Tensor& buf_ptrs, Tensor& packed, Tensor& sumsq, int64_t rows, int64_t cols,
                      int64_t g_stride, int64_t b_stride, double momentum, bool nesterov, bool transpose,
-                     const std::vector<int64_t>& peer_deltas) {
+                     const std::vector<int64_t>& peer_deltas, bool normalize) {
     c10::cuda::CUDAGuard guard(packed.device());
     check_bf16(packed, "packed");
     const int n = grad_ptrs.numel();
@@ -267,7 +267,8 @@ void rs_muon_prepare(const Tensor& grad_ptrs, const Tensor& buf_ptrs, Tensor& pa
                                     reinterpret_cast<float* const*>(buf_ptrs.data_ptr<int64_t>()), packed.data_ptr(), sumsq.data_ptr<float>(), n,
                                     rows, cols, g_stride, b_stride, momentum, nesterov, transpose, d.data(), d.size(), stream()),
              "rs_muon_prepare: at most 16 ranks, column count a multiple of 4");
-    launch_muon_normalize(packed.data_ptr(), sumsq.data_ptr<float>(), n, rows * cols, stream());
+    // normalize = false leaves `packed` as it is: the caller hands `sumsq` to the first GEMMs of the orthogonalisation instead
+    if (normalize) launch_muon_normalize(packed.data_ptr(), sumsq.data_ptr<float>(), n, rows * cols, stream());
 }
 
 // W_master += alpha * O on the owner; the refreshed bf16 copy is stored into every rank's weight buffer.
@@ -421,7 +422,9 @@ void register_kernels(pybind11::module_& m) {
     m.def("muon_prepare", &muon_prepare);
     m.def("muon_apply", &muon_apply);
     m.def("cast_bf16", &cast_bf16);
-    m.def("rs_muon_prepare", &rs_muon_prepare);
+    m.def("rs_muon_prepare", &rs_muon_prepare, py::arg("grad_ptrs"), py::arg("buf_ptrs"), py::arg("packed"), py::arg("sumsq"), py::arg("rows"),
+          py::arg("cols"), py::arg("g_stride"), py::arg("b_stride"), py::arg("momentum"), py::arg("nesterov"), py::arg("transpose"),
+          py::arg("peer_deltas"), py::arg("normalize") = true);
     m.def("muon_apply_push", &muon_apply_push);
     m.def("adamw_sharded", &adamw_sharded);
     m.def("flag_signal", &flag_signal);

@@ -22,6 +22,10 @@ struct GemmParams {
     const int* tile_expert;      // GROUPED_M: expert of each 128-row tile
     const int* num_m_tiles;      // GROUPED_M: number of 128-row tiles (device scalar)
     const int* seg_ends;         // GROUPED_K: cumulative padded row ends per expert
+    int symmetric;               // DENSE, M == N, bf16 output: the result is known to be symmetric (X X^T); only tiles on or above the
+                                 // diagonal are computed and every off-diagonal tile is also stored transposed
+    const float* batch_sumsq;    // DENSE, optional: per-batch sum of squares; s = 1 / (sqrt(sumsq[z]) * 1.02 + 1e-6) is Muon's Frobenius
+    int scale_mode;              // normalisation of an operand, folded into the epilogue: 1 -> alpha * s and beta * s, 2 -> alpha * s * s
     int* status;                 // device word; kernels write a non-zero code if a bounded wait gives up
 };
 

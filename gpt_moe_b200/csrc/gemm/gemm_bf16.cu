@@ -19,6 +19,9 @@
 //
 // Three tile enumerations share the kernel:
 //   DENSE     (optionally batched over z)                      - projections, LM head, Polar Express
+//             symmetric results (X X^T, A A with A symmetric): only the tiles on or above the diagonal are computed, the
+//             epilogue stores every off-diagonal tile a second time transposed (the reference's triangle-and-mirror
+//             kernels, optimizers/polar_express.py:60-121 and :155-230)
 //   GROUPED_M rows of A belong to experts; tile -> expert table on the device picks B's z slice
 //             (expert segments are padded to 128 rows, so a tile never straddles two experts)
 //   GROUPED_K one output matrix per expert, contraction over that expert's (padded) row segment
@@ -57,6 +60,7 @@ __device__ __forceinline__ int total_tiles(const GemmParams& p, int& m_tiles, in
         return m_tiles / 2 * n_tiles;
     }
     m_tiles = ((p.M + BM - 1) / BM + 1) & ~1;
+    if (p.symmetric) return n_tiles * (n_tiles + 1) / 2 * p.batch;      // M == N: pair tiles (i, j) with i <= j
     return m_tiles / 2 * n_tiles * p.batch * p.split_k;
 }
 
@@ -68,16 +72,25 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, i
         tile /= p.split_k;
     }
     const int m_pairs = m_tiles / 2;
-    const int per_batch = m_pairs * n_tiles;
+    const int per_batch = p.symmetric ? n_tiles * (n_tiles + 1) / 2 : m_pairs * n_tiles;
     const int z = (p.mode == GEMM_GROUPED_M) ? 0 : tile / per_batch;
     int r = tile - z * per_batch;
-    // grouped raster: GROUP_M pair-rows share their column sweep so A tiles stay in L2
-    const int group = r / (GROUP_M * n_tiles);
-    const int first_m = group * GROUP_M;
-    const int rows_in_group = min(GROUP_M, m_pairs - first_m);
-    r -= group * GROUP_M * n_tiles;
-    const int mt = 2 * (first_m + r % rows_in_group) + cta_rank;
-    const int nt = r / rows_in_group;
+    int mt, nt;
+    if (p.symmetric) {
+        // row i of the upper triangle holds n_tiles - i tiles
+        int i = 0;
+        while (r >= n_tiles - i) { r -= n_tiles - i; ++i; }
+        mt = 2 * i + cta_rank;
+        nt = i + r;
+    } else {
+        // grouped raster: GROUP_M pair-rows share their column sweep so A tiles stay in L2
+        const int group = r / (GROUP_M * n_tiles);
+        const int first_m = group * GROUP_M;
+        const int rows_in_group = min(GROUP_M, m_pairs - first_m);
+        r -= group * GROUP_M * n_tiles;
+        mt = 2 * (first_m + r % rows_in_group) + cta_rank;
+        nt = r / rows_in_group;
+    }
     t.m0 = mt * BM;
     t.n0 = nt * BN;
     t.m_limit = p.M;
@@ -222,6 +235,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (!have_acc && !(t.store_zeros && !p.accumulate)) continue;      // nothing to add, nothing to clear
             const int row = t.m0 + row_in_tile;
             const bool row_ok = row < t.m_limit;
+            float alpha = p.alpha, beta = p.beta;
+            if (p.batch_sumsq != nullptr) {                   // an operand is an un-normalised Muon update: scale the result instead
+                const float inv = 1.f / (sqrtf(p.batch_sumsq[t.dz]) * 1.02f + 1e-6f);
+                if (p.scale_mode == 2) alpha *= inv * inv;
+                else { alpha *= inv; beta *= inv; }
+            }
+            const bool mirror = p.symmetric && t.n0 != t.m0 - cta_rank * BM;      // off-diagonal pair tile (uniform across the pair)
             if (have_acc) {
                 if (!mbar_wait(&acc_full[acc], acc_ph)) { atomicExch(p.status, 104); ok = false; break; }
                 tc_fence_after();
@@ -260,7 +280,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const int col0 = round_col0 + (half * my_chunks + j) * 32;
                     float v[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[j][i]) * p.alpha;
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[j][i]) * alpha;
                     if (p.C != nullptr && row_ok && col0 < t.n_limit) {
                         const __nv_bfloat16* c = reinterpret_cast<const __nv_bfloat16*>(p.C) +
                             static_cast<long long>(t.dz) * p.c_batch_stride + static_cast<long long>(row) * p.ldc + col0;
@@ -272,15 +292,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
                                     const float2 f = __bfloat1622float2(h[e]);
-                                    v[i + 2 * e] += p.beta * f.x;
-                                    v[i + 2 * e + 1] += p.beta * f.y;
+                                    v[i + 2 * e] += beta * f.x;
+                                    v[i + 2 * e + 1] += beta * f.y;
                                 }
                             }
                         } else {
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
-                                if (col0 + i < t.n_limit) v[i] += p.beta * __bfloat162float(c[i]);
+                                if (col0 + i < t.n_limit) v[i] += beta * __bfloat162float(c[i]);
                         }
+                    }
+                    if (mirror) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[j][i] = __float_as_uint(v[i]);      // kept for the transposed store below
                     }
                     // 16-byte pieces of this thread's row go to piece index (i ^ row%8) of the 128-byte slab row
                     if (p.out_fp32) {
@@ -317,6 +341,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
                 ++stores;
+                if (mirror) {
+                    // The same 128 x 128 block goes out transposed (bf16 only): element (row, c) of this round lands in row c of
+                    // the transposed block, and 64 of this CTA's rows make one 128-byte slab row, so the two slabs are the
+                    // column ranges [m0, m0 + 64) and [m0 + 64, m0 + 128) of the mirrored tile.
+                    uint8_t* tbuf = staging + (stores & 1) * STAGING_BYTES;
+                    if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    uint8_t* tcol = tbuf + (row_in_tile >> 6) * (BM * 128) + (row_in_tile & 7) * 2;
+                    const int piece = (row_in_tile & 63) >> 3;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int cl = (half * 2 + j) * 32 + i;
+                            *reinterpret_cast<__nv_bfloat16*>(tcol + cl * 128 + ((piece ^ (i & 7)) << 4)) =
+                                __float2bfloat16_rn(__uint_as_float(r[j][i]));
+                        }
+                    }
+                    fence_proxy_async();
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    if (leader) {
+                        for (int sl = 0; sl < 2; ++sl) {
+                            const int col = t.m0 + sl * 64;
+                            if (col >= t.n_limit || round_col0 >= t.m_limit) break;
+                            const uint32_t src = smem_u32(tbuf + sl * (BM * 128));
+                            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                                         ::"l"(&tmap_d), "r"(src), "r"(col), "r"(round_col0), "r"(t.dz) : "memory");
+                        }
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    ++stores;
+                }
             }
             if (have_acc) {
                 // tiles narrower than BN leave the round loop early: the accumulator is released here in that case

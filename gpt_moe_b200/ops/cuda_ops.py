@@ -696,18 +696,22 @@ def _ptr_table(tensors: Sequence[Tensor]) -> Tensor:
     return table
 
 
-def polar_express_bf16(x: Tensor) -> Tensor:
-    """Five Polar Express iterations on a batch of wide, pre-normalised bf16 matrices x[n, m, k] (m <= k),
-    every product on the tcgen05 GEMM: A = X X^T; B = b A + c A A; X = a X + B X."""
+def polar_express_bf16(x: Tensor, sumsq: Optional[Tensor] = None) -> Tensor:
+    """Five Polar Express iterations on a batch of wide bf16 matrices x[n, m, k] (m <= k), every product on the tcgen05 GEMM:
+    A = X X^T; B = b A + c A A; X = a X + B X.  A and B are symmetric: their GEMMs compute the tiles on or above the
+    diagonal and mirror them (reference optimizers/polar_express.py:60-121, :155-230).  x is pre-normalised, or `sumsq` holds
+    the sum of squares of each matrix and the factor 1 / (1.02 * norm + 1e-6) is applied by the epilogues of the first
+    iteration.  The buffer of x is reused as scratch from the second iteration on."""
     c = ext()
     n, m, k = x.shape
     a_buf = torch.empty((n, m, m), dtype=BF16, device=x.device)
     b_buf = torch.empty_like(a_buf)
     y = torch.empty_like(x)
-    for ca, cb, cc in ref.POLAR_EXPRESS_COEFFS:
-        c.gemm_bf16(x, x, a_buf)                                            # A = X X^T
-        c.gemm_bf16(a_buf, a_buf, b_buf, False, False, cc, cb, a_buf)       # B = c A A^T + b A   (A symmetric)
-        c.gemm_bf16(b_buf, x, y, False, True, 1.0, ca, x)                   # Y = B X + a X       (X read MN-major)
+    for step, (ca, cb, cc) in enumerate(ref.POLAR_EXPRESS_COEFFS):
+        first = sumsq if step == 0 else None
+        c.gemm_bf16(x, x, a_buf, symmetric=True, batch_sumsq=first, scale_mode=2 if first is not None else 0)      # A = X X^T
+        c.gemm_bf16(a_buf, a_buf, b_buf, False, False, cc, cb, a_buf, symmetric=True)                               # B = c A A^T + b A
+        c.gemm_bf16(b_buf, x, y, False, True, 1.0, ca, x, batch_sumsq=first, scale_mode=1 if first is not None else 0)   # Y = B X + a X
         x, y = y, x
     return x
 

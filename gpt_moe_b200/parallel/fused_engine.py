@@ -371,8 +371,8 @@ class FusedEngine:
                 packed = torch.empty((len(batch), m, k), dtype=torch.bfloat16, device=self.device)
                 sumsq = torch.zeros(len(batch), dtype=torch.float32, device=self.device)
                 c.rs_muon_prepare(cuda_ops._ptr_table([p.main_grad for p in batch]), cuda_ops._ptr_table(bufs), packed, sumsq,
-                                  rows, cols, cols, cols, momentum, nesterov, tall, deltas_grad)
-                update = cuda_ops.polar_express_bf16(packed)
+                                  rows, cols, cols, cols, momentum, nesterov, tall, deltas_grad, normalize=False)
+                update = cuda_ops.polar_express_bf16(packed, sumsq)      # the first iteration's epilogues apply the normalisation
                 c.muon_apply_push(cuda_ops._ptr_table([p.data for p in batch]), cuda_ops._ptr_table([p.compute for p in batch]),
                                   update, rows, cols, cols, cols, alpha, tall, deltas_compute)
 

@@ -25,7 +25,7 @@ def _timed(fn, iters):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_mxfp8", "quantize", "gemm_wgrad", "grouped", "attn_fwd", "attn_bwd", "rs_muon", "ce", "rmsnorm", "rope", "rope_bwd", "ep_dispatch", "ep_combine", "rmsnorm_bwd", "attn_fwd_mla", "attn_bwd_mla"])
+    ap.add_argument("case", choices=["gemm", "gemm_mxfp8", "quantize", "gemm_wgrad", "grouped", "attn_fwd", "attn_bwd", "rs_muon", "ce", "rmsnorm", "rope", "rope_bwd", "ep_dispatch", "ep_combine", "rmsnorm_bwd", "attn_fwd_mla", "attn_bwd_mla", "gemm_xxt", "gemm_xxt_full", "polar"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     from gpt_moe_b200.ops import attention_tc, cuda_ops
@@ -89,6 +89,16 @@ def main() -> None:
             g = torch.randn_like(out)
             fn = lambda: torch.autograd.grad(out, (q, k, v), g, retain_graph=True)
             flops = 2 * (128 + 64 + 64 + 128 + 128) * pairs
+    elif args.case in ("gemm_xxt", "gemm_xxt_full"):   # A = X X^T for 96 expert up-projection gradients [768, 6144]; triangle-and-mirror or every tile
+        x = torch.randn(96, 768, 6144, device=dev).mul_(0.01).bfloat16()
+        a = torch.empty(96, 768, 768, device=dev, dtype=torch.bfloat16)
+        fn = lambda: c.gemm_bf16(x, x, a, symmetric=args.case == "gemm_xxt")
+        flops = 2 * 96 * 768 * 768 * 6144                 # of the full product: the symmetric form does two thirds of it
+    elif args.case == "polar":                   # five Polar Express iterations on the same batch
+        x = torch.randn(96, 768, 6144, device=dev)
+        x = (x / (x.norm(dim=(-2, -1), keepdim=True) * 1.02 + 1e-6)).bfloat16()
+        fn = lambda: cuda_ops.polar_express_bf16(x)
+        flops = 5 * 96 * (4 * 768 * 768 * 6144 + 2 * 768 ** 3)
     elif args.case == "rs_muon":                 # reduce + momentum + pack for 16 matrices of 6144 x 768 (world of one)
         grads = [torch.randn(6144, 768, device=dev) for _ in range(16)]
         bufs = [torch.zeros(6144, 768, device=dev) for _ in range(16)]

@@ -169,6 +169,28 @@ def test_linear_cross_entropy(ops):
     assert rel(x.grad, x2.grad) < 2e-2 and rel(w.grad, w2.grad) < 2e-2
 
 
+@pytest.mark.parametrize("m,k,batch", [(768, 768, 3), (768, 3072, 2), (640, 256, 2), (1024, 512, 1), (128, 256, 2), (264, 128, 1)])
+def test_gemm_symmetric_mirror(ops, m, k, batch):
+    """Triangle-and-mirror GEMMs of Polar Express: X X^T, and c A A + b A for a symmetric A, against fp32 matmuls."""
+    torch.manual_seed(12)
+    c = ops.ext()
+    x = torch.randn(batch, m, k, device="cuda").bfloat16()
+    a = torch.full((batch, m, m), float("nan"), device="cuda", dtype=torch.bfloat16)      # every element must be written
+    c.gemm_bf16(x, x, a, symmetric=True)
+    want = torch.bmm(x.float(), x.float().transpose(1, 2))
+    assert rel(a, want) < BF16_TOL
+    assert torch.equal(a, a.transpose(1, 2))
+    full = torch.empty_like(a)
+    c.gemm_bf16(x, x, full)
+    assert torch.equal(torch.triu(a), torch.triu(full))          # the computed tiles are the ones the full product writes
+    a.mul_(1.0 / k)
+    b = torch.full_like(a, float("nan"))
+    c.gemm_bf16(a, a, b, False, False, 0.7, -1.3, a, symmetric=True)
+    want = 0.7 * torch.bmm(a.float(), a.float()) - 1.3 * a.float()
+    assert rel(b, want) < BF16_TOL
+    assert torch.equal(b, b.transpose(1, 2))
+
+
 def test_polar_express_gemms(ops):
     """The tcgen05 Polar Express against the same iteration in torch bf16 (same rounding regime) and fp32."""
     torch.manual_seed(6)
@@ -183,6 +205,11 @@ def test_polar_express_gemms(ops):
         sv = torch.linalg.svdvals(got.float())
         inside = ((sv > 0.5) & (sv < 1.3)).float().mean().item()      # the smallest few singular values converge last
         assert sv.max().item() < 1.3 and inside > 0.95, (shape, inside, sv.max().item())
+        # the normalisation folded into the first iteration's epilogues: raw matrices plus their sums of squares
+        raw = (g * 3e-4).bfloat16()
+        sumsq = raw.float().pow(2).sum(dim=(-2, -1))
+        folded = ops.polar_express_bf16(raw.clone(), sumsq)
+        assert rel(folded, same_regime) < 5e-2, shape
 
 
 def test_adamw_and_muon_steps(ops):
