@@ -147,22 +147,49 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const TX* __restrict__ 
 }
 
 // out[col] = sum over rows of partial[row][col]  (second pass of the deterministic column reductions).
-// Each block owns 32 columns; 8 warps stride over the rows and combine through shared memory in a fixed order.
-__global__ void __launch_bounds__(256)
+// Each block owns 32 columns; 32 warps stride over the rows (four independent loads in flight per thread) and combine
+// through shared memory in a fixed order.
+constexpr int COLSUM_WARPS = 32;
+__global__ void __launch_bounds__(COLSUM_WARPS * 32)
 column_sum_kernel(const float* __restrict__ partial, float* __restrict__ out, int rows, int cols, int accumulate) {
-    __shared__ float red[8][32];
+    __shared__ float red[COLSUM_WARPS][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int col = blockIdx.x * 32 + tx;
     float s = 0.f;
-    if (col < cols)
-        for (int r = ty; r < rows; r += 8) s += partial[static_cast<long long>(r) * cols + col];
+    if (col < cols) {
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        int r = ty;
+        for (; r + 3 * COLSUM_WARPS < rows; r += 4 * COLSUM_WARPS) {
+            s0 += partial[static_cast<long long>(r) * cols + col];
+            s1 += partial[static_cast<long long>(r + COLSUM_WARPS) * cols + col];
+            s2 += partial[static_cast<long long>(r + 2 * COLSUM_WARPS) * cols + col];
+            s3 += partial[static_cast<long long>(r + 3 * COLSUM_WARPS) * cols + col];
+        }
+        for (; r < rows; r += COLSUM_WARPS) s0 += partial[static_cast<long long>(r) * cols + col];
+        s = (s0 + s1) + (s2 + s3);
+    }
     red[ty][tx] = s;
     __syncthreads();
     if (ty == 0 && col < cols) {
         float t = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) t += red[w][tx];
+        for (int w = 0; w < COLSUM_WARPS; ++w) t += red[w][tx];
         out[col] = accumulate ? out[col] + t : t;
+    }
+}
+
+// out[0] = sum of partial[0 .. n)  (the one-column case: every thread takes a strided share, fixed combination order)
+__global__ void __launch_bounds__(1024)
+vector_sum_kernel(const float* __restrict__ partial, float* __restrict__ out, int n) {
+    __shared__ float red[32];
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n; i += 1024) s += partial[i];
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = warp_sum(red[threadIdx.x]);
+        if (threadIdx.x == 0) *out = t;
     }
 }
 
@@ -197,7 +224,7 @@ void launch_residual_bwd(const float* dxn, const void* branch, const float* beta
                          long long n, cudaStream_t s) {
     const int blocks = residual_bwd_blocks(n);
     residual_bwd_kernel<<<blocks, 256, 0, s>>>(dxn, static_cast<const __nv_bfloat16*>(branch), beta, static_cast<__nv_bfloat16*>(dbranch), partial, n);
-    column_sum_kernel<<<1, 256, 0, s>>>(partial, dbeta, blocks, 1, 0);
+    vector_sum_kernel<<<1, 1024, 0, s>>>(partial, dbeta, blocks);
 }
 
 bool norm_dim_supported(int d) {
@@ -256,12 +283,12 @@ bool launch_rmsnorm_bwd(const void* dy, const void* x, bool x_fp32, const float*
     }
     GM_DISPATCH_CHUNKS(d, GM_BWD)
 #undef GM_BWD
-    if (dw_partial) column_sum_kernel<<<(d + 31) / 32, 256, 0, s>>>(dw_partial, dw, blocks, d, dw_accumulate);
+    if (dw_partial) column_sum_kernel<<<(d + 31) / 32, COLSUM_WARPS * 32, 0, s>>>(dw_partial, dw, blocks, d, dw_accumulate);
     return true;
 }
 
 void launch_column_sum(const float* partial, float* out, int rows, int cols, int accumulate, cudaStream_t s) {
-    column_sum_kernel<<<(cols + 31) / 32, 256, 0, s>>>(partial, out, rows, cols, accumulate);
+    column_sum_kernel<<<(cols + 31) / 32, COLSUM_WARPS * 32, 0, s>>>(partial, out, rows, cols, accumulate);
 }
 
 // ---- RoPE + QK-norm ---------------------------------------------------------------------------------------
