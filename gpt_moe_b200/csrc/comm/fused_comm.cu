@@ -29,6 +29,7 @@ __device__ __forceinline__ float4 ld_peer4(const float* p, long long delta) {
 // Sum of the same float4 on every rank, added in rank order.  The loads of up to eight ranks are issued before any of them
 // is consumed, so a thread keeps eight NVLink requests in flight instead of one.
 __device__ __forceinline__ float4 sum_peers4(const float* p, const PeerDeltas& peers, int world) {
+    if (world == 1) return ld_peer4(p, peers.d[0]);          // one GPU: a plain load, no batch of predicated slots
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int base = 0; base < world; base += 8) {
         float4 t[8];
