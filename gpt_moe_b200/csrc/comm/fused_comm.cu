@@ -175,16 +175,37 @@ adamw_sharded_kernel(float* __restrict__ params, const float* __restrict__ grads
         float pp[4] = {pw.x, pw.y, pw.z, pw.w};
         const float4 wd4 = *reinterpret_cast<const float4*>(decay + lo + i);      // per-element weight decay (0 for no-decay groups)
         const float wd[4] = {wd4.x, wd4.y, wd4.z, wd4.w};
+        // the four moments of this thread travel as one 16-byte (fp32) or 8-byte (bf16) access each way
+        float mm[4], vv[4];
+        if constexpr (sizeof(TM) == 4) {
+            const float4 m4 = *reinterpret_cast<const float4*>(m + i), v4 = *reinterpret_cast<const float4*>(v + i);
+            mm[0] = m4.x; mm[1] = m4.y; mm[2] = m4.z; mm[3] = m4.w;
+            vv[0] = v4.x; vv[1] = v4.y; vv[2] = v4.z; vv[3] = v4.w;
+        } else {
+            const uint2 mr = *reinterpret_cast<const uint2*>(m + i), vr = *reinterpret_cast<const uint2*>(v + i);
+            const float2 m01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&mr.x)), m23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&mr.y));
+            const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.x)), v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.y));
+            mm[0] = m01.x; mm[1] = m01.y; mm[2] = m23.x; mm[3] = m23.y;
+            vv[0] = v01.x; vv[1] = v01.y; vv[2] = v23.x; vv[3] = v23.y;
+        }
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            float mi, vi;
-            if constexpr (sizeof(TM) == 4) { mi = m[i + e]; vi = v[i + e]; } else { mi = __bfloat162float(m[i + e]); vi = __bfloat162float(v[i + e]); }
-            mi = beta1 * mi + (1.f - beta1) * gg[e];
-            vi = beta2 * vi + (1.f - beta2) * gg[e] * gg[e];
-            if constexpr (sizeof(TM) == 4) { m[i + e] = mi; v[i + e] = vi; } else { m[i + e] = __float2bfloat16(mi); v[i + e] = __float2bfloat16(vi); }
+            const float mi = beta1 * mm[e] + (1.f - beta1) * gg[e];
+            const float vi = beta2 * vv[e] + (1.f - beta2) * gg[e] * gg[e];
+            mm[e] = mi; vv[e] = vi;
             float x = pp[e] * (1.f - lr * wd[e]);
             x -= lr / bc1 * mi / (sqrtf(vi) / bc2_sqrt + eps);
             pp[e] = x;
+        }
+        if constexpr (sizeof(TM) == 4) {
+            *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+            *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+        } else {
+            uint2 mo, vo;
+            mo.x = pack_bf16x2(mm[0], mm[1]); mo.y = pack_bf16x2(mm[2], mm[3]);
+            vo.x = pack_bf16x2(vv[0], vv[1]); vo.y = pack_bf16x2(vv[2], vv[3]);
+            *reinterpret_cast<uint2*>(m + i) = mo;
+            *reinterpret_cast<uint2*>(v + i) = vo;
         }
         const float4 nw = make_float4(pp[0], pp[1], pp[2], pp[3]);
         char* dst = reinterpret_cast<char*>(params + lo + i);
