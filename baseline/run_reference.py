@@ -178,8 +178,10 @@ def run_reference(args) -> dict:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
         "config": {"model": "GPT-MoE-small (12L d768 12x64 heads, SWA 1024, 8 SwiGLU experts h3072 top-1, vocab 50304)",
-                   "global_batch": batch * world, "seq_len": seq, "parallelism": f"dp{world}", "torch_compile_mode": used_mode,
-                   "compile_fallbacks": errors, "linear_precision": "default (bf16 autocast)"},
+                   "global_batch": batch * world, "seq_len": seq, "parallelism": f"dp{world}",
+                   "l2": "per-step working set >> 126 MB L2; no explicit flush"},
+        "notes": {"torch_compile_mode": used_mode, "compile_fallbacks": errors, "linear_precision": "default (bf16 autocast)",
+                  "optimizer": "the reference's Muon (Polar Express) + torch fused AdamW"},
         "e2e": {"value": tokens / (total_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * batch * seq * 8, "d2h_bytes_per_step": 4},
         "last_loss": loss,
     }

@@ -149,6 +149,7 @@ def run_ours(args) -> dict:
         trainer.engine.set_comm_dry_run(False)
         exposed_ms = (device_ms - dry_ms) / args.steps
 
+    engine_info = trainer.engine.describe() if hasattr(trainer.engine, "describe") else {"engine": type(trainer.engine).__name__}
     result = {
         "metric": "train tok/s (box, max over ranks)", "value": tokens_per_step * args.steps / (device_ms / 1e3),
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -156,8 +157,10 @@ def run_ours(args) -> dict:
         "dtype": "bf16" if args.precision == "default" else "bf16+mxfp8", "data": "synthetic",
         "config": {"model": MODEL_NAMES.get(args.preset, args.preset),
                    "global_batch": cfg.gpu_batch_size_train * world, "seq_len": cfg.seq_len_train,
-                   "parallelism": f"dp{world}" + (f"+ep{trainer.ep_size}" if trainer.ep_size > 1 else ""), "optimizer": "muon(polar express)+adamw",
+                   "parallelism": f"dp{world}" + (f"+ep{trainer.ep_size}" if trainer.ep_size > 1 else ""),
                    "l2": "per-step working set >> 126 MB L2; no explicit flush"},
+        "notes": {"optimizer": "muon(polar express)+adamw", "linear_precision": args.precision, **engine_info,
+                  "op_paths": cuda_ops.path_counts()},
         "clocks": clocks,
         "e2e": {"value": tokens_per_step * args.steps / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                 "h2d_bytes_per_step": 2 * cfg.gpu_batch_size_train * cfg.seq_len_train * 8 * cfg.grad_accum_mini_steps,

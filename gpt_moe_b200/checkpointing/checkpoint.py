@@ -68,6 +68,110 @@ def gather_full_state_dict(model: nn.Module, ep_group=None) -> Dict[str, torch.T
     return state
 
 
+_EXPERT_RE = re.compile(r"^(.*\.mlp\.experts\.)(\d+)(\..*)$")
+
+
+def _expert_key(name: str) -> str:
+    """Parameter name with the expert index blanked: experts of one layer share it."""
+    m = _EXPERT_RE.match(name)
+    return name if m is None else f"{m.group(1)}*{m.group(3)}"
+
+
+def global_param_order(model: nn.Module) -> List[str]:
+    """Parameter names of the UNSHARDED model in its `named_parameters()` order.  With expert parallelism the local
+    module holds only some experts of every MoE layer; the others are filled in under their global indices, at the
+    place the unsharded module lists them (all experts of a layer, in index order, with one expert's parameter order)."""
+    model = unwrap(model)
+    experts_of_layer: Dict[str, int] = {}
+    for mod_name, module in model.named_modules():
+        if hasattr(module, "num_experts") and hasattr(module, "experts"):
+            experts_of_layer[mod_name + ".experts."] = int(module.num_experts)
+    names = [n for n, _ in model.named_parameters()]
+    out: List[str] = []
+    done = set()
+    for i, name in enumerate(names):
+        m = _EXPERT_RE.match(name)
+        if m is None:
+            out.append(name)
+            continue
+        prefix = m.group(1)
+        if prefix in done:
+            continue
+        done.add(prefix)
+        first = m.group(2)
+        suffixes = [mm.group(3) for mm in (_EXPERT_RE.match(n) for n in names[i:]) if mm and mm.group(1) == prefix and mm.group(2) == first]
+        for e in range(experts_of_layer.get(prefix, 0)):
+            out.extend(f"{prefix}{e}{suffix}" for suffix in suffixes)
+    return out
+
+
+def _optimizer_layout(model: nn.Module, optimizer: torch.optim.Optimizer):
+    """(local names per param group, global names per param group, {global name: global index}) of one optimizer: the
+    global lists are what the optimizer of the unsharded model would hold, in its order."""
+    name_of = {id(p): n for n, p in unwrap(model).named_parameters()}
+    local_groups = [[name_of[id(p)] for p in g["params"]] for g in optimizer.param_groups]
+    order = global_param_order(model)
+    global_groups, index = [], {}
+    for local in local_groups:
+        keys = {_expert_key(n) for n in local}
+        names = [n for n in order if _expert_key(n) in keys]
+        for n in names:
+            index[n] = len(index)
+        global_groups.append(names)
+    return local_groups, global_groups, index
+
+
+def merge_optimizer_state(model: nn.Module, optimizer: torch.optim.Optimizer, contributes, group=None) -> Dict[str, Any]:
+    """State dict of `optimizer` in the unsharded torch layout, assembled from all ranks of `group`.
+
+    Every rank hands in the state of the parameters for which `contributes(name)` is true on that rank (the owner of a
+    sharded matrix; one holder of each expert); entries are matched by parameter NAME, so expert-parallel ranks whose
+    local parameter lists differ merge correctly, and are re-keyed by the parameter's position in the unsharded model.
+    Collective over `group`."""
+    local_groups, global_groups, index = _optimizer_layout(model, optimizer)
+    sd = optimizer.state_dict()
+    flat_local = [n for names in local_groups for n in names]
+    mine = {flat_local[i]: _state_to_cpu(state) for i, state in sd["state"].items() if contributes(flat_local[i])}
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        parts: List[Optional[dict]] = [None] * dist.get_world_size(group)
+        dist.all_gather_object(parts, mine, group=group)
+        merged: Dict[str, Any] = {}
+        for part in parts:
+            for name, state in part.items():
+                merged.setdefault(name, state)
+    else:
+        merged = mine
+    state = {index[name]: value for name, value in merged.items() if name in index}
+    param_groups = []
+    for saved, names in zip(sd["param_groups"], global_groups):
+        param_groups.append({**saved, "params": [index[n] for n in names]})
+    return {"state": dict(sorted(state.items())), "param_groups": param_groups}
+
+
+def localize_optimizer_state(model: nn.Module, optimizer: torch.optim.Optimizer, state_dict: Dict[str, Any]) -> Dict[str, Any]:
+    """Inverse of `merge_optimizer_state` for loading: the entries of an unsharded-layout state dict that belong to this
+    rank's parameters, keyed by the local optimizer's indices."""
+    local_groups, _, index = _optimizer_layout(model, optimizer)
+    state, param_groups, cursor = {}, [], 0
+    for saved, names in zip(state_dict["param_groups"], local_groups):
+        ids = list(range(cursor, cursor + len(names)))
+        cursor += len(names)
+        for i, name in zip(ids, names):
+            entry = state_dict["state"].get(index[name])
+            if entry is not None:
+                state[i] = entry
+        param_groups.append({**saved, "params": ids})
+    return {"state": state, "param_groups": param_groups}
+
+
+def _state_to_cpu(obj):
+    if isinstance(obj, torch.Tensor):
+        return obj.detach().cpu()
+    if isinstance(obj, dict):
+        return {k: _state_to_cpu(v) for k, v in obj.items()}
+    return obj
+
+
 def keep_latest_checkpoints(checkpoint_dir: str, max_checkpoints_to_keep: int, log_buffer: List[str]) -> None:
     by_step: Dict[int, List[str]] = {}
     for name in os.listdir(checkpoint_dir):

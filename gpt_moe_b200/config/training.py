@@ -195,13 +195,15 @@ class TrainingConfig:
     # ---- new capabilities ---------------------------------------------------------------------
     expert_parallel_size: int = 1     # experts are sharded over this many ranks (must divide world size and num_experts)
     shard_muon: bool = True           # each rank orthogonalises only the matrices it owns, then all-gathers
-    grad_reduce_dtype: str = "fp32"   # wire dtype of the gradient reduction; only "fp32" (the reference's DDP precision) is implemented
+    grad_reduce_dtype: str = "fp32"   # wire dtype of the Muon gradient reduction: "fp32" (the reference's DDP precision) or "bf16"
+                                      # (peers read a bf16 shadow of the gradient buffer, the owner still sums in fp32)
     grad_bucket_mb: int = 64          # flat gradient bucket size
     use_fused_collectives: bool = True  # peer-memory kernels; False = NCCL calls (the measured baseline)
     use_cuda_graphs: bool = True        # fused engine: forward+backward of a training step is captured once per (shape, window) and replayed
     nvtx_ranges: bool = False           # NVTX ranges around the phases of a training step (forward+backward per micro-step, optimizer)
-    overlap_grad_reduce: bool = False   # fused engine: a block's Muon reduce / update / push runs beside the backward of earlier blocks
-                                        # (measured slightly slower at 2 GPUs, where the per-block batches are small: 67.9 vs 66.3 ms/step)
+    overlap_grad_reduce: bool = False   # fused engine: a block's gradient reduce (+ momentum, pack) runs on a second stream beside the
+                                        # backward of the earlier blocks; orthogonalisation and the weight push follow the backward pass
+    allow_nccl_fallback: bool = False   # fused engine requested but symmetric memory unavailable: fall back to NCCL instead of raising
     ep_capacity_factor: float = 0.0     # fused expert parallelism: receive buffers hold this many times a rank's own slots (0 = worst case)
     step_deadline_s: float = 0.0      # >0 arms the host watchdog: abort the job if a step exceeds it
     use_synthetic_data: bool = False  # uniform random token ids from `base_seed` instead of .npy shards

@@ -255,17 +255,26 @@ std::vector<long long> to_deltas(const std::vector<int64_t>& deltas) { return st
 
 // Owner-side gradient reduction over peer memory fused with Muon's momentum / Nesterov / bf16 pack / Frobenius normalisation.
 // grad_ptrs point into THIS rank's symmetric gradient buffer; peer_deltas[r] = (rank r's buffer base) - (this rank's base).
+// bf16 wire: `grad_base` is this rank's flat fp32 gradient buffer and `shadow` its bf16 shadow (same element offsets);
+// peer_deltas are then the deltas of the SHADOW buffers and peers' contributions are read from their shadows.
 void rs_muon_prepare(const Tensor& grad_ptrs, const Tensor& buf_ptrs, Tensor& packed, Tensor& sumsq, int64_t rows, int64_t cols,
                      int64_t g_stride, int64_t b_stride, double momentum, bool nesterov, bool transpose,
-                     const std::vector<int64_t>& peer_deltas, bool normalize) {
+                     const std::vector<int64_t>& peer_deltas, bool normalize, const OptTensor& grad_base, const OptTensor& shadow) {
     c10::cuda::CUDAGuard guard(packed.device());
     check_bf16(packed, "packed");
     const int n = grad_ptrs.numel();
     GM_CHECK(packed.numel() == n * rows * cols && (rows * cols) % 8 == 0, "packed buffer shape");
     auto d = to_deltas(peer_deltas);
+    GM_CHECK(grad_base.has_value() == shadow.has_value(), "rs_muon_prepare: grad_base and shadow come together");
+    if (shadow.has_value())
+        GM_CHECK(grad_base->scalar_type() == torch::kFloat32 && shadow->scalar_type() == torch::kBFloat16 && shadow->numel() >= grad_base->numel(),
+                 "rs_muon_prepare: fp32 gradient buffer and a bf16 shadow at least as long");
+    GM_CHECK(sumsq.numel() >= n, "rs_muon_prepare: one sum of squares per matrix");
     GM_CHECK(launch_rs_muon_prepare(reinterpret_cast<const float* const*>(grad_ptrs.data_ptr<int64_t>()),
                                     reinterpret_cast<float* const*>(buf_ptrs.data_ptr<int64_t>()), packed.data_ptr(), sumsq.data_ptr<float>(), n,
-                                    rows, cols, g_stride, b_stride, momentum, nesterov, transpose, d.data(), d.size(), stream()),
+                                    rows, cols, g_stride, b_stride, momentum, nesterov, transpose, d.data(), d.size(),
+                                    grad_base.has_value() ? grad_base->data_ptr<float>() : nullptr,
+                                    shadow.has_value() ? shadow->data_ptr() : nullptr, stream()),
              "rs_muon_prepare: at most 16 ranks, column count a multiple of 4");
     // normalize = false leaves `packed` as it is: the caller hands `sumsq` to the first GEMMs of the orthogonalisation instead
     if (normalize) launch_muon_normalize(packed.data_ptr(), sumsq.data_ptr<float>(), n, rows * cols, stream());
@@ -309,18 +318,41 @@ void cast_bf16(const Tensor& src, Tensor& dst) {
 
 }  // namespace
 
-// Publish `value` into flags[index] of every rank / wait until flags[first .. first + world) of this rank have all reached `value`.
-void flag_signal(Tensor& flags, const std::vector<int64_t>& deltas, int64_t index, int64_t value) {
+// Publish a value into flags[index] of every rank / wait until flags[first .. first + world) of this rank have all reached it.
+// The value is `value`, or the content of the int32 device word `value_word` when given (no host state in the launch).
+void flag_signal(Tensor& flags, const std::vector<int64_t>& deltas, int64_t index, int64_t value, const OptTensor& value_word) {
     c10::cuda::CUDAGuard guard(flags.device());
     GM_CHECK(flags.scalar_type() == torch::kInt32 && index >= 0 && index < flags.numel(), "flag_signal: int32 flag table, index in range");
+    if (value_word.has_value()) GM_CHECK(value_word->is_cuda() && value_word->scalar_type() == torch::kInt32 && value_word->numel() >= 1, "value_word: int32 CUDA tensor");
     auto d = to_deltas(deltas);
-    GM_CHECK(launch_flag_signal(flags.data_ptr<int>(), d.data(), d.size(), index, value, stream()), "flag_signal: at most 16 ranks");
+    GM_CHECK(launch_flag_signal(flags.data_ptr<int>(), d.data(), d.size(), index, value, value_word.has_value() ? value_word->data_ptr<int>() : nullptr, stream()),
+             "flag_signal: at most 16 ranks");
 }
 
-void flag_wait(const Tensor& flags, int64_t first, int64_t world, int64_t value) {
+void flag_wait(const Tensor& flags, int64_t first, int64_t world, int64_t value, const OptTensor& value_word) {
     c10::cuda::CUDAGuard guard(flags.device());
     GM_CHECK(flags.scalar_type() == torch::kInt32 && first >= 0 && first + world <= flags.numel(), "flag_wait: int32 flag table, range inside it");
-    GM_CHECK(launch_flag_wait(flags.data_ptr<int>(), first, world, value, status_word(flags.device().index()), stream()), "flag_wait: at most 16 ranks");
+    if (value_word.has_value()) GM_CHECK(value_word->is_cuda() && value_word->scalar_type() == torch::kInt32 && value_word->numel() >= 1, "value_word: int32 CUDA tensor");
+    GM_CHECK(launch_flag_wait(flags.data_ptr<int>(), first, world, value, value_word.has_value() ? value_word->data_ptr<int>() : nullptr,
+                              status_word(flags.device().index()), stream()), "flag_wait: at most 16 ranks");
+}
+
+void bump_word(Tensor& word) {
+    c10::cuda::CUDAGuard guard(word.device());
+    GM_CHECK(word.is_cuda() && word.scalar_type() == torch::kInt32 && word.numel() >= 1, "bump_word: int32 CUDA tensor");
+    launch_bump_word(word.data_ptr<int>(), stream());
+}
+
+// One-launch barrier over a symmetric int32 flag table of `world` entries per rank (see peer_barrier_kernel).  `budget_cycles`
+// = 0 selects the common wait budget; a wait that runs out sets status 601 and returns.
+void peer_barrier(Tensor& flags, const std::vector<int64_t>& deltas, int64_t me, Tensor& epoch_word, int64_t budget_cycles) {
+    c10::cuda::CUDAGuard guard(flags.device());
+    GM_CHECK(flags.is_cuda() && flags.scalar_type() == torch::kInt32 && flags.numel() >= static_cast<int64_t>(deltas.size()),
+             "peer_barrier: int32 flag table with one entry per rank");
+    GM_CHECK(epoch_word.is_cuda() && epoch_word.scalar_type() == torch::kInt32 && epoch_word.numel() >= 1, "peer_barrier: int32 epoch word");
+    auto d = to_deltas(deltas);
+    GM_CHECK(launch_peer_barrier(flags.data_ptr<int>(), d.data(), d.size(), me, epoch_word.data_ptr<int>(), status_word(flags.device().index()),
+                                 budget_cycles, stream()), "peer_barrier: at most 16 ranks, rank inside the group");
 }
 
 // ---- expert-parallel dispatch / combine over peer memory ---------------------------------------------------------------
@@ -424,11 +456,13 @@ void register_kernels(pybind11::module_& m) {
     m.def("cast_bf16", &cast_bf16);
     m.def("rs_muon_prepare", &rs_muon_prepare, py::arg("grad_ptrs"), py::arg("buf_ptrs"), py::arg("packed"), py::arg("sumsq"), py::arg("rows"),
           py::arg("cols"), py::arg("g_stride"), py::arg("b_stride"), py::arg("momentum"), py::arg("nesterov"), py::arg("transpose"),
-          py::arg("peer_deltas"), py::arg("normalize") = true);
+          py::arg("peer_deltas"), py::arg("normalize") = true, py::arg("grad_base") = py::none(), py::arg("shadow") = py::none());
     m.def("muon_apply_push", &muon_apply_push);
     m.def("adamw_sharded", &adamw_sharded);
-    m.def("flag_signal", &flag_signal);
-    m.def("flag_wait", &flag_wait);
+    m.def("flag_signal", &flag_signal, py::arg("flags"), py::arg("deltas"), py::arg("index"), py::arg("value"), py::arg("value_word") = py::none());
+    m.def("flag_wait", &flag_wait, py::arg("flags"), py::arg("first"), py::arg("world"), py::arg("value"), py::arg("value_word") = py::none());
+    m.def("bump_word", &bump_word);
+    m.def("peer_barrier", &peer_barrier, py::arg("flags"), py::arg("deltas"), py::arg("me"), py::arg("epoch_word"), py::arg("budget_cycles") = 0);
     m.def("ep_push_counts", &ep_push_counts);
     m.def("ep_plan", &ep_plan);
     m.def("ep_zero_pads", &ep_zero_pads);

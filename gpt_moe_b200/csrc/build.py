@@ -18,10 +18,17 @@ from concurrent.futures import ThreadPoolExecutor
 
 CSRC = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(CSRC)
-BUILD = os.path.join(CSRC, "build")
-TARGET = os.path.join(PKG, "_C.so")
+BUILD = os.path.join(CSRC, "build_checked" if os.environ.get("GM_CHECK_BOUNDS", "0") == "1" else "build")
+TARGET = os.path.join(PKG, "_C_checked.so" if os.environ.get("GM_CHECK_BOUNDS", "0") == "1" else "_C.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--use_fast_math", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+              "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+# --use_fast_math only where the arithmetic is an exponential / reciprocal inside a softmax or a GEMM epilogue; the
+# optimizer, normalisation, loss and quantisation kernels keep IEEE division and square root (they name the fast
+# intrinsics they want explicitly)
+FAST_MATH_DIRS = ("gemm", "attention")
+# GM_CHECK_BOUNDS=1 in the environment builds the checked variant (`_C_checked.so`): every guarded index is tested, an
+# out-of-range access is skipped and recorded in the status word (code 9xx) instead of touching memory
+CHECKED = os.environ.get("GM_CHECK_BOUNDS", "0") == "1"
 
 
 def _sources():
@@ -81,13 +88,17 @@ def build(verbose: bool = False) -> str:
     nvcc = os.path.join(cuda_home, "bin", "nvcc")
     includes = [f"-I{p}" for p in cpp_extension.include_paths(device_type="cuda")] + [f"-I{sysconfig.get_paths()['include']}"]
     abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
-    cxx_flags = ["-O2", "-std=c++17", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-DTORCH_EXTENSION_NAME=_C",
+    ext_name = "_C_checked" if CHECKED else "_C"
+    cxx_flags = ["-O2", "-std=c++17", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={abi}", f"-DTORCH_EXTENSION_NAME={ext_name}",
                  "-DTORCH_API_INCLUDE_EXTENSION_H", "-Wno-deprecated-declarations"]
     jobs, objects = [], []
     for src in cu:
         obj = os.path.join(BUILD, os.path.relpath(src, CSRC).replace(os.sep, "_") + ".o")
         objects.append(obj)
-        cmd = [nvcc] + NVCC_FLAGS + [f"-I{CSRC}", "-c", src, "-o", obj]
+        extra = ["--use_fast_math"] if os.path.relpath(src, CSRC).split(os.sep)[0] in FAST_MATH_DIRS else []
+        if CHECKED:
+            extra.append("-DGM_CHECK_BOUNDS=1")
+        cmd = [nvcc] + NVCC_FLAGS + extra + [f"-I{CSRC}", "-c", src, "-o", obj]
         key = hashlib.sha256((open(src).read() + headers + " ".join(cmd)).encode()).hexdigest()
         jobs.append((cmd, src, obj, key))
     for src in cpp:

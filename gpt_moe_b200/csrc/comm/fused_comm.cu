@@ -42,11 +42,39 @@ __device__ __forceinline__ float4 sum_peers4(const float* p, const PeerDeltas& p
     return s;
 }
 
+// bf16 wire format: every rank keeps a bf16 shadow of its gradient buffer (same element offsets); a peer's contribution is
+// read from its shadow (half the NVLink bytes), this rank's own from its fp32 buffer; the sum is formed in fp32 in rank order.
+__device__ __forceinline__ float4 ld_peer4_bf16(const __nv_bfloat16* p, long long delta) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const char*>(p) + delta);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ float4 sum_peers4_bf16(const float* own, const __nv_bfloat16* shadow, const PeerDeltas& peers, int world) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int base = 0; base < world; base += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (base + k >= world) t[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            else if (peers.d[base + k] == 0) t[k] = *reinterpret_cast<const float4*>(own);
+            else t[k] = ld_peer4_bf16(shadow, peers.d[base + k]);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { s.x += t[k].x; s.y += t[k].y; s.z += t[k].z; s.w += t[k].w; }
+    }
+    return s;
+}
+
 // tile: 32 rows x 128 columns, 256 threads; thread (tx, ty) owns columns 4*tx..4*tx+3 of rows ty, ty+8, ty+16, ty+24
+// `shadow_gap` != 0 selects the bf16 wire: the bf16 shadow of gradient element i of this rank's flat buffer sits at
+// shadow_base + i, where shadow_base - grad_base (in bytes, through `shadow_gap` and the element index) is uniform; `peers`
+// then holds the deltas of the SHADOW buffers.
 __global__ void __launch_bounds__(256)
 rs_muon_prepare_kernel(const float* const* __restrict__ grads, float* const* __restrict__ bufs, __nv_bfloat16* __restrict__ packed,
                        float* __restrict__ sumsq, int rows, int cols, long long g_stride, long long b_stride, float momentum,
-                       int nesterov, int transpose, PeerDeltas peers, int world, float inv_world) {
+                       int nesterov, int transpose, PeerDeltas peers, int world, float inv_world,
+                       const float* grad_base, const __nv_bfloat16* shadow_base) {
     __shared__ float tile[32][132];
     __shared__ float part[8];
     const int mat = blockIdx.z;
@@ -62,7 +90,7 @@ rs_muon_prepare_kernel(const float* const* __restrict__ grads, float* const* __r
         float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
         if (r < rows && c < cols) {
             const float* gp = g + r * g_stride + c;
-            float4 s = sum_peers4(gp, peers, world);
+            float4 s = shadow_base ? sum_peers4_bf16(gp, shadow_base + (gp - grad_base), peers, world) : sum_peers4(gp, peers, world);
             s.x *= inv_world; s.y *= inv_world; s.z *= inv_world; s.w *= inv_world;
             float4 b = *reinterpret_cast<const float4*>(buf + r * b_stride + c);
             b.x = b.x * momentum + s.x; b.y = b.y * momentum + s.y; b.z = b.z * momentum + s.z; b.w = b.w * momentum + s.w;
@@ -221,11 +249,13 @@ static PeerDeltas make_deltas(const long long* deltas, int world) {
 
 bool launch_rs_muon_prepare(const float* const* grads, float* const* bufs, void* packed, float* sumsq, int n_mats, int rows, int cols,
                             long long g_stride, long long b_stride, float momentum, int nesterov, int transpose,
-                            const long long* peer_deltas, int world, cudaStream_t s) {
+                            const long long* peer_deltas, int world, const float* grad_base, const void* shadow_base, cudaStream_t s) {
     if (world > MAX_RANKS || cols % 4) return false;
+    if (n_mats == 0) return true;
     dim3 grid((cols + 127) / 128, (rows + 31) / 32, n_mats);
     rs_muon_prepare_kernel<<<grid, 256, 0, s>>>(grads, bufs, static_cast<__nv_bfloat16*>(packed), sumsq, rows, cols, g_stride, b_stride,
-                                                momentum, nesterov, transpose, make_deltas(peer_deltas, world), world, 1.f / world);
+                                                momentum, nesterov, transpose, make_deltas(peer_deltas, world), world, 1.f / world,
+                                                grad_base, static_cast<const __nv_bfloat16*>(shadow_base));
     return true;
 }
 
@@ -256,26 +286,30 @@ bool launch_adamw_sharded(float* params, const float* grads, void* m, void* v, b
     return true;
 }
 
-// ---- cross-rank readiness flags --------------------------------------------------------------------------------------------
+// ---- cross-rank readiness flags and barrier -------------------------------------------------------------------------------
 // flags[slot * world + src] on every rank holds the last step for which rank `src` has finished producing the data of `slot`
 // (the gradients of one transformer block).  flag_signal publishes this rank's value to every rank after a system-scope
-// fence; flag_wait polls this rank's own copy until every source has reached `value`.  The poll is bounded: when the
-// budget runs out the kernel records code 601 in the status word and returns, so a missing peer fails the step instead
-// of hanging the GPU.  The two kernels run on different GPUs (or at least never wait for one another on one GPU).
-__global__ void flag_signal_kernel(int* flags, PeerDeltas peers, int world, int index, int value) {
+// fence; flag_wait polls this rank's own copy until every source has reached `value`.  The value is a kernel argument or,
+// when `value_word` is given, read from device memory (a step counter bumped on the device: the launches then carry no
+// host state and can be replayed from a CUDA graph).  The poll is bounded: when the budget runs out the kernel records
+// code 601 in the status word and returns, so a missing peer fails the step instead of hanging the GPU.  Kernels that
+// wait for one another always run on different GPUs.
+__global__ void flag_signal_kernel(int* flags, PeerDeltas peers, int world, int index, int value, const int* value_word) {
     const int r = threadIdx.x;
     if (r < world) {
+        const int v = value_word ? *value_word : value;
         __threadfence_system();
-        *reinterpret_cast<volatile int*>(reinterpret_cast<char*>(flags + index) + peers.d[r]) = value;
+        *reinterpret_cast<volatile int*>(reinterpret_cast<char*>(flags + index) + peers.d[r]) = v;
     }
 }
 
-__global__ void flag_wait_kernel(const int* flags, int first, int world, int value, int* status) {
+__global__ void flag_wait_kernel(const int* flags, int first, int world, int value, const int* value_word, int* status) {
     const int r = threadIdx.x;
     if (r < world) {
+        const int v = value_word ? *value_word : value;
         const volatile int* f = flags + first + r;
         const long long start = clock64();
-        while (*f < value) {
+        while (*f < v) {
             if (clock64() - start > kWaitBudgetCycles) { atomicExch(status, 601); break; }
             __nanosleep(256);
         }
@@ -283,15 +317,51 @@ __global__ void flag_wait_kernel(const int* flags, int first, int world, int val
     __threadfence_system();
 }
 
-bool launch_flag_signal(int* flags, const long long* deltas, int world, int index, int value, cudaStream_t s) {
+__global__ void bump_word_kernel(int* word) { *word += 1; }
+
+// Barrier across the ranks of a symmetric flag table, as ONE launch per rank: everything this rank queued on the stream before
+// it is complete when the kernel starts; thread r publishes this rank's next epoch into slot `me` of rank r's table
+// (system-scope fence first, so this rank's earlier peer stores are visible before the flag), then waits until rank r's
+// epoch has arrived in this rank's own table.  The epoch lives in device memory (`epoch_word`, bumped here), so the launch
+// carries no host state.  The wait is bounded like every wait in this code base: status 601 and return when a peer does
+// not arrive within the budget.
+__global__ void peer_barrier_kernel(int* flags, PeerDeltas peers, int world, int me, int* epoch_word, int* status, long long budget) {
+    __shared__ int epoch;
+    if (threadIdx.x == 0) { epoch = *epoch_word + 1; *epoch_word = epoch; }
+    __syncthreads();
+    const int r = threadIdx.x;
+    if (r < world) {
+        __threadfence_system();
+        *reinterpret_cast<volatile int*>(reinterpret_cast<char*>(flags + me) + peers.d[r]) = epoch;
+        const volatile int* f = flags + r;
+        const long long start = clock64();
+        while (*f < epoch) {
+            if (clock64() - start > budget) { atomicExch(status, 601); break; }
+            __nanosleep(128);
+        }
+    }
+    __threadfence_system();
+}
+
+bool launch_flag_signal(int* flags, const long long* deltas, int world, int index, int value, const int* value_word, cudaStream_t s) {
     if (world > MAX_RANKS) return false;
-    flag_signal_kernel<<<1, 32, 0, s>>>(flags, make_deltas(deltas, world), world, index, value);
+    flag_signal_kernel<<<1, 32, 0, s>>>(flags, make_deltas(deltas, world), world, index, value, value_word);
     return true;
 }
 
-bool launch_flag_wait(const int* flags, int first, int world, int value, int* status, cudaStream_t s) {
+bool launch_flag_wait(const int* flags, int first, int world, int value, const int* value_word, int* status, cudaStream_t s) {
     if (world > MAX_RANKS) return false;
-    flag_wait_kernel<<<1, 32, 0, s>>>(flags, first, world, value, status);
+    flag_wait_kernel<<<1, 32, 0, s>>>(flags, first, world, value, value_word, status);
+    return true;
+}
+
+void launch_bump_word(int* word, cudaStream_t s) { bump_word_kernel<<<1, 1, 0, s>>>(word); }
+
+bool launch_peer_barrier(int* flags, const long long* deltas, int world, int me, int* epoch_word, int* status, long long budget_cycles,
+                         cudaStream_t s) {
+    if (world > MAX_RANKS || me < 0 || me >= world) return false;
+    peer_barrier_kernel<<<1, 32, 0, s>>>(flags, make_deltas(deltas, world), world, me, epoch_word, status,
+                                         budget_cycles > 0 ? budget_cycles : kWaitBudgetCycles);
     return true;
 }
 

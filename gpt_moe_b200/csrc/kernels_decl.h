@@ -50,7 +50,7 @@ void launch_muon_normalize(void* packed, const float* sumsq, int n_mats, long lo
 // comm/fused_comm.cu
 bool launch_rs_muon_prepare(const float* const* grads, float* const* bufs, void* packed, float* sumsq, int n_mats, int rows, int cols,
                             long long g_stride, long long b_stride, float momentum, int nesterov, int transpose,
-                            const long long* peer_deltas, int world, cudaStream_t s);
+                            const long long* peer_deltas, int world, const float* grad_base, const void* shadow_base, cudaStream_t s);
 bool launch_muon_apply_push(float* const* weights, void* const* weights_bf16, const void* update, int n_mats, int rows, int cols,
                             long long w_stride, long long wb_stride, float alpha, int transpose, const long long* peer_deltas, int world,
                             cudaStream_t s);
@@ -58,8 +58,11 @@ bool launch_adamw_sharded(float* params, const float* grads, void* m, void* v, b
                           long long n, float lr, float beta1, float beta2, float eps, float bc1, float bc2_sqrt,
                           const long long* grad_deltas, const long long* param_deltas, int world, cudaStream_t s);
 
-bool launch_flag_signal(int* flags, const long long* deltas, int world, int index, int value, cudaStream_t s);
-bool launch_flag_wait(const int* flags, int first, int world, int value, int* status, cudaStream_t s);
+bool launch_flag_signal(int* flags, const long long* deltas, int world, int index, int value, const int* value_word, cudaStream_t s);
+bool launch_flag_wait(const int* flags, int first, int world, int value, const int* value_word, int* status, cudaStream_t s);
+void launch_bump_word(int* word, cudaStream_t s);
+bool launch_peer_barrier(int* flags, const long long* deltas, int world, int me, int* epoch_word, int* status, long long budget_cycles,
+                         cudaStream_t s);
 
 // ---- expert-parallel dispatch / combine over peer memory (comm/ep_comm.cu) -------------------------------------------
 bool launch_ep_push_counts(const int* counts, int* table, const long long* deltas, int world, int me, int experts, cudaStream_t s);

@@ -133,7 +133,6 @@ class GPT(nn.Module):
         self._linear_modules = tuple(m for m in self.modules() if isinstance(m, Linear))
         self.precision_phase = None
         self.set_precision_phase("training")
-        self.engine = None      # set by parallel.ddp_engine when the model is placed on a GPU
 
     def set_sliding_window(self, window: int) -> None:
         """Update the device-resident window and remember the host value (ops that need a host integer read
@@ -153,13 +152,22 @@ class GPT(nn.Module):
         self.precision_phase = phase
 
     def prepare_fp8_weights(self) -> None:
-        """Quantise the weights once for all micro-steps of a gradient-accumulation step."""
-        if self.engine is not None:
-            self.engine.prepare_quantized_weights()
+        """Quantise the MXFP8 weights once, ahead of the micro-steps of a gradient-accumulation step (reference
+        `train.py:379-380`).  On the GPU the quantised copies (row-wise for the forward GEMM, transposed for the
+        input-gradient GEMM) live in `ops.cuda_ops`' parameter-epoch cache: this fills it, later uses hit it until an
+        optimizer step or `clear_fp8_weights` invalidates it.  Nothing to do on the CPU path, which quantises inline."""
+        if not any(p.is_cuda for p in self.parameters()):
+            return
+        from ..ops import mxfp8
+        for block in self.transformer.h:
+            mxfp8.prepare_block_weights(block)
 
     def clear_fp8_weights(self) -> None:
-        if getattr(self, "engine", None) is not None:
-            self.engine.clear_quantized_weights()
+        """Drop the quantised weight copies (before an optimizer step, on a phase change, at exit: reference
+        `train.py:488, 755`, `model/gpt.py:198`)."""
+        if any(p.is_cuda for p in self.parameters()):
+            from ..ops import mxfp8
+            mxfp8.clear_quantized_weights()
 
     def _init_weights(self, module: nn.Module) -> None:
         if isinstance(module, nn.Linear):

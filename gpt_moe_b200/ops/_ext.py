@@ -22,5 +22,6 @@ def load():
     if not fresh:
         builder.build()
     import torch  # noqa: F401  (libtorch must be loaded before the extension)
-    _ext = importlib.import_module("gpt_moe_b200._C")
+    # GM_CHECK_BOUNDS=1 selects the bounds-checked build of the same sources (`_C_checked.so`)
+    _ext = importlib.import_module("gpt_moe_b200." + os.path.splitext(os.path.basename(builder.TARGET))[0])
     return _ext

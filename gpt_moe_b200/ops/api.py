@@ -2,7 +2,16 @@
 
 One function per op.  CUDA tensors go to the sm_100a kernels in `cuda_ops` (and fail loudly if
 the extension is not built); CPU tensors go to the plain-PyTorch definitions in `reference`,
-which are also the oracle of the GPU tests.  There is no third path.
+which are also the oracle of the GPU tests.
+
+Shapes the kernels do not cover stay correct through library or torch ops, and every such call is
+counted in `cuda_ops.path_counts()` under a name that says which one ran, so a benchmark record can
+show that none did:
+  attention   head widths other than 64 / 128x64, padding masks, non-causal -> flash-attn or torch SDPA
+              (`ops/attention_cuda.py`)
+  linear      row pitch not a multiple of 16 bytes (k or n not a multiple of 8)  -> torch `F.linear`
+  rms_norm    widths other than 128*{1,2,4,6,8,12,16}, other dtypes               -> torch ops
+  cross_entropy on materialised logits (evaluation)                              -> torch ops
 """
 from __future__ import annotations
 

@@ -52,17 +52,22 @@ def attention(q: Tensor, k: Tensor, v: Tensor, *, causal: bool = True, window=No
         w = None
     if attn_mask is None and causal:
         from . import attention_tc
+        from .cuda_ops import count_path
         if attention_tc.supported(q, k, v, softcap_value):
+            count_path("attention:tcgen05")
             return attention_tc.attention(q, k, v, window=w, scale=scale, softcap=softcap_value, document_ids=document_ids)
         flash = _flash_attn()
         dv = v.shape[-1]
         if document_ids is None and flash and q.dtype == torch.bfloat16 and dv <= dk and dk <= 256 and softcap_value == 0.0:
             # head sizes the tcgen05 kernel is not built for (e.g. MLA: 128-wide keys, 64-wide values) go to the library kernel;
             # it wants equal widths, so narrower values are zero-padded and the padding columns of the result dropped
+            count_path("attention:flash_attn")
             vp = v if dv == dk else F.pad(v, (0, dk - dv))
             out = flash(q, k, vp, softmax_scale=scale if scale is not None else dk ** -0.5, causal=True,
                         window_size=(w, 0) if w is not None else (-1, -1))
             return out if dv == dk else out[..., :dv]
+    from .cuda_ops import count_path
+    count_path("attention:torch")
     if softcap_value > 0.0:
         return ref.attention(q, k, v, causal=causal, window=w, scale=scale, softcap_value=softcap_value,
                              tanh_backend=tanh_backend, attn_mask=attn_mask, document_ids=document_ids)

@@ -58,6 +58,19 @@ def ext():
     return _proxy
 
 
+_path_counts: dict = {}
+
+
+def count_path(name: str) -> None:
+    """Record that an op ran on path `name` (`attention:tcgen05`, `attention:sdpa`, `linear:torch`, ...)."""
+    _path_counts[name] = _path_counts.get(name, 0) + 1
+
+
+def path_counts() -> dict:
+    """How often each op path ran in this process; a key that does not end in the kernel's own name is a library or torch path."""
+    return dict(_path_counts)
+
+
 def launch_count() -> int:
     """Number of extension launches issued so far by this process."""
     return ext().calls
@@ -266,6 +279,7 @@ def linear_multi(x: Tensor, weights: Sequence[Tensor], precision: str = "default
 def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor], precision: str = "default") -> Tensor:
     k, n = weight.shape[1], weight.shape[0]
     if k % 8 or n % 8 or n < 8:
+        count_path("linear:torch")
         y = F.linear(x.to(BF16), weight.to(BF16))          # shapes TMA cannot address (row pitch not a multiple of 16 bytes)
     else:
         y = linear_multi(x, (weight,), precision)
@@ -296,6 +310,7 @@ def rms_norm(x: Tensor, weight: Optional[Tensor], eps: float) -> Tensor:
     """bf16 output; fp32 or bf16 input; statistics fp32."""
     d = x.shape[-1]
     if x.dtype not in (torch.float32, BF16) or d % 128 or (d // 128) not in (1, 2, 4, 6, 8, 12, 16):
+        count_path("rms_norm:torch")
         return ref.rms_norm(x, weight, eps).to(BF16)
     return _RMSNormFn.apply(x, weight, eps)
 
@@ -472,6 +487,7 @@ def rope_attention_packed(qkv: Tensor, cos, sin, q_scale, k_scale, batch: int, s
     smin = max(smin, -3.0e38)
     smax = min(smax, 3.0e38)
     w = seq_len if window is None else int(window)
+    count_path("attention:tcgen05")
     return _RopeAttentionFn.apply(qkv, cos, sin, q_scale, k_scale, batch, seq_len, hq, hk, d, eps, rms, smin, smax, w,
                                   d ** -0.5 if scale is None else float(scale), float(softcap), doc_start)
 
@@ -659,6 +675,7 @@ def linear_cross_entropy(x, weight, targets, ignore_index=-100):
 
 
 def cross_entropy(logits, targets, ignore_index=-100):
+    count_path("cross_entropy:torch")
     return ref.cross_entropy(logits, targets, ignore_index)
 
 

@@ -3,7 +3,7 @@
 Same update rule and state keys (`step`, `exp_avg`, `exp_avg_sq`) as `torch.optim.AdamW`, which
 the reference uses in fused mode (`model/gpt.py:284-293`), so optimizer state dicts interchange.
 On CUDA all parameters of a group are updated by one multi-tensor kernel launch
-(`csrc/optim/adamw.cu`) that also refreshes the bf16 compute copy of each weight; moments may be
+(`csrc/fused/loss_optim.cu`) that also refreshes the bf16 compute copy of each weight; moments may be
 bf16 while parameters stay fp32 (reference `runtime/precision.py:52-75`).
 """
 from __future__ import annotations

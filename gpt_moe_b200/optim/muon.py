@@ -10,8 +10,9 @@ State key per parameter: `momentum_buffer` (full shape), as in the reference.
 Sharding (new): with `owner_of` set by the engine, a rank updates only the matrices it owns;
 the engine then all-gathers the updated weights.  The reference repeats the whole computation on
 every rank.  On CUDA the momentum update, the Gram/Newton-Schulz GEMMs and the final
-GEMM+weight update run as hand-written kernels (`csrc/optim/polar.cu`); here is the host
-orchestration and the CPU path.
+weight update run as hand-written kernels (`csrc/fused/loss_optim.cu`, `csrc/comm/fused_comm.cu`, the
+tcgen05 GEMM in `csrc/gemm/gemm_bf16.cu` driven by `ops/cuda_ops.py::polar_express_bf16`); here is
+the host orchestration and the CPU path.
 """
 from __future__ import annotations
 

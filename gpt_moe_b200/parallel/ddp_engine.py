@@ -54,7 +54,7 @@ class HostEngine:
     """Gradient reduction + sharded optimizer step with `torch.distributed` collectives."""
 
     def __init__(self, model: nn.Module, training_config, optimizers: Dict[str, torch.optim.Optimizer],
-                 dp_group=None, ep_size: int = 1) -> None:
+                 dp_group=None, ep_size: int = 1, expert_replica_group=None) -> None:
         self.model = model
         self.cfg = training_config
         self.optimizers = optimizers
@@ -65,9 +65,13 @@ class HostEngine:
         self.shard_optimizer = bool(training_config.shard_muon) and self.world > 1
         named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
         self.expert_names = {n for n, _ in named if ".mlp.experts." in n} if ep_size > 1 else set()
-        # replicas of one expert exist only when the expert-parallel group is smaller than the world
-        self.expert_replica_group = None
+        # replicas of one expert exist only when the expert-parallel group is smaller than the world: the ranks with the
+        # same position in their expert-parallel group (rank % ep_size) hold the same experts and form a replica group
         self.expert_replicas = self.world // ep_size if ep_size > 1 else 1
+        if self.expert_replicas > 1 and expert_replica_group is None:
+            raise ValueError("expert_parallel_size smaller than the world size needs the expert replica group "
+                             "(ranks with equal rank % expert_parallel_size)")
+        self.expert_replica_group = expert_replica_group if self.expert_replicas > 1 else None
         self.dense = [(n, p) for n, p in named if n not in self.expert_names]
         self.experts = [(n, p) for n, p in named if n in self.expert_names]
         self.owners: Dict[str, int] = {}
@@ -170,20 +174,30 @@ class HostEngine:
             opt.zero_grad(set_to_none=True)
 
     # ---- checkpoint helpers ----------------------------------------------------------------------
+    def contributes_state(self, name: str) -> bool:
+        """Does this rank hand in the optimizer state of parameter `name` at save time?  Exactly one rank does: the owner of
+        a sharded tensor (rank 0 when the optimizer is replicated), and for an expert its holder in the first
+        expert-parallel group."""
+        if name in self.expert_names:
+            return self.rank < self.ep_size
+        return self.owners.get(name, 0) == self.rank
+
+    def drop_foreign_state(self) -> None:
+        """After a resume every rank has loaded the full optimizer state; keep only what this rank updates, so that a stale
+        copy of someone else's state can never be saved."""
+        if not self.shard_optimizer:
+            return
+        foreign = {id(p) for n, p in self.dense if self.owners.get(n, self.rank) != self.rank}
+        for opt in self.optimizers.values():
+            for p in [p for p in opt.state if id(p) in foreign]:
+                del opt.state[p]
+
     def full_optimizer_state_dicts(self) -> Dict[str, dict]:
-        """Optimizer state dicts in the replicated layout: owners contribute the state of what they own."""
-        out = {}
-        for name, opt in self.optimizers.items():
-            sd = opt.state_dict()
-            if self.shard_optimizer:
-                gathered: List[Optional[dict]] = [None] * self.world
-                dist.all_gather_object(gathered, {k: _to_cpu(v) for k, v in sd["state"].items()}, group=self.group)
-                merged = {}
-                for part in gathered:
-                    merged.update(part)
-                sd = {"state": dict(sorted(merged.items())), "param_groups": sd["param_groups"]}
-            out[name] = sd
-        return out
+        """Optimizer state dicts in the unsharded torch layout (collective): each entry comes from the one rank that
+        `contributes_state` names, matched by parameter name and keyed by the unsharded model's parameter order."""
+        from ..checkpointing.checkpoint import merge_optimizer_state
+        return {name: merge_optimizer_state(self.model, opt, self.contributes_state, self.group)
+                for name, opt in self.optimizers.items()}
 
 
 def _to_cpu(obj):

@@ -37,7 +37,7 @@ class EPWorkspace:
     receive buffer per MoE layer (it doubles as the saved grouped-GEMM input of that layer, so nothing is copied)."""
 
     def __init__(self, group, slots: int, d: int, experts: int, device, capacity_factor: float = 0.0) -> None:
-        from .fused_engine import SymmetricBuffer
+        from .fused_engine import PeerBarrier, SymmetricBuffer
         self.group = group
         self.world, self.rank = du.world_size(group), du.get_rank(group)
         assert experts % self.world == 0
@@ -51,6 +51,7 @@ class EPWorkspace:
         self.ret = self._make(self.cap_rows * d, BF16)
         self.grad_recv = self._make(self.cap_rows * d, BF16)
         self.layer_recv: Dict[int, object] = {}
+        self._barrier = PeerBarrier(device, group)
 
     def recv_for(self, layer_key: int):
         buf = self.layer_recv.get(layer_key)
@@ -62,7 +63,8 @@ class EPWorkspace:
         return buf.tensor[: self.cap_rows * self.d].view(self.cap_rows, self.d)
 
     def barrier(self) -> None:
-        self.table.barrier()
+        """Bounded device-side barrier of the expert-parallel group (status 601 if a peer never arrives)."""
+        self._barrier.sync()
 
 
 _workspaces: Dict[tuple, EPWorkspace] = {}

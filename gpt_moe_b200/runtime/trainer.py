@@ -120,8 +120,9 @@ class Trainer:
             convert_to_bf16(self.raw_gpt_model, cfg.bf16_weights_params_and_scales, cfg.keep_1d_weights_params_and_scales_in_fp32)
         self.gpt_model = self.raw_gpt_model
 
-        # expert-parallel groups: consecutive ranks form one group
-        self.ep_group = None
+        # expert-parallel groups: consecutive ranks form one group; ranks at the same position of their groups hold the
+        # same experts and form an expert replica group (their expert gradients are summed, nobody else's)
+        self.ep_group = self.expert_replica_group = None
         if self.ep_size > 1:
             from ..parallel.ep import attach_expert_parallel
             for start in range(0, self.world_size, self.ep_size):
@@ -129,6 +130,12 @@ class Trainer:
                 group = dist.new_group(ranks)
                 if self.rank in ranks:
                     self.ep_group = group
+            if self.world_size > self.ep_size:
+                for position in range(self.ep_size):
+                    ranks = list(range(position, self.world_size, self.ep_size))
+                    group = dist.new_group(ranks)
+                    if self.rank in ranks:
+                        self.expert_replica_group = group
             attach_expert_parallel(self.raw_gpt_model, self.ep_group,
                                    fused=self.device_type == "cuda" and cfg.use_fused_collectives,
                                    capacity_factor=cfg.ep_capacity_factor)
@@ -140,7 +147,8 @@ class Trainer:
             if set(self.optimizers) != set(optimizer_state_dicts):
                 raise ValueError("checkpoint optimizer names differ from the current run")
             for name, opt in self.optimizers.items():
-                opt.load_state_dict(optimizer_state_dicts[name])
+                # saved files hold the unsharded layout: pick this rank's entries by parameter name
+                opt.load_state_dict(ckpt.localize_optimizer_state(self.raw_gpt_model, opt, optimizer_state_dicts[name]))
             du.barrier()
         configure_adamw_moments(self.optimizers["adamw"], cfg.use_bf16_adamw_moments)
 
@@ -200,8 +208,14 @@ class Trainer:
             return _LocalEngine(self.optimizers)
         if self.device_type == "cuda":
             from ..parallel.fused_engine import build_cuda_engine
-            return build_cuda_engine(self.raw_gpt_model, cfg, self.optimizers, ep_size=self.ep_size, ep_group=self.ep_group)
-        return HostEngine(self.raw_gpt_model, cfg, self.optimizers, dp_group=None, ep_size=self.ep_size)
+            engine = build_cuda_engine(self.raw_gpt_model, cfg, self.optimizers, ep_size=self.ep_size, ep_group=self.ep_group,
+                                       expert_replica_group=self.expert_replica_group)
+        else:
+            engine = HostEngine(self.raw_gpt_model, cfg, self.optimizers, dp_group=None, ep_size=self.ep_size,
+                                expert_replica_group=self.expert_replica_group)
+        if cfg.resume_from_checkpoint and hasattr(engine, "drop_foreign_state"):
+            engine.drop_foreign_state()
+        return engine
 
     def _init_schedules(self, state: Optional[dict]) -> None:
         cfg = self.cfg

@@ -163,3 +163,104 @@ def test_two_stage_pipeline_matches_single_process(tmp_path):
             parts[2] = str(int(parts[2]) + 1)
             name = ".".join(parts)
         assert torch.allclose(got, full[name], atol=2e-4, rtol=1e-3), name
+
+
+def test_expert_replicas_reduce_only_among_themselves(tmp_path):
+    """World 4 with expert_parallel_size 2: ranks 0/2 and 1/3 hold the same experts.  Expert gradients are summed over those
+    replica pairs only (and nothing else's), so the run reproduces the single-process result and the replicas stay equal."""
+    results = run_ranks(_train, 4, tmp_path, {"moe_top_k": 2}, {"expert_parallel_size": 2, "shard_muon": True}, 2, join_timeout=480)
+    oracle_losses, oracle_state = _single({"moe_top_k": 2}, {}, 2, 4)
+    mean_losses = [sum(r["losses"][i] for r in results) / 4 for i in range(2)]
+    assert mean_losses == pytest.approx(oracle_losses, abs=1e-3)
+    for r in results:
+        assert set(r["state"]) == set(oracle_state)
+        for name, want in oracle_state.items():
+            assert torch.allclose(r["state"][name], want, atol=3e-4, rtol=1e-3), name
+        assert r["muon_state_count"] == 26          # every Muon matrix of the unsharded model exactly once
+
+
+def _train_save_resume(rank, world, train_kw, ckpt_dir, resume):
+    """Three steps and a save; or (resume) a fresh trainer from that save, one more step and a second save."""
+    import os
+    from gpt_moe_b200.runtime.trainer import Trainer
+    gc, tc = _config(moe_top_k=2)
+    for k, v in train_kw.items():
+        setattr(tc, k, v)
+    tc.checkpoint_dir = os.path.join(ckpt_dir, "resumed" if resume else "first")
+    if resume:
+        first = os.path.join(ckpt_dir, "first")
+        weights = [f for f in os.listdir(first) if f.startswith("model_step_0000002")][0]
+        tc.resume_from_checkpoint = True
+        tc.resume_checkpoint_path = os.path.join(first, weights)
+        tc.resume_state_dict_path = os.path.join(first, "training_state_step_0000002.pt")
+    trainer = Trainer(gc, tc, device_type="cpu", quiet=True)
+    rows = tc.gpu_batch_size_train
+    batches = _batches(4, rows * world, tc.seq_len_train, gc.vocab_size)
+    steps = range(3, 4) if resume else range(4)
+    for i in steps:
+        mine = batches[i][rank * rows: (rank + 1) * rows]
+        trainer.train_step([(mine[:, :-1].contiguous(), mine[:, 1:].contiguous(), None)])
+        if not resume and i == 2:
+            trainer.save(2, 0.0, None)
+    trainer.save(3, 0.0, None)
+    return {"dir": tc.checkpoint_dir}
+
+
+@pytest.mark.parametrize("ep", [1, 2])
+def test_sharded_checkpoint_resume_saves_the_same_state_as_an_uninterrupted_run(tmp_path, ep):
+    """Two ranks with the sharded optimizer (and with expert parallelism): save after step 2, resume in fresh processes, take
+    step 3 and save again.  Weights and every optimizer entry of that second save equal the uninterrupted run's save after
+    step 3 — stale momentum of non-owned matrices or expert state keyed by a local index would show up here."""
+    import os
+    from safetensors.torch import load_file
+    kw = {"expert_parallel_size": ep, "shard_muon": True}
+    work, ckpt_dir = tmp_path / "work", tmp_path / "ckpt"
+    for d in (work / "a", work / "b", ckpt_dir):
+        os.makedirs(d)
+    run_ranks(_train_save_resume, 2, work / "a", kw, str(ckpt_dir), False)
+    run_ranks(_train_save_resume, 2, work / "b", kw, str(ckpt_dir), True)
+
+    def load(sub):
+        folder = ckpt_dir / sub
+        weights = [f for f in os.listdir(folder) if f.startswith("model_step_0000003")][0]
+        return load_file(str(folder / weights)), torch.load(str(folder / "training_state_step_0000003.pt"), weights_only=False)
+
+    w_first, s_first = load("first")
+    w_resumed, s_resumed = load("resumed")
+    assert set(w_first) == set(w_resumed)
+    for name in w_first:
+        assert torch.allclose(w_first[name], w_resumed[name], atol=1e-6), name
+    for opt in ("muon", "adamw"):
+        a, b = s_first["optimizer_state_dicts"][opt], s_resumed["optimizer_state_dicts"][opt]
+        assert a["param_groups"][0]["params"] == b["param_groups"][0]["params"]
+        assert set(a["state"]) == set(b["state"]) and len(a["state"]) > 0
+        for key in a["state"]:
+            for field, value in a["state"][key].items():
+                other = b["state"][key][field]
+                if isinstance(value, torch.Tensor):
+                    assert torch.allclose(value.float(), other.float(), atol=1e-6), (opt, key, field)
+    assert len(s_first["optimizer_state_dicts"]["muon"]["state"]) == 26      # unsharded layout: every Muon matrix once
+
+
+def _pipeline_warmup(rank, world):
+    from gpt_moe_b200.runtime.trainer import Trainer
+    from gpt_moe_b200.runtime.warmup import kernel_warmup
+    gc, tc = _config()
+    tc.parallel_mode = "pp"
+    tc.total_tokens_per_step_train = 2 * tc.gpu_batch_size_train * tc.seq_len_train
+    trainer = Trainer(gc, tc, device_type="cpu", quiet=True)
+    before = {n: p.detach().clone() for n, p in trainer.raw_gpt_model.named_parameters()}
+    rng = torch.get_rng_state()
+    elapsed = kernel_warmup(trainer.run, num_train_steps=1)
+    same = all(torch.equal(p.detach(), before[n]) for n, p in trainer.raw_gpt_model.named_parameters())
+    empty_state = all(not entry for o in trainer.optimizers.values() for entry in o.state_dict()["state"].values())
+    return {"elapsed": elapsed, "same": same, "empty_state": empty_state, "rng": torch.equal(rng, torch.get_rng_state()),
+            "tokens": trainer.train_tokens_processed}
+
+
+def test_pipeline_warmup_runs_both_stages_and_restores(tmp_path):
+    """The warm-up in pipeline mode takes real 1F1B steps and a forward-only pass on both stages, then puts weights,
+    optimizer state, RNG and counters back exactly."""
+    results = run_ranks(_pipeline_warmup, 2, tmp_path)
+    for r in results:
+        assert r["elapsed"] > 0.0 and r["same"] and r["empty_state"] and r["rng"] and r["tokens"] == 0

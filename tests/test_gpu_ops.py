@@ -355,6 +355,31 @@ def test_bounded_wait_gives_up_and_reports(ops):
     assert rel(d, a.float() @ a.float().t()) < BF16_TOL
 
 
+def test_peer_barrier_completes_alone_and_gives_up_on_a_missing_peer(ops):
+    """The device-side barrier on one GPU: a group of one passes at once and bumps its epoch; a group of two whose second
+    member's slot nothing writes runs out of its (shortened) budget, records 601 and returns with the context usable.  Flag
+    values can also come from a device word."""
+    c = ops.ext()
+    c.reset_status()
+    flags = torch.zeros(4, dtype=torch.int32, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c.peer_barrier(flags, [0], 0, epoch)
+    c.peer_barrier(flags, [0], 0, epoch)
+    torch.cuda.synchronize()
+    assert c.read_status() == 0 and epoch.item() == 2 and flags.tolist() == [2, 0, 0, 0]
+    c.peer_barrier(flags, [0, 0], 0, epoch, 200_000_000)      # "rank 1" shares this table and never publishes into slot 1
+    torch.cuda.synchronize()
+    assert c.read_status() == 601 and flags.tolist() == [3, 0, 0, 0]
+    c.reset_status()
+    word = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c.bump_word(word)
+    c.bump_word(word)
+    c.flag_signal(flags, [0], 2, 0, word)                     # value read from the device word
+    c.flag_wait(flags, 2, 1, 0, word)
+    torch.cuda.synchronize()
+    assert c.read_status() == 0 and flags.tolist() == [3, 0, 2, 0]
+
+
 @pytest.mark.parametrize("dqk,window", [(64, 200), (128, 2000)])
 def test_attention_kernels_with_logit_softcapping(ops, dqk, window):
     """softcap * tanh(scale * s / softcap) before the softmax, forward and backward (hardware tanh.approx)."""
