@@ -177,7 +177,8 @@ std::vector<torch::Tensor> mxfp8_quantize(const torch::Tensor& x, const c10::opt
     const int64_t batch = x.dim() == 3 ? x.size(0) : 1, rows = x.size(-2), cols = x.size(-1);
     GM_CHECK(batch == 1 || rows % 128 == 0 || x.is_contiguous(), "mxfp8_quantize: batched input must be contiguous");
     auto q = torch::empty(x.sizes(), x.options().dtype(torch::kUInt8));
-    auto sf = torch::zeros({batch, sf_records(rows, cols) * 512}, x.options().dtype(torch::kUInt8));
+    // not cleared: bytes of rows that exist are all written; the rest belongs to rows the GEMM clips
+    auto sf = torch::empty({batch, sf_records(rows, cols) * 512}, x.options().dtype(torch::kUInt8));
     for (int64_t z = 0; z < batch; ++z) {
         const auto* src = static_cast<const at::BFloat16*>(x.data_ptr()) + (x.dim() == 3 ? z * x.stride(0) : 0);
         gm::launch_quantize_rows(src, q.data_ptr<uint8_t>() + z * rows * cols, sf.data_ptr<uint8_t>() + z * sf.stride(0), rows,
@@ -187,17 +188,20 @@ std::vector<torch::Tensor> mxfp8_quantize(const torch::Tensor& x, const c10::opt
     return {q, sf};
 }
 
-// w [.., rows, cols] bf16 contiguous -> (q [.., cols, rows] e4m3, scales) with the groups of 32 running along `rows`
-std::vector<torch::Tensor> mxfp8_quantize_transposed(const torch::Tensor& w) {
+// w [.., rows, cols] bf16 contiguous -> (q [.., rows, cols], scales along cols, qt [.., cols, rows], scales along the original rows)
+std::vector<torch::Tensor> mxfp8_quantize_weight(const torch::Tensor& w) {
     c10::cuda::CUDAGuard guard(w.device());
-    GM_CHECK(w.is_cuda() && w.scalar_type() == torch::kBFloat16 && w.is_contiguous() && (w.dim() == 2 || w.dim() == 3), "mxfp8_quantize_transposed wants a contiguous bf16 CUDA tensor");
+    GM_CHECK(w.is_cuda() && w.scalar_type() == torch::kBFloat16 && w.is_contiguous() && (w.dim() == 2 || w.dim() == 3), "mxfp8_quantize_weight wants a contiguous bf16 CUDA tensor");
     const int64_t batch = w.dim() == 3 ? w.size(0) : 1, rows = w.size(-2), cols = w.size(-1);
-    GM_CHECK(rows % 32 == 0, "mxfp8_quantize_transposed: the contraction dimension must be a multiple of 32");
-    auto q = w.dim() == 3 ? torch::empty({batch, cols, rows}, w.options().dtype(torch::kUInt8)) : torch::empty({cols, rows}, w.options().dtype(torch::kUInt8));
-    auto sf = torch::zeros({batch, sf_records(cols, rows) * 512}, w.options().dtype(torch::kUInt8));
-    gm::launch_quantize_transposed(w.data_ptr(), q.data_ptr(), sf.data_ptr(), static_cast<int>(batch), static_cast<int>(rows), static_cast<int>(cols),
-                                   sf.stride(0), current_stream());
-    return {q, sf};
+    GM_CHECK(rows % 32 == 0 && cols % 32 == 0, "mxfp8_quantize_weight: both dimensions must be multiples of 32");
+    auto opt = w.options().dtype(torch::kUInt8);
+    auto q = torch::empty(w.sizes(), opt);
+    auto qt = w.dim() == 3 ? torch::empty({batch, cols, rows}, opt) : torch::empty({cols, rows}, opt);
+    auto sf = torch::empty({batch, sf_records(rows, cols) * 512}, opt);
+    auto sft = torch::empty({batch, sf_records(cols, rows) * 512}, opt);
+    gm::launch_quantize_weight_dual(w.data_ptr(), q.data_ptr(), sf.data_ptr(), qt.data_ptr(), sft.data_ptr(), static_cast<int>(batch),
+                                    static_cast<int>(rows), static_cast<int>(cols), sf.stride(0), sft.stride(0), current_stream());
+    return {q, sf, qt, sft};
 }
 
 // d [.., M, N] bf16 = alpha * a [.., M, K] b [.., N, K]^T from e4m3 bytes and their scale records.
@@ -213,7 +217,7 @@ void gemm_mxfp8(const torch::Tensor& a, const torch::Tensor& sfa, const torch::T
     GM_CHECK(b.size(-1) == p.K && b.size(-2) == p.N && p.K % 128 == 0, "mxfp8 GEMM shapes (K must be a multiple of 128)");
     p.grouped = tile_expert.has_value();
     if (p.grouped) {
-        GM_CHECK(a.dim() == 2 && b.dim() == 3 && d.dim() == 2 && num_m_tiles.has_value() && a.size(0) % 128 == 0, "grouped mxfp8 operand ranks");
+        GM_CHECK(a.dim() == 2 && b.dim() == 3 && d.dim() == 2 && num_m_tiles.has_value() && a.size(0) % 256 == 0, "grouped mxfp8 operand ranks (rows padded to 256)");
         p.tile_expert = tile_expert->data_ptr<int>();
         p.num_m_tiles = num_m_tiles->data_ptr<int>();
         p.batch = 1;
@@ -234,7 +238,11 @@ void gemm_mxfp8(const torch::Tensor& a, const torch::Tensor& sfa, const torch::T
     const CUtensorMap& ta = cached_map(a.data_ptr(), 1, p.K, a.size(-2), ab, p.K, a.size(-2) * static_cast<uint64_t>(p.K), 128, 128, 128);
     const CUtensorMap& tb = cached_map(b.data_ptr(), 1, p.K, p.N, bb, p.K, static_cast<uint64_t>(p.N) * p.K, 128, 128, 128);
     const CUtensorMap& td = cached_map(d.data_ptr(), 2, p.N, p.M, d.dim() == 3 ? d.size(0) : 1, d.stride(-2) * 2, d.dim() == 3 ? d.stride(0) * 2 : 0, 64, 128, 128);
-    cudaError_t e = gm::launch_gemm_mxfp8(ta, tb, td, p, sm_count(), current_stream());
+    // scale arrays as [records, 128 words]: one TMA row per 512-byte record, no swizzle
+    GM_CHECK(reinterpret_cast<uintptr_t>(sfa.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(sfb.data_ptr()) % 16 == 0, "scale arrays must be 16-byte aligned");
+    const CUtensorMap& tsfa = cached_map(sfa.data_ptr(), 4, 128, sfa.numel() / 512, 1, 512, 0, 128, 1, 0);
+    const CUtensorMap& tsfb = cached_map(sfb.data_ptr(), 4, 128, sfb.numel() / 512, 1, 512, 0, 128, 1, 0);
+    cudaError_t e = gm::launch_gemm_mxfp8(ta, tb, td, tsfa, tsfb, p, sm_count(), current_stream());
     GM_CHECK(e == cudaSuccess, cudaGetErrorString(e));
 }
 
@@ -329,7 +337,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("seg_ends") = py::none(), py::arg("symmetric") = false,
           py::arg("batch_sumsq") = py::none(), py::arg("scale_mode") = 0);
     m.def("mxfp8_quantize", &mxfp8_quantize, py::arg("x"), py::arg("rows_limit") = py::none());
-    m.def("mxfp8_quantize_transposed", &mxfp8_quantize_transposed);
+    m.def("mxfp8_quantize_weight", &mxfp8_quantize_weight);
     m.def("gemm_mxfp8", &gemm_mxfp8, py::arg("a"), py::arg("sfa"), py::arg("b"), py::arg("sfb"), py::arg("d"), py::arg("alpha") = 1.0,
           py::arg("tile_expert") = py::none(), py::arg("num_m_tiles") = py::none());
     m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0,

@@ -19,10 +19,26 @@ const float* fptr(const OptTensor& t) { return t.has_value() ? t->data_ptr<float
 void check_bf16(const Tensor& t, const char* name) {
     GM_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.is_contiguous(), std::string(name) + " must be a contiguous CUDA bf16 tensor");
 }
+// MXFP8 copy of a [rows, cols] matrix: e4m3 payload (uint8 [rows, cols]) and scale records (uint8 [ceil(rows/128) * ceil(cols/128) * 512]).
+// The scale array is not cleared: every byte that belongs to a row the producer writes is written by it, the others belong to
+// rows the GEMM clips.
+struct QuantOut { Tensor q, sf; uint8_t* qp = nullptr; uint8_t* sp = nullptr; };
+QuantOut alloc_quant(bool wanted, int64_t rows, int64_t cols, const Tensor& like) {
+    QuantOut o;
+    if (!wanted) return o;
+    GM_CHECK(cols % 32 == 0, "MXFP8 copy: the row width must be a multiple of 32");
+    auto opt = like.options().dtype(torch::kUInt8);
+    o.q = torch::empty({rows, cols}, opt);
+    o.sf = torch::empty({((rows + 127) / 128) * ((cols + 127) / 128) * 512}, opt);
+    o.qp = o.q.data_ptr<uint8_t>();
+    o.sp = o.sf.data_ptr<uint8_t>();
+    return o;
+}
 
-// y = rmsnorm(x_new) * w with x_new = alpha*x + beta*branch when a branch is given.  Returns (y, rstd, x_new).
+// y = rmsnorm(x_new) * w with x_new = alpha*x + beta*branch when a branch is given.  Returns (y, rstd, x_new) and, with
+// `quantize`, the MXFP8 copy of y as two more tensors (payload, scale records).
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const OptTensor& w, double eps, const OptTensor& branch, const OptTensor& alpha,
-                                const OptTensor& beta) {
+                                const OptTensor& beta, bool quantize) {
     c10::cuda::CUDAGuard guard(x.device());
     GM_CHECK(x.is_cuda() && x.is_contiguous(), "rmsnorm input must be contiguous");
     GM_CHECK(x.scalar_type() == torch::kFloat32 || x.scalar_type() == torch::kBFloat16, "rmsnorm input must be fp32 or bf16");
@@ -36,9 +52,11 @@ std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const OptTensor& w, double eps,
         check_bf16(*branch, "branch");
         x_new = torch::empty_like(x);
     }
+    QuantOut qo = alloc_quant(quantize, rows, d, x);
     launch_rmsnorm_fwd(x.data_ptr(), x.scalar_type() == torch::kFloat32, branch.has_value() ? branch->data_ptr() : nullptr,
-                       fptr(alpha), fptr(beta), x_new.data_ptr(), fptr(w), y.data_ptr(), rstd.data_ptr<float>(), rows, d,
+                       fptr(alpha), fptr(beta), x_new.data_ptr(), fptr(w), y.data_ptr(), rstd.data_ptr<float>(), qo.qp, qo.sp, rows, d,
                        static_cast<float>(eps), stream());
+    if (quantize) return {y, rstd, x_new, qo.q, qo.sf};
     return {y, rstd, x_new};
 }
 
@@ -88,16 +106,19 @@ void rope_qknorm_fwd(const Tensor& x, Tensor& out, const OptTensor& cos_t, const
     const long long tokens = x.size(0);
     GM_CHECK(launch_rope_qknorm(false, head_dim, x.data_ptr(), nullptr, out.data_ptr(), fptr(cos_t), fptr(sin_t), fptr(q_scale),
                                 fptr(k_scale), nullptr, tokens, seq_len, q_heads, k_heads, x.stride(0), out.stride(0),
-                                static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), copy_cols, nullptr, 0, stream()),
+                                static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), copy_cols, nullptr, 0,
+                                nullptr, nullptr, 0, stream()),
              "unsupported head size for rope_qknorm");
 }
 
 // backward: dx written into `dx` (layout of x) for the q and k heads; returns dscale [q_heads + k_heads] (fp32)
 // `dq32` (optional, fp32 [tokens, q_heads * head_dim]): gradients of the query heads in full precision; when given, the query
 // columns of `dy` are not read.
-Tensor rope_qknorm_bwd(const Tensor& x, const Tensor& dy, Tensor& dx, const OptTensor& cos_t, const OptTensor& sin_t,
-                       const OptTensor& q_scale, const OptTensor& k_scale, int64_t seq_len, int64_t q_heads, int64_t k_heads,
-                       int64_t head_dim, double eps, bool rms, double smin, double smax, const OptTensor& dq32) {
+// `quantize`: also return the MXFP8 copy (payload, scale records) of the whole gradient row of width dx.size(1) — the rotated /
+// normalised heads as written here plus the trailing columns of dy (value-head gradients) that pass through unchanged.
+std::vector<Tensor> rope_qknorm_bwd(const Tensor& x, const Tensor& dy, Tensor& dx, const OptTensor& cos_t, const OptTensor& sin_t,
+                                    const OptTensor& q_scale, const OptTensor& k_scale, int64_t seq_len, int64_t q_heads, int64_t k_heads,
+                                    int64_t head_dim, double eps, bool rms, double smin, double smax, const OptTensor& dq32, bool quantize) {
     c10::cuda::CUDAGuard guard(x.device());
     const long long tokens = x.size(0);
     const int heads = q_heads + k_heads;
@@ -107,14 +128,21 @@ Tensor rope_qknorm_bwd(const Tensor& x, const Tensor& dy, Tensor& dx, const OptT
     if (dq32.has_value())
         GM_CHECK(dq32->scalar_type() == torch::kFloat32 && dq32->is_contiguous() && dq32->numel() == tokens * q_heads * head_dim,
                  "dq32 must be a contiguous fp32 [tokens, q_heads * head_dim] tensor");
+    const int width = dx.size(1);
+    const int copy_cols = quantize ? width - heads * static_cast<int>(head_dim) : 0;
+    if (quantize) GM_CHECK(dx.data_ptr() == dy.data_ptr() && width % 32 == 0 && copy_cols >= 0 && copy_cols % 32 == 0 && head_dim % 32 == 0,
+                           "rope_qknorm_bwd with an MXFP8 copy runs in place on the full packed gradient rows");
+    QuantOut qo = alloc_quant(quantize, tokens, width, x);
     GM_CHECK(launch_rope_qknorm(true, head_dim, x.data_ptr(), dy.data_ptr(), dx.data_ptr(), fptr(cos_t), fptr(sin_t), fptr(q_scale),
                                 fptr(k_scale), partial.data_ptr<float>(), tokens, seq_len, q_heads, k_heads, x.stride(0),
-                                dy.stride(0), static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), 0,
-                                dq32.has_value() ? dq32->data_ptr<float>() : nullptr, dq32.has_value() ? q_heads * head_dim : 0, stream()),
+                                dy.stride(0), static_cast<float>(eps), rms, static_cast<float>(smin), static_cast<float>(smax), copy_cols,
+                                dq32.has_value() ? dq32->data_ptr<float>() : nullptr, dq32.has_value() ? q_heads * head_dim : 0,
+                                qo.qp, qo.sp, width, stream()),
              "unsupported head size for rope_qknorm");
     Tensor dscale = torch::empty({heads}, partial.options());
     launch_column_sum(partial.data_ptr<float>(), dscale.data_ptr<float>(), blocks, heads, 0, stream());
-    return dscale;
+    if (quantize) return {dscale, qo.q, qo.sf};
+    return {dscale};
 }
 
 // Counted routing.  Returns (dest[S], src_of_row[cap], seg_ends[E], counts[E], tile_expert[cap/128], meta[2]).
@@ -136,15 +164,17 @@ std::vector<Tensor> route(const Tensor& top_idx, int64_t experts) {
     return {dest, src, seg, counts, tiles, meta};
 }
 
-Tensor gather_rows(const Tensor& hidden, const Tensor& src_of_row, const Tensor& meta, int64_t top_k) {
+std::vector<Tensor> gather_rows(const Tensor& hidden, const Tensor& src_of_row, const Tensor& meta, int64_t top_k, bool quantize) {
     c10::cuda::CUDAGuard guard(hidden.device());
     check_bf16(hidden, "hidden");
     const int d = hidden.size(-1);
     GM_CHECK(d % 8 == 0, "row width must be a multiple of 8");
     const int cap = src_of_row.numel();
     Tensor packed = torch::empty({cap, d}, hidden.options());
-    launch_gather_rows(hidden.data_ptr(), src_of_row.data_ptr<int>(), meta.data_ptr<int>(), packed.data_ptr(), d, top_k, cap, stream());
-    return packed;
+    QuantOut qo = alloc_quant(quantize, cap, d, hidden);
+    launch_gather_rows(hidden.data_ptr(), src_of_row.data_ptr<int>(), meta.data_ptr<int>(), packed.data_ptr(), qo.qp, qo.sp, d, top_k, cap, stream());
+    if (quantize) return {packed, qo.q, qo.sf};
+    return {packed};
 }
 
 Tensor combine_fwd(const Tensor& y, const Tensor& dest, const Tensor& gates) {
@@ -157,15 +187,17 @@ Tensor combine_fwd(const Tensor& y, const Tensor& dest, const Tensor& gates) {
     return out;
 }
 
-std::vector<Tensor> combine_bwd(const Tensor& dout, const Tensor& y, const Tensor& src_of_row, const Tensor& gates, const Tensor& meta) {
+std::vector<Tensor> combine_bwd(const Tensor& dout, const Tensor& y, const Tensor& src_of_row, const Tensor& gates, const Tensor& meta, bool quantize) {
     c10::cuda::CUDAGuard guard(y.device());
     check_bf16(dout, "dout");
     check_bf16(y, "y");
     const int top_k = gates.size(1), d = y.size(-1), cap = src_of_row.numel();
     Tensor dy = torch::empty_like(y);
     Tensor dgates = torch::zeros_like(gates);
+    QuantOut qo = alloc_quant(quantize, cap, d, y);
     launch_combine_bwd(dout.data_ptr(), y.data_ptr(), src_of_row.data_ptr<int>(), gates.data_ptr<float>(), meta.data_ptr<int>(),
-                       dy.data_ptr(), dgates.data_ptr<float>(), d, top_k, cap, stream());
+                       dy.data_ptr(), dgates.data_ptr<float>(), qo.qp, qo.sp, d, top_k, cap, stream());
+    if (quantize) return {dy, dgates, qo.q, qo.sf};
     return {dy, dgates};
 }
 
@@ -179,7 +211,7 @@ int act_kind(const std::string& name) {
     return -1;
 }
 
-Tensor activation_fwd(const Tensor& pre, const std::string& name, const OptTensor& meta) {
+std::vector<Tensor> activation_fwd(const Tensor& pre, const std::string& name, const OptTensor& meta, bool quantize) {
     c10::cuda::CUDAGuard guard(pre.device());
     check_bf16(pre, "pre");
     const int kind = act_kind(name);
@@ -189,11 +221,14 @@ Tensor activation_fwd(const Tensor& pre, const std::string& name, const OptTenso
     auto sizes = pre.sizes().vec();
     sizes.back() = h;
     Tensor act = torch::empty(sizes, pre.options());
-    launch_activation_fwd(pre.data_ptr(), act.data_ptr(), meta.has_value() ? meta->data_ptr<int>() : nullptr, rows, h, kind, stream());
-    return act;
+    GM_CHECK(!quantize || h % 32 == 0, "activation with an MXFP8 copy: width must be a multiple of 32");
+    QuantOut qo = alloc_quant(quantize, rows, h, pre);
+    launch_activation_fwd(pre.data_ptr(), act.data_ptr(), meta.has_value() ? meta->data_ptr<int>() : nullptr, qo.qp, qo.sp, rows, h, kind, stream());
+    if (quantize) return {act, qo.q, qo.sf};
+    return {act};
 }
 
-Tensor activation_bwd(const Tensor& dact, const Tensor& pre, const std::string& name, const OptTensor& meta) {
+std::vector<Tensor> activation_bwd(const Tensor& dact, const Tensor& pre, const std::string& name, const OptTensor& meta, bool quantize) {
     c10::cuda::CUDAGuard guard(pre.device());
     check_bf16(dact, "dact");
     const int kind = act_kind(name);
@@ -201,8 +236,11 @@ Tensor activation_bwd(const Tensor& dact, const Tensor& pre, const std::string& 
     const int rows = pre.numel() / in_w;
     GM_CHECK(h % 8 == 0 && pre.is_contiguous() && dact.is_contiguous(), "activation width must be a multiple of 8 (16-byte vectors) and rows contiguous");
     Tensor dpre = torch::empty_like(pre);
-    launch_activation_bwd(dact.data_ptr(), pre.data_ptr(), dpre.data_ptr(), meta.has_value() ? meta->data_ptr<int>() : nullptr, rows, h, kind, stream());
-    return dpre;
+    GM_CHECK(!quantize || h % 32 == 0, "activation with an MXFP8 copy: width must be a multiple of 32");
+    QuantOut qo = alloc_quant(quantize, rows, in_w, pre);
+    launch_activation_bwd(dact.data_ptr(), pre.data_ptr(), dpre.data_ptr(), meta.has_value() ? meta->data_ptr<int>() : nullptr, qo.qp, qo.sp, rows, h, kind, stream());
+    if (quantize) return {dpre, qo.q, qo.sf};
+    return {dpre};
 }
 
 // loss per row; logits overwritten with (softmax - onehot) * grad_scale when write_grad
@@ -434,7 +472,7 @@ std::vector<Tensor> ep_combine(const Tensor& ret, const Tensor& top_idx, const T
 void register_kernels(pybind11::module_& m) {
     namespace py = pybind11;
     m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("eps"), py::arg("branch") = py::none(),
-          py::arg("alpha") = py::none(), py::arg("beta") = py::none());
+          py::arg("alpha") = py::none(), py::arg("beta") = py::none(), py::arg("quantize") = false);
     m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("dres") = py::none());
     m.def("residual_bwd", &residual_bwd);
     m.def("rope_qknorm_fwd", &rope_qknorm_fwd, py::arg("x"), py::arg("out"), py::arg("cos"), py::arg("sin"), py::arg("q_scale"), py::arg("k_scale"),
@@ -442,13 +480,13 @@ void register_kernels(pybind11::module_& m) {
           py::arg("smax"), py::arg("copy_cols") = 0);
     m.def("rope_qknorm_bwd", &rope_qknorm_bwd, py::arg("x"), py::arg("dy"), py::arg("dx"), py::arg("cos"), py::arg("sin"), py::arg("q_scale"),
           py::arg("k_scale"), py::arg("seq_len"), py::arg("q_heads"), py::arg("k_heads"), py::arg("head_dim"), py::arg("eps"), py::arg("rms"),
-          py::arg("smin"), py::arg("smax"), py::arg("dq32") = py::none());
+          py::arg("smin"), py::arg("smax"), py::arg("dq32") = py::none(), py::arg("quantize") = false);
     m.def("route", &route);
-    m.def("gather_rows", &gather_rows);
+    m.def("gather_rows", &gather_rows, py::arg("hidden"), py::arg("src_of_row"), py::arg("meta"), py::arg("top_k"), py::arg("quantize") = false);
     m.def("combine_fwd", &combine_fwd);
-    m.def("combine_bwd", &combine_bwd);
-    m.def("activation_fwd", &activation_fwd, py::arg("pre"), py::arg("name"), py::arg("meta") = py::none());
-    m.def("activation_bwd", &activation_bwd, py::arg("dact"), py::arg("pre"), py::arg("name"), py::arg("meta") = py::none());
+    m.def("combine_bwd", &combine_bwd, py::arg("dout"), py::arg("y"), py::arg("src_of_row"), py::arg("gates"), py::arg("meta"), py::arg("quantize") = false);
+    m.def("activation_fwd", &activation_fwd, py::arg("pre"), py::arg("name"), py::arg("meta") = py::none(), py::arg("quantize") = false);
+    m.def("activation_bwd", &activation_bwd, py::arg("dact"), py::arg("pre"), py::arg("name"), py::arg("meta") = py::none(), py::arg("quantize") = false);
     m.def("ce_fwd_bwd", &ce_fwd_bwd);
     m.def("adamw", &adamw);
     m.def("muon_prepare", &muon_prepare);

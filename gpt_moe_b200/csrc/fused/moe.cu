@@ -12,6 +12,7 @@
 // Reference counterparts: `model/feedforward/routing.py:12-96` (histogram -> prefix -> stable permutation),
 // `model/linear/fp8/custom/grouped.py:57-72` (per-expert padding to 128), `experiments/053-fused-expert-output-combine.patch`.
 #include "../common/ptx.cuh"
+#include "../common/mxfp8.cuh"
 #include "../kernels_decl.h"
 
 namespace gm {
@@ -107,28 +108,60 @@ bool launch_route(const long long* idx, int slots, int experts, int* chunk_hist,
     return true;
 }
 
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+    uint4 o;
+    o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]); o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+    return o;
+}
+
+// Every kernel below that writes a bf16 matrix feeding an MXFP8 GEMM can emit the quantised copy in the same pass (`q`, `sf`
+// non-null): e4m3 payload + scale records of exactly the bf16 values it stores, so the GEMM operand never costs a pass of its
+// own (reference: gather + activation + quantise in one kernel, model/linear/fp8/custom/grouped.py:15-84).  A thread holds 8
+// consecutive elements, so a 32-element block is 4 adjacent lanes.
+
 // packed[row] = hidden[src_of_row[row] / k] (zeros for pad rows); one warp per row, 16-byte vectors
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const __nv_bfloat16* __restrict__ hidden, const int* __restrict__ src_of_row, const int* __restrict__ meta,
-                   __nv_bfloat16* __restrict__ packed, int d, int top_k, int cap_rows) {
+                   __nv_bfloat16* __restrict__ packed, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int d, int top_k, int cap_rows) {
     const int lane = threadIdx.x & 31;
     const int total = min(meta[1], cap_rows);
+    const int vecs = d / 8, k_blocks = (d + 127) >> 7;
     for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total; row += gridDim.x * 8) {
         const int src = src_of_row[row];
         uint4* out = reinterpret_cast<uint4*>(packed + static_cast<long long>(row) * d);
-        if (src < 0) {
-            for (int i = lane; i < d / 8; i += 32) out[i] = make_uint4(0, 0, 0, 0);
-        } else {
-            const uint4* in = reinterpret_cast<const uint4*>(hidden + static_cast<long long>(src / top_k) * d);
-            for (int i = lane; i < d / 8; i += 32) out[i] = in[i];
+        const uint4* in = reinterpret_cast<const uint4*>(hidden + static_cast<long long>(src < 0 ? 0 : src / top_k) * d);
+        for (int base = 0; base < vecs; base += 32) {                  // warp-uniform trip count: the quantiser shuffles
+            const int i = base + lane;
+            const bool active = i < vecs;
+            const uint4 raw = (active && src >= 0) ? in[i] : make_uint4(0, 0, 0, 0);
+            if (active) out[i] = raw;
+            if (q != nullptr) {
+                float v[8];
+                unpack8(raw, v);
+                uint32_t o[2];
+                const uint32_t e8 = quantize_block_lanes<8>(v, o);
+                if (active) {
+                    *reinterpret_cast<uint2*>(q + static_cast<long long>(row) * d + i * 8) = make_uint2(o[0], o[1]);
+                    if ((lane & 3) == 0) sf[sf_offset(row, i >> 2, k_blocks)] = static_cast<uint8_t>(e8);
+                }
+            }
         }
     }
 }
 
-void launch_gather_rows(const void* hidden, const int* src_of_row, const int* meta, void* packed, int d, int top_k, int cap_rows,
-                        cudaStream_t s) {
+void launch_gather_rows(const void* hidden, const int* src_of_row, const int* meta, void* packed, void* q, void* sf, int d, int top_k,
+                        int cap_rows, cudaStream_t s) {
     gather_rows_kernel<<<1184, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(hidden), src_of_row, meta,
-                                            static_cast<__nv_bfloat16*>(packed), d, top_k, cap_rows);
+                                            static_cast<__nv_bfloat16*>(packed), static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), d, top_k,
+                                            cap_rows);
 }
 
 // out[t] = sum_k gates[t,k] * y[dest[t*k+k']]   (fp32 accumulation, bf16 result); one warp per token
@@ -162,37 +195,49 @@ combine_fwd_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ 
 __global__ void __launch_bounds__(256)
 combine_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ y, const int* __restrict__ src_of_row,
                    const float* __restrict__ gates, const int* __restrict__ meta, __nv_bfloat16* __restrict__ dy,
-                   float* __restrict__ dgates, int d, int top_k, int cap_rows) {
+                   float* __restrict__ dgates, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int d, int top_k, int cap_rows) {
     const int lane = threadIdx.x & 31;
     const int total = min(meta[1], cap_rows);
+    const int vecs = d / 8, k_blocks = (d + 127) >> 7;
     for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total; row += gridDim.x * 8) {
         const int src = src_of_row[row];
+        const bool live = src >= 0;
         uint4* o = reinterpret_cast<uint4*>(dy + static_cast<long long>(row) * d);
-        if (src < 0) {
-            for (int i = lane; i < d / 8; i += 32) o[i] = make_uint4(0, 0, 0, 0);
-            continue;
-        }
-        const float g = gates[src];
-        const uint4* gin = reinterpret_cast<const uint4*>(dout + static_cast<long long>(src / top_k) * d);
+        const float g = live ? gates[src] : 0.f;
+        const uint4* gin = reinterpret_cast<const uint4*>(dout + static_cast<long long>(live ? src / top_k : 0) * d);
         const uint4* yin = reinterpret_cast<const uint4*>(y + static_cast<long long>(row) * d);
         float dot = 0.f;
-        for (int i = lane; i < d / 8; i += 32) {
-            const uint4 a = gin[i], b = yin[i];
-            const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
-            const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
-            uint4 w;
-            uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
+        for (int base = 0; base < vecs; base += 32) {
+            const int i = base + lane;
+            const bool active = i < vecs;
+            uint4 w = make_uint4(0, 0, 0, 0);
+            if (active && live) {
+                const uint4 a = gin[i], b = yin[i];
+                const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+                const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+                uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 fa = __bfloat1622float2(ha[e]), fb = __bfloat1622float2(hb[e]);
-                dot += fa.x * fb.x + fa.y * fb.y;
-                wp[e] = pack_bf16x2(g * fa.x, g * fa.y);
+                for (int e = 0; e < 4; ++e) {
+                    const float2 fa = __bfloat1622float2(ha[e]), fb = __bfloat1622float2(hb[e]);
+                    dot += fa.x * fb.x + fa.y * fb.y;
+                    wp[e] = pack_bf16x2(g * fa.x, g * fa.y);
+                }
             }
-            o[i] = w;
+            if (active) o[i] = w;
+            if (q != nullptr) {
+                float v[8];
+                unpack8(w, v);                                       // the bf16 values just stored
+                uint32_t out[2];
+                const uint32_t e8 = quantize_block_lanes<8>(v, out);
+                if (active) {
+                    *reinterpret_cast<uint2*>(q + static_cast<long long>(row) * d + i * 8) = make_uint2(out[0], out[1]);
+                    if ((lane & 3) == 0) sf[sf_offset(row, i >> 2, k_blocks)] = static_cast<uint8_t>(e8);
+                }
+            }
         }
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
-        if (lane == 0) dgates[src] = dot;
+        if (lane == 0 && live) dgates[src] = dot;
     }
 }
 
@@ -200,9 +245,10 @@ void launch_combine_fwd(const void* y, const int* dest, const float* gates, void
     combine_fwd_kernel<<<1184, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(y), dest, gates, static_cast<__nv_bfloat16*>(out), tokens, d, top_k);
 }
 void launch_combine_bwd(const void* dout, const void* y, const int* src_of_row, const float* gates, const int* meta, void* dy,
-                        float* dgates, int d, int top_k, int cap_rows, cudaStream_t s) {
+                        float* dgates, void* q, void* sf, int d, int top_k, int cap_rows, cudaStream_t s) {
     combine_bwd_kernel<<<1184, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(y), src_of_row,
-                                            gates, meta, static_cast<__nv_bfloat16*>(dy), dgates, d, top_k, cap_rows);
+                                            gates, meta, static_cast<__nv_bfloat16*>(dy), dgates, static_cast<uint8_t*>(q),
+                                            static_cast<uint8_t*>(sf), d, top_k, cap_rows);
 }
 
 // ---- activations ---------------------------------------------------------------------------------------
@@ -226,91 +272,116 @@ __device__ __forceinline__ float act_grad(int kind, float x) {
 
 // rows limited by meta[1] when meta != nullptr (padded expert rows), else by `rows`.  A thread handles 8 consecutive
 // elements (16-byte loads and stores); SWIGLU is a template parameter so the common case carries no per-element switch.
-__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(h[i]);
-        v[2 * i] = f.x; v[2 * i + 1] = f.y;
+// store 8 quantised values of one thread (a quarter of a 32-element block) + the block's scale byte from its first lane
+__device__ __forceinline__ void emit_quantized8(const uint4& stored, bool active, uint8_t* q, uint8_t* sf, long long row, int col, int width,
+                                                int k_blocks) {
+    float v[8];
+    unpack8(stored, v);
+    uint32_t out[2];
+    const uint32_t e8 = quantize_block_lanes<8>(v, out);
+    if (active) {
+        *reinterpret_cast<uint2*>(q + row * width + col) = make_uint2(out[0], out[1]);
+        if ((threadIdx.x & 3) == 0) sf[sf_offset(row, col >> 5, k_blocks)] = static_cast<uint8_t>(e8);
     }
-}
-__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
-    uint4 o;
-    o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]); o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-    return o;
 }
 
 template <bool SWIGLU>
 __global__ void __launch_bounds__(256)
 activation_fwd_kernel(const __nv_bfloat16* __restrict__ pre, __nv_bfloat16* __restrict__ act, const int* __restrict__ meta,
-                      int rows, int h, int kind) {
+                      uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int rows, int h, int kind) {
     const int total = meta ? min(meta[1], rows) : rows;
     const int per_row = h / 8;
     const long long n = static_cast<long long>(total) * per_row;
     const int in_w = SWIGLU ? 2 * h : h;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long r = i / per_row;
-        const int c = static_cast<int>(i - r * per_row) * 8;
-        float a[8], o[8];
-        unpack8(*reinterpret_cast<const uint4*>(pre + r * in_w + c), a);
-        if (SWIGLU) {
-            float u[8];
-            unpack8(*reinterpret_cast<const uint4*>(pre + r * in_w + h + c), u);
+    const int k_blocks = (h + 127) >> 7;
+    // warp-uniform trip count (the quantiser shuffles inside 4-lane groups; h % 32 == 0 keeps a group inside one row)
+    for (long long base = blockIdx.x * static_cast<long long>(blockDim.x) + (threadIdx.x & ~31); base < n; base += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long i = base + (threadIdx.x & 31);
+        const bool active = i < n;
+        const long long r = active ? i / per_row : 0;
+        const int c = active ? static_cast<int>(i - r * per_row) * 8 : 0;
+        uint4 stored = make_uint4(0, 0, 0, 0);
+        if (active) {
+            float a[8], o[8];
+            unpack8(*reinterpret_cast<const uint4*>(pre + r * in_w + c), a);
+            if (SWIGLU) {
+                float u[8];
+                unpack8(*reinterpret_cast<const uint4*>(pre + r * in_w + h + c), u);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = a[j] / (1.f + __expf(-a[j])) * u[j];
-        } else {
+                for (int j = 0; j < 8; ++j) o[j] = a[j] / (1.f + __expf(-a[j])) * u[j];
+            } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = act_fwd(kind, a[j]);
+                for (int j = 0; j < 8; ++j) o[j] = act_fwd(kind, a[j]);
+            }
+            stored = pack8(o);
+            *reinterpret_cast<uint4*>(act + r * h + c) = stored;
         }
-        *reinterpret_cast<uint4*>(act + r * h + c) = pack8(o);
+        if (q != nullptr) emit_quantized8(stored, active, q, sf, r, c, h, k_blocks);
     }
 }
 
 template <bool SWIGLU>
 __global__ void __launch_bounds__(256)
 activation_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16* __restrict__ pre, __nv_bfloat16* __restrict__ dpre,
-                      const int* __restrict__ meta, int rows, int h, int kind) {
+                      const int* __restrict__ meta, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int rows, int h, int kind) {
     const int total = meta ? min(meta[1], rows) : rows;
     const int per_row = h / 8;
     const long long n = static_cast<long long>(total) * per_row;
     const int in_w = SWIGLU ? 2 * h : h;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long r = i / per_row;
-        const int c = static_cast<int>(i - r * per_row) * 8;
-        float g[8], a[8], d0[8];
-        unpack8(*reinterpret_cast<const uint4*>(dact + r * h + c), g);
-        unpack8(*reinterpret_cast<const uint4*>(pre + r * in_w + c), a);
-        if (SWIGLU) {
-            float u[8], d1[8];
-            unpack8(*reinterpret_cast<const uint4*>(pre + r * in_w + h + c), u);
+    const int k_blocks = (in_w + 127) >> 7;
+    for (long long base = blockIdx.x * static_cast<long long>(blockDim.x) + (threadIdx.x & ~31); base < n; base += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long i = base + (threadIdx.x & 31);
+        const bool active = i < n;
+        const long long r = active ? i / per_row : 0;
+        const int c = active ? static_cast<int>(i - r * per_row) * 8 : 0;
+        uint4 s0 = make_uint4(0, 0, 0, 0), s1 = s0;
+        if (active) {
+            float g[8], a[8], d0[8];
+            unpack8(*reinterpret_cast<const uint4*>(dact + r * h + c), g);
+            unpack8(*reinterpret_cast<const uint4*>(pre + r * in_w + c), a);
+            if (SWIGLU) {
+                float u[8], d1[8];
+                unpack8(*reinterpret_cast<const uint4*>(pre + r * in_w + h + c), u);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float sg = 1.f / (1.f + __expf(-a[j]));
-                d0[j] = g[j] * u[j] * sg * (1.f + a[j] * (1.f - sg));      // d/d(gate): up * silu'(gate)
-                d1[j] = g[j] * a[j] * sg;                                    // d/d(up):   silu(gate)
+                for (int j = 0; j < 8; ++j) {
+                    const float sg = 1.f / (1.f + __expf(-a[j]));
+                    d0[j] = g[j] * u[j] * sg * (1.f + a[j] * (1.f - sg));      // d/d(gate): up * silu'(gate)
+                    d1[j] = g[j] * a[j] * sg;                                    // d/d(up):   silu(gate)
+                }
+                s1 = pack8(d1);
+                *reinterpret_cast<uint4*>(dpre + r * in_w + h + c) = s1;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) d0[j] = g[j] * act_grad(kind, a[j]);
             }
-            *reinterpret_cast<uint4*>(dpre + r * in_w + h + c) = pack8(d1);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) d0[j] = g[j] * act_grad(kind, a[j]);
+            s0 = pack8(d0);
+            *reinterpret_cast<uint4*>(dpre + r * in_w + c) = s0;
         }
-        *reinterpret_cast<uint4*>(dpre + r * in_w + c) = pack8(d0);
+        if (q != nullptr) {
+            emit_quantized8(s0, active, q, sf, r, c, in_w, k_blocks);
+            if (SWIGLU) emit_quantized8(s1, active, q, sf, r, h + c, in_w, k_blocks);
+        }
     }
 }
 
-void launch_activation_fwd(const void* pre, void* act, const int* meta, int rows, int h, int kind, cudaStream_t s) {
+void launch_activation_fwd(const void* pre, void* act, const int* meta, void* q, void* sf, int rows, int h, int kind, cudaStream_t s) {
+    auto* qp = static_cast<uint8_t*>(q);
+    auto* sp = static_cast<uint8_t*>(sf);
     if (kind == 4)
-        activation_fwd_kernel<true><<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(act), meta, rows, h, kind);
+        activation_fwd_kernel<true><<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(act), meta, qp, sp, rows, h, kind);
     else
-        activation_fwd_kernel<false><<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(act), meta, rows, h, kind);
+        activation_fwd_kernel<false><<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(pre), static_cast<__nv_bfloat16*>(act), meta, qp, sp, rows, h, kind);
 }
-void launch_activation_bwd(const void* dact, const void* pre, void* dpre, const int* meta, int rows, int h, int kind, cudaStream_t s) {
+void launch_activation_bwd(const void* dact, const void* pre, void* dpre, const int* meta, void* q, void* sf, int rows, int h, int kind,
+                           cudaStream_t s) {
+    auto* qp = static_cast<uint8_t*>(q);
+    auto* sp = static_cast<uint8_t*>(sf);
     if (kind == 4)
         activation_bwd_kernel<true><<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dact), static_cast<const __nv_bfloat16*>(pre),
-                                                         static_cast<__nv_bfloat16*>(dpre), meta, rows, h, kind);
+                                                         static_cast<__nv_bfloat16*>(dpre), meta, qp, sp, rows, h, kind);
     else
         activation_bwd_kernel<false><<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dact), static_cast<const __nv_bfloat16*>(pre),
-                                                          static_cast<__nv_bfloat16*>(dpre), meta, rows, h, kind);
+                                                          static_cast<__nv_bfloat16*>(dpre), meta, qp, sp, rows, h, kind);
 }
 
 }  // namespace gm

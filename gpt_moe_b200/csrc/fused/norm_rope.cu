@@ -5,6 +5,7 @@
 // `model/attention/qk_norm_rope.py:21-150` (RoPE -> QK-norm -> clamped learned scale),
 // `experiments/057-fused-attention-residual-rmsnorm.patch` (residual + RMSNorm).
 #include "../common/ptx.cuh"
+#include "../common/mxfp8.cuh"
 #include "../kernels_decl.h"
 
 namespace gm {
@@ -37,14 +38,18 @@ constexpr int NORM_WARPS = 8;
 // parameter so the per-lane row copy stays in registers.  Supported: d = 128*{1,2,4,6,8,12,16} (up to 2048).
 
 // x_new = alpha*x + beta*branch (when branch != nullptr; written to x_out), y = rmsnorm(x_new) * w
+// yq / ysf (optional): the MXFP8 copy of y (e4m3 + scale records of the bf16 values stored), so the projection that consumes y
+// needs no quantisation pass (reference: RMSNorm writing the FP8 layouts directly, model/linear/fp8/custom/rms_norm.py:23-55).
+// A lane holds 4 consecutive columns per chunk: a 32-column block is 8 adjacent lanes.
 template <typename TX, int MAX_CHUNKS>
 __global__ void __launch_bounds__(NORM_WARPS * 32)
 rmsnorm_fwd_kernel(const TX* __restrict__ x, const __nv_bfloat16* __restrict__ branch, const float* __restrict__ alpha,
                    const float* __restrict__ beta, TX* __restrict__ x_out, const float* __restrict__ w,
-                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int d, float eps) {
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, uint8_t* __restrict__ yq, uint8_t* __restrict__ ysf,
+                   int rows, int d, float eps) {
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
-    if (row >= rows) return;
+    if (row >= rows) return;                       // whole warps leave together: a warp owns one row
     const int chunks = d >> 7;
     const float a = alpha ? *alpha : 1.f, b = beta ? *beta : 1.f;
     float4 v[MAX_CHUNKS];
@@ -72,7 +77,15 @@ rmsnorm_fwd_kernel(const TX* __restrict__ x, const __nv_bfloat16* __restrict__ b
         if (c < chunks) {
             const int col = (c * 32 + lane) * 4;
             float4 g = w ? *reinterpret_cast<const float4*>(w + col) : make_float4(1.f, 1.f, 1.f, 1.f);
-            store4<__nv_bfloat16>(y + base + col, make_float4(v[c].x * r * g.x, v[c].y * r * g.y, v[c].z * r * g.z, v[c].w * r * g.w));
+            const float4 o = make_float4(v[c].x * r * g.x, v[c].y * r * g.y, v[c].z * r * g.z, v[c].w * r * g.w);
+            store4<__nv_bfloat16>(y + base + col, o);
+            if (yq != nullptr) {
+                const float q4[4] = {round_bf16(o.x), round_bf16(o.y), round_bf16(o.z), round_bf16(o.w)};
+                uint32_t out[1];
+                const uint32_t e8 = quantize_block_lanes<4>(q4, out);
+                *reinterpret_cast<uint32_t*>(yq + base + col) = out[0];
+                if ((lane & 7) == 0) ysf[sf_offset(row, col >> 5, d >> 7)] = static_cast<uint8_t>(e8);
+            }
         }
     }
 }
@@ -245,18 +258,19 @@ bool norm_dim_supported(int d) {
     }
 
 bool launch_rmsnorm_fwd(const void* x, bool x_fp32, const void* branch, const float* alpha, const float* beta, void* x_out,
-                        const float* w, void* y, float* rstd, int rows, int d, float eps, cudaStream_t s) {
+                        const float* w, void* y, float* rstd, void* yq, void* ysf, int rows, int d, float eps, cudaStream_t s) {
     if (!norm_dim_supported(d)) return false;
     const int blocks = (rows + NORM_WARPS - 1) / NORM_WARPS;
 #define GM_FWD(C)                                                                                                              \
     if (x_fp32)                                                                                                                \
         rmsnorm_fwd_kernel<float, C><<<blocks, NORM_WARPS * 32, 0, s>>>(                                                       \
             static_cast<const float*>(x), static_cast<const __nv_bfloat16*>(branch), alpha, beta, static_cast<float*>(x_out), w, \
-            static_cast<__nv_bfloat16*>(y), rstd, rows, d, eps);                                                               \
+            static_cast<__nv_bfloat16*>(y), rstd, static_cast<uint8_t*>(yq), static_cast<uint8_t*>(ysf), rows, d, eps);         \
     else                                                                                                                       \
         rmsnorm_fwd_kernel<__nv_bfloat16, C><<<blocks, NORM_WARPS * 32, 0, s>>>(                                               \
             static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(branch), alpha, beta,                      \
-            static_cast<__nv_bfloat16*>(x_out), w, static_cast<__nv_bfloat16*>(y), rstd, rows, d, eps);
+            static_cast<__nv_bfloat16*>(x_out), w, static_cast<__nv_bfloat16*>(y), rstd, static_cast<uint8_t*>(yq),            \
+            static_cast<uint8_t*>(ysf), rows, d, eps);
     GM_DISPATCH_CHUNKS(d, GM_FWD)
 #undef GM_FWD
     return true;
@@ -314,7 +328,8 @@ rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* dy,
                    const float* __restrict__ cos_t, const float* __restrict__ sin_t, const float* __restrict__ q_scale,
                    const float* __restrict__ k_scale, float* __restrict__ dscale_partial, long long tokens, int seq_len,
                    int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin, float smax,
-                   int copy_cols, const float* __restrict__ dq32, long long dq_stride) {
+                   int copy_cols, const float* __restrict__ dq32, long long dq_stride, uint8_t* __restrict__ mxq, uint8_t* __restrict__ mxsf,
+                   int mx_width) {
     constexpr int PAIRS = D / 2;
     constexpr int LANES = D / 8;                 // lanes per head
     constexpr int HEADS_PER_WARP = 32 / LANES;
@@ -391,6 +406,23 @@ rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* dy,
                 op[i] = __floats2bfloat162_rn(d1 * c[i] + d2 * sn[i], -d1 * sn[i] + d2 * c[i]);
             }
             if (live) *reinterpret_cast<uint4*>(out + t * x_stride + h * D + li * 8) = oraw;
+            if (mxq != nullptr) {
+                // MXFP8 copy of the packed gradient row (the operand of the projection's input-gradient GEMM): a lane's 8
+                // values are a quarter of a 32-column block, the 4 lanes of a block are adjacent
+                float v8[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(op[i]);
+                    v8[2 * i] = live ? f.x : 0.f; v8[2 * i + 1] = live ? f.y : 0.f;
+                }
+                uint32_t o2[2];
+                const uint32_t e8 = quantize_block_lanes<8>(v8, o2);
+                if (live) {
+                    const int col = h * D + li * 8;
+                    *reinterpret_cast<uint2*>(mxq + t * mx_width + col) = make_uint2(o2[0], o2[1]);
+                    if ((lane & 3) == 0) mxsf[sf_offset(t, col >> 5, (mx_width + 127) >> 7)] = static_cast<uint8_t>(e8);
+                }
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < 4; ++i) op[i] = __floats2bfloat162_rn(r1[i] * mult, r2[i] * mult);
@@ -404,6 +436,30 @@ rope_qknorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* dy,
             const long long t = i / vecs;
             const int v = static_cast<int>(i - t * vecs);
             *reinterpret_cast<uint4*>(out + t * o_stride + heads * D + v * 8) = *reinterpret_cast<const uint4*>(x + t * x_stride + heads * D + v * 8);
+        }
+    }
+    if (BWD && mxq != nullptr && copy_cols > 0) {
+        // the trailing (value) columns of the gradient row pass through unchanged: only their quantised copy is produced here
+        const int vecs = copy_cols / 8;
+        const long long n = tokens * vecs;
+        for (long long base = static_cast<long long>(blockIdx.x) * blockDim.x + (threadIdx.x & ~31); base < n; base += static_cast<long long>(gridDim.x) * blockDim.x) {
+            const long long i = base + lane;
+            const bool active = i < n;
+            const long long t = active ? i / vecs : 0;
+            const int col = heads * D + (active ? static_cast<int>(i - t * vecs) * 8 : 0);
+            float v8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (active) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(dy + t * o_stride + col);
+                const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(hp[e]); v8[2 * e] = f.x; v8[2 * e + 1] = f.y; }
+            }
+            uint32_t o2[2];
+            const uint32_t e8 = quantize_block_lanes<8>(v8, o2);
+            if (active) {
+                *reinterpret_cast<uint2*>(mxq + t * mx_width + col) = make_uint2(o2[0], o2[1]);
+                if ((lane & 3) == 0) mxsf[sf_offset(t, col >> 5, (mx_width + 127) >> 7)] = static_cast<uint8_t>(e8);
+            }
         }
     }
     if (BWD && dscale_partial) {
@@ -425,18 +481,20 @@ int rope_blocks(long long tokens, int heads) {
 bool launch_rope_qknorm(bool bwd, int D, const void* x, const void* dy, void* out, const float* cos_t, const float* sin_t,
                         const float* q_scale, const float* k_scale, float* dscale_partial, long long tokens, int seq_len,
                         int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin,
-                        float smax, int copy_cols, const float* dq32, long long dq_stride, cudaStream_t s) {
+                        float smax, int copy_cols, const float* dq32, long long dq_stride, void* gq, void* gsf, int gq_width,
+                        cudaStream_t s) {
     if (q_heads + k_heads > 64) return false;
     const int blocks = rope_blocks(tokens, q_heads + k_heads);
 #define GM_ROPE(DD)                                                                                                            \
     if (bwd)                                                                                                                   \
         rope_qknorm_kernel<DD, true><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), \
             static_cast<__nv_bfloat16*>(out), cos_t, sin_t, q_scale, k_scale, dscale_partial, tokens, seq_len, q_heads, k_heads,  \
-            x_stride, o_stride, eps, rms, smin, smax, 0, dq32, dq_stride);                                                     \
+            x_stride, o_stride, eps, rms, smin, smax, copy_cols, dq32, dq_stride, static_cast<uint8_t*>(gq),                   \
+            static_cast<uint8_t*>(gsf), gq_width);                                                                             \
     else                                                                                                                       \
         rope_qknorm_kernel<DD, false><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), nullptr,                     \
             static_cast<__nv_bfloat16*>(out), cos_t, sin_t, q_scale, k_scale, nullptr, tokens, seq_len, q_heads, k_heads,        \
-            x_stride, o_stride, eps, rms, smin, smax, copy_cols, nullptr, 0);
+            x_stride, o_stride, eps, rms, smin, smax, copy_cols, nullptr, 0, nullptr, nullptr, 0);
     switch (D) {
         case 32: GM_ROPE(32); break;
         case 64: GM_ROPE(64); break;

@@ -57,13 +57,15 @@ struct Mxfp8Params {
     int* status;
 };
 
-cudaError_t launch_gemm_mxfp8(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const Mxfp8Params& p, int sms,
-                              cudaStream_t stream);
+// tsfa / tsfb: maps over the scale arrays seen as [records, 128] 32-bit words (one 512-byte record per row), box {128, 1}
+cudaError_t launch_gemm_mxfp8(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const CUtensorMap& tsfa,
+                              const CUtensorMap& tsfb, const Mxfp8Params& p, int sms, cudaStream_t stream);
 // x [rows, cols] bf16 with row pitch ld -> q [rows, cols] e4m3 and scale records; rows at or beyond *rows_limit (optional,
 // device) are left untouched.  cols must be a multiple of 32.
 void launch_quantize_rows(const void* x, void* q, void* sf, long long rows, int cols, long long ld, const int* rows_limit, cudaStream_t s);
-// w [batch, rows, cols] bf16 -> q [batch, cols, rows] e4m3 (transposed) with scales along the original row index.
-// rows must be a multiple of 32.
-void launch_quantize_transposed(const void* w, void* q, void* sf, int batch, int rows, int cols, long long sf_batch_stride, cudaStream_t s);
+// w [batch, rows, cols] bf16 -> q [batch, rows, cols] e4m3 with scales along the columns AND qt [batch, cols, rows] e4m3 (the
+// transpose) with scales along the original rows, in one pass.  rows and cols must be multiples of 32.
+void launch_quantize_weight_dual(const void* w, void* q, void* sf, void* qt, void* sft, int batch, int rows, int cols, long long sf_batch_stride,
+                                 long long sft_batch_stride, cudaStream_t s);
 
 }  // namespace gm

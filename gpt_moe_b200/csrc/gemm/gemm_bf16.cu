@@ -138,8 +138,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int cta_rank = static_cast<int>(cluster_ctarank());     // 0 = leader of the pair
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        // acc_empty of the leader collects the 256 epilogue threads of each of the two CTAs
-        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 512); }
+        // acc_empty of the leader collects one arrival per epilogue warp of each of the two CTAs (a remote arrival per thread
+        // would put 256 messages per tile on the cluster's shared-memory network)
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 16); }
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
@@ -271,7 +272,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
                 if (have_acc && round == rounds - 1) {                        // accumulator fully read: release it early
                     tc_fence_before();
-                    mbar_arrive_cluster(&acc_empty[acc], 0);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(&acc_empty[acc], 0);
                 }
                 uint8_t* slab_row = buf + half * (BM * 128) + row_in_tile * 128;
 #pragma unroll
@@ -377,7 +379,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (have_acc) {
                 // tiles narrower than BN leave the round loop early: the accumulator is released here in that case
                 const int rounds_done = min(rounds, (t.n_limit - t.n0 + chunks_per_round * 32 - 1) / (chunks_per_round * 32));
-                if (rounds_done < rounds) { tc_fence_before(); mbar_arrive_cluster(&acc_empty[acc], 0); }
+                if (rounds_done < rounds) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive_cluster(&acc_empty[acc], 0); }
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
         }

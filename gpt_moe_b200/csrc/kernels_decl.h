@@ -8,7 +8,7 @@ namespace gm {
 // fused/norm_rope.cu
 bool norm_dim_supported(int d);
 bool launch_rmsnorm_fwd(const void* x, bool x_fp32, const void* branch, const float* alpha, const float* beta, void* x_out,
-                        const float* w, void* y, float* rstd, int rows, int d, float eps, cudaStream_t s);
+                        const float* w, void* y, float* rstd, void* yq, void* ysf, int rows, int d, float eps, cudaStream_t s);
 int rmsnorm_bwd_blocks(int rows);
 bool launch_rmsnorm_bwd(const void* dy, const void* x, bool x_fp32, const float* w, const float* rstd, const void* dres, void* dx,
                         float* dw_partial, float* dw, int dw_accumulate, int rows, int d, cudaStream_t s);
@@ -20,18 +20,21 @@ int rope_blocks(long long tokens, int heads);
 bool launch_rope_qknorm(bool bwd, int D, const void* x, const void* dy, void* out, const float* cos_t, const float* sin_t,
                         const float* q_scale, const float* k_scale, float* dscale_partial, long long tokens, int seq_len,
                         int q_heads, int k_heads, long long x_stride, long long o_stride, float eps, int rms, float smin,
-                        float smax, int copy_cols, const float* dq32, long long dq_stride, cudaStream_t s);
+                        float smax, int copy_cols, const float* dq32, long long dq_stride, void* gq, void* gsf, int gq_width,
+                        cudaStream_t s);
 
 // fused/moe.cu
 bool launch_route(const long long* idx, int slots, int experts, int* chunk_hist, int* chunk_start, int* counts, int* seg_ends,
                   int* tile_expert, int* meta, int* dest, int* src_of_row, cudaStream_t s);
-void launch_gather_rows(const void* hidden, const int* src_of_row, const int* meta, void* packed, int d, int top_k, int cap_rows,
-                        cudaStream_t s);
+// q / sf (optional, every launcher below that has them): MXFP8 copy of the bf16 matrix the kernel writes, emitted in the same pass
+void launch_gather_rows(const void* hidden, const int* src_of_row, const int* meta, void* packed, void* q, void* sf, int d, int top_k,
+                        int cap_rows, cudaStream_t s);
 void launch_combine_fwd(const void* y, const int* dest, const float* gates, void* out, int tokens, int d, int top_k, cudaStream_t s);
 void launch_combine_bwd(const void* dout, const void* y, const int* src_of_row, const float* gates, const int* meta, void* dy,
-                        float* dgates, int d, int top_k, int cap_rows, cudaStream_t s);
-void launch_activation_fwd(const void* pre, void* act, const int* meta, int rows, int h, int kind, cudaStream_t s);
-void launch_activation_bwd(const void* dact, const void* pre, void* dpre, const int* meta, int rows, int h, int kind, cudaStream_t s);
+                        float* dgates, void* q, void* sf, int d, int top_k, int cap_rows, cudaStream_t s);
+void launch_activation_fwd(const void* pre, void* act, const int* meta, void* q, void* sf, int rows, int h, int kind, cudaStream_t s);
+void launch_activation_bwd(const void* dact, const void* pre, void* dpre, const int* meta, void* q, void* sf, int rows, int h, int kind,
+                           cudaStream_t s);
 
 // fused/loss_optim.cu
 void launch_ce_fwd_bwd(void* logits, const long long* targets, float* loss, const float* grad_scale, int rows, int vocab,

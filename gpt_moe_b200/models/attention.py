@@ -120,7 +120,6 @@ class SelfAttention(nn.Module):
             return None
         from ..ops import cuda_ops
         from ..ops.attention_cuda import _window_int
-        qkv = cuda_ops.linear_multi(x, (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight), self.q_proj.precision)
         cos = sin = None
         if self.rotary is not None:
             cos, sin = self.rotary.cos_cached[:t], self.rotary.sin_cached[:t]
@@ -131,6 +130,18 @@ class SelfAttention(nn.Module):
                 from ..ops.attention_tc import document_starts
                 ctx.doc_start = document_starts(ctx.document_ids)
             doc_start = ctx.doc_start
+        weights = (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight)
+        if self.q_proj.precision in ("mxfp8", "fp8"):
+            # MXFP8 projection: one autograd node from the projection to the attention output, so the backward's RoPE kernel
+            # hands the quantised dQKV rows straight to the input-gradient GEMM
+            from ..ops import mxfp8
+            y = mxfp8.qkv_rope_attention(
+                x, weights, cos, sin, self.q_scale if self.use_qk_norm else None, self.k_scale if self.use_qk_norm else None,
+                b, t, hq, hk, d, self.qk_eps, self.qk_norm_type == "rms", self.qk_scale_min, self.qk_scale_max, window, None,
+                self.softcap, doc_start)
+            if y is not None:
+                return y
+        qkv = cuda_ops.linear_multi(x, weights, self.q_proj.precision)
         return cuda_ops.rope_attention_packed(
             qkv.view(b * t, -1), cos, sin, self.q_scale if self.use_qk_norm else None, self.k_scale if self.use_qk_norm else None,
             b, t, hq, hk, d, self.qk_eps, self.qk_norm_type == "rms", self.qk_scale_min, self.qk_scale_max, window, None, self.softcap, doc_start)

@@ -70,11 +70,12 @@ class Block(nn.Module):
         res = x if alpha is None else alpha * x
         return res + (branch if beta is None else beta * branch)
 
-    def forward_prenormed(self, x: Tensor, h: Tensor, ctx: AttentionContext, next_norm: nn.Module
+    def forward_prenormed(self, x: Tensor, h: Tensor, ctx: AttentionContext, next_norm: nn.Module, next_is_mxfp8: bool = False
                           ) -> Tuple[Tensor, Tensor, Optional[Tensor]]:
         """Block step for a chain of RMSNorm blocks: `h` is ln_1(x) computed by the previous link; every
         residual update is fused with the norm that follows it (the next block's ln_1, or the final norm).
-        Returns (x_out, next_norm(x_out), balance_loss)."""
+        `next_is_mxfp8`: the consumer of the returned normalised rows is an MXFP8 projection (the norm kernel then emits
+        their quantised copy too).  Returns (x_out, next_norm(x_out), balance_loss)."""
         alpha, beta = self._scales("attn")
         x, h2 = api.residual_rms_norm(x, self.attn(h, ctx), alpha, beta, self.ln_2.weight, norm_eps(self.ln_2, x.dtype))
         out = self.mlp(h2)
@@ -82,7 +83,7 @@ class Block(nn.Module):
         if self.use_moe:
             out, balance = out
         alpha, beta = self._scales("mlp")
-        x, h_next = api.residual_rms_norm(x, out, alpha, beta, next_norm.weight, norm_eps(next_norm, x.dtype))
+        x, h_next = api.residual_rms_norm(x, out, alpha, beta, next_norm.weight, norm_eps(next_norm, x.dtype), next_is_mxfp8)
         return x, h_next, balance
 
     def forward(self, x: Tensor, ctx: AttentionContext) -> Tuple[Tensor, Optional[Tensor]]:

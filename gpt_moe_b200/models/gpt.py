@@ -259,7 +259,9 @@ class GPT(nn.Module):
                     # the gradient of a block's normalised input is the last thing its backward produces
                     h.register_hook(lambda grad, layer=i, fn=hook: fn(layer))
                 next_norm = blocks[i + 1].ln_1 if i + 1 < len(blocks) else self.transformer.ln_f
-                x, h, block_balance = block.forward_prenormed(x, h, ctx, next_norm)
+                next_q = getattr(blocks[i + 1].attn, "q_proj", None) if i + 1 < len(blocks) else None
+                next_mxfp8 = next_q is not None and next_q.precision in ("mxfp8", "fp8") and hasattr(blocks[i + 1].attn, "k_proj")
+                x, h, block_balance = block.forward_prenormed(x, h, ctx, next_norm, next_mxfp8)
                 if block_balance is not None:
                     balance_loss = block_balance if balance_loss is None else balance_loss + block_balance
             x = h

@@ -88,10 +88,11 @@ def rms_norm(x: Tensor, weight: Optional[Tensor], eps: float) -> Tensor:
 
 
 def residual_rms_norm(x: Tensor, branch: Tensor, alpha: Optional[Tensor], beta: Optional[Tensor], weight: Optional[Tensor],
-                      eps: float) -> Tuple[Tensor, Tensor]:
-    """x_new = alpha*x + beta*branch (alpha/beta None = 1) and rmsnorm(x_new); returns (x_new, normed)."""
+                      eps: float, quantize_out: bool = False) -> Tuple[Tensor, Tensor]:
+    """x_new = alpha*x + beta*branch (alpha/beta None = 1) and rmsnorm(x_new); returns (x_new, normed).  `quantize_out` tells
+    the GPU kernel that an MXFP8 projection consumes `normed`, so it writes the quantised copy in the same pass."""
     if x.is_cuda:
-        return _cuda().residual_rms_norm(x, branch, alpha, beta, weight, eps)
+        return _cuda().residual_rms_norm(x, branch, alpha, beta, weight, eps, quantize_out)
     x_new = (x if alpha is None else alpha * x) + (branch if beta is None else beta * branch).to(x.dtype)
     return x_new, ref.rms_norm(x_new, weight, eps)
 

@@ -320,18 +320,22 @@ class _ResidualRMSNormFn(torch.autograd.Function):
     gradient onto the residual gradient in the norm-backward kernel and derives d(branch), d(beta) in one more pass."""
 
     @staticmethod
-    def forward(ctx, x: Tensor, branch: Tensor, beta: Tensor, weight: Tensor, eps: float):
+    def forward(ctx, x: Tensor, branch: Tensor, beta: Tensor, weight: Tensor, eps: float, quantize: bool):
         xc = x if x.is_contiguous() else x.contiguous()
         br = branch if (branch.dtype == BF16 and branch.is_contiguous()) else branch.to(BF16).contiguous()
         w = weight.detach().float()
         b = beta.detach().float().reshape(1)
-        h, rstd, x_new = ext().rmsnorm_fwd(xc, w, eps, br, None, b)
+        res = ext().rmsnorm_fwd(xc, w, eps, br, None, b, quantize)
+        h, rstd, x_new = res[0], res[1], res[2]
         ctx.save_for_backward(x_new, w, rstd, br, b)
         ctx.meta = (beta.shape, beta.dtype, weight.dtype, beta.requires_grad)
-        return x_new, h
+        if quantize:                           # the MXFP8 copy of h (payload, scale records) for the projection that consumes it
+            ctx.mark_non_differentiable(res[3], res[4])
+            return x_new, h, res[3], res[4]
+        return x_new, h, None, None
 
     @staticmethod
-    def backward(ctx, dx_new: Optional[Tensor], dh: Optional[Tensor]):
+    def backward(ctx, dx_new: Optional[Tensor], dh: Optional[Tensor], _dq=None, _dsf=None):
         x_new, w, rstd, br, b = ctx.saved_tensors
         beta_shape, beta_dtype, w_dtype, beta_grad = ctx.meta
         dw = None
@@ -343,12 +347,15 @@ class _ResidualRMSNormFn(torch.autograd.Function):
         else:
             dxn = dx_new.contiguous()
         dbranch, dbeta = ext().residual_bwd(dxn, br, b)
-        return dxn, dbranch, (dbeta.reshape(beta_shape).to(beta_dtype) if beta_grad else None), dw, None
+        return dxn, dbranch, (dbeta.reshape(beta_shape).to(beta_dtype) if beta_grad else None), dw, None, None
 
 
-def residual_rms_norm(x: Tensor, branch: Tensor, alpha: Optional[Tensor], beta: Optional[Tensor], weight: Tensor, eps: float):
+def residual_rms_norm(x: Tensor, branch: Tensor, alpha: Optional[Tensor], beta: Optional[Tensor], weight: Tensor, eps: float,
+                      quantize_out: bool = False):
     """(x_new, rmsnorm(x_new)) with x_new = alpha*x + beta*branch.  The fused kernel covers the common case
-    (fp32 residual stream, no alpha); other cases compose the unfused ops."""
+    (fp32 residual stream, no alpha); other cases compose the unfused ops.  `quantize_out`: the consumer of the normalised
+    rows is an MXFP8 projection; the kernel then also writes their e4m3 payload and scale records, handed over as the
+    attribute `mxq` of the returned tensor."""
     d = x.shape[-1]
     fused = (alpha is None and x.dtype == torch.float32 and weight is not None and d % 128 == 0
              and (d // 128) in (1, 2, 4, 6, 8, 12, 16) and x.numel() % 4 == 0)
@@ -357,7 +364,11 @@ def residual_rms_norm(x: Tensor, branch: Tensor, alpha: Optional[Tensor], beta: 
         return x_new, rms_norm(x_new, weight, eps)
     if beta is None:
         beta = torch.ones(1, device=x.device)
-    return _ResidualRMSNormFn.apply(x, branch, beta, weight, eps)
+    quantize = bool(quantize_out and d % 128 == 0)
+    x_new, h, hq, hsf = _ResidualRMSNormFn.apply(x, branch, beta, weight, eps, quantize)
+    if quantize:
+        h.mxq = (hq, hsf)
+    return x_new, h
 
 
 class _SplitQKVFn(torch.autograd.Function):
@@ -414,8 +425,8 @@ class _RopeQKNormFn(torch.autograd.Function):
         seq_len, hq, hk, d, eps, rms, smin, smax, has_rope, has_norm = ctx.cfg
         dout = dout if dout.is_contiguous() else dout.contiguous()
         dx = dout                             # in place: q and k columns are rewritten, v columns pass through unchanged
-        dscale = ext().rope_qknorm_bwd(qkv, dout, dx, cos if has_rope else None, sin if has_rope else None,
-                                       qs if has_norm else None, ks if has_norm else None, seq_len, hq, hk, d, eps, rms, smin, smax)
+        (dscale,) = ext().rope_qknorm_bwd(qkv, dout, dx, cos if has_rope else None, sin if has_rope else None,
+                                          qs if has_norm else None, ks if has_norm else None, seq_len, hq, hk, d, eps, rms, smin, smax)
         dq = dk = None
         if has_norm:
             (qshape, qdt), (kshape, kdt) = ctx.scale_shapes
@@ -471,8 +482,8 @@ class _RopeAttentionFn(torch.autograd.Function):
         dv = grad[..., (hq + hk) * d:].unflatten(-1, (hk, d))
         dq32 = c.attn_bwd(q, k, v, o, d_out, lse, dk, dv, window, scale, softcap, ctx.doc_start)
         g2 = grad.view(batch * seq_len, -1)
-        dscale = c.rope_qknorm_bwd(qkv, g2, g2, cos if has_rope else None, sin if has_rope else None, qs if has_norm else None,
-                                   ks if has_norm else None, seq_len, hq, hk, d, eps, rms, smin, smax, dq32.view(batch * seq_len, -1))
+        (dscale,) = c.rope_qknorm_bwd(qkv, g2, g2, cos if has_rope else None, sin if has_rope else None, qs if has_norm else None,
+                                      ks if has_norm else None, seq_len, hq, hk, d, eps, rms, smin, smax, dq32.view(batch * seq_len, -1))
         dqs = dks = None
         if has_norm:
             (qshape, qdt), (kshape, kdt) = ctx.scale_shapes
@@ -519,13 +530,13 @@ class _ActivationFn(torch.autograd.Function):
         pre = pre if (pre.dtype == BF16 and pre.is_contiguous()) else pre.to(BF16).contiguous()
         ctx.save_for_backward(pre)
         ctx.name = name
-        return ext().activation_fwd(pre, name)
+        return ext().activation_fwd(pre, name)[0]
 
     @staticmethod
     def backward(ctx, dact: Tensor):
         (pre,) = ctx.saved_tensors
         dact = dact if (dact.dtype == BF16 and dact.is_contiguous()) else dact.to(BF16).contiguous()
-        return ext().activation_bwd(dact, pre, ctx.name), None
+        return ext().activation_bwd(dact, pre, ctx.name)[0], None
 
 
 def activate(x: Tensor, name: str) -> Tensor:
@@ -547,12 +558,12 @@ class _MoEExpertsFn(torch.autograd.Function):
         h2 = _as_bf16_2d(hidden)
         gates32 = gates.detach().float().contiguous()
         dest, src_of_row, seg_ends, counts, tile_expert, meta = c.route(top_idx.contiguous(), num_experts)
-        packed = c.gather_rows(h2, src_of_row, meta, top_k)
+        (packed,) = c.gather_rows(h2, src_of_row, meta, top_k)
         w_up, w_down = stacked_weight(up), stacked_weight(down)
         cap = packed.shape[0]
         pre = torch.empty((cap, w_up.shape[1]), dtype=BF16, device=hidden.device)
         c.gemm_bf16(packed, w_up, pre, False, False, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
-        act = c.activation_fwd(pre, activation, meta)
+        (act,) = c.activation_fwd(pre, activation, meta)
         y = torch.empty((cap, w_down.shape[1]), dtype=BF16, device=hidden.device)
         c.gemm_bf16(act, w_down, y, False, False, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
         out = c.combine_fwd(y, dest, gates32)
@@ -587,7 +598,7 @@ class _MoEExpertsFn(torch.autograd.Function):
                 grads[offset + i] = dw[i].to(p.dtype)
 
         wgrad(dy, act, down, e)
-        dpre = c.activation_bwd(dact, pre, ctx.activation, meta)
+        (dpre,) = c.activation_bwd(dact, pre, ctx.activation, meta)
         wgrad(dpre, packed, up, 0)
         dhidden = None
         if ctx.needs_input_grad[0]:

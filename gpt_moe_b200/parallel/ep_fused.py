@@ -103,7 +103,7 @@ class _FusedEPMoEFn(torch.autograd.Function):
         w_up, w_down = co.stacked_weight(up), co.stacked_weight(down)
         pre = torch.empty((ws.cap_rows, w_up.shape[1]), dtype=BF16, device=hidden.device)
         c.gemm_bf16(packed, w_up, pre, False, False, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
-        act = c.activation_fwd(pre, activation, meta)
+        (act,) = c.activation_fwd(pre, activation, meta)
         y = ws.rows(ws.ret)
         c.gemm_bf16(act, w_down, y, False, False, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
         ws.barrier()
@@ -146,7 +146,7 @@ class _FusedEPMoEFn(torch.autograd.Function):
                 grads[offset + i] = dw[i].to(p.dtype)
 
         wgrad(dy, act, down, e)
-        dpre = c.activation_bwd(dact, pre, ctx.activation, meta)
+        (dpre,) = c.activation_bwd(dact, pre, ctx.activation, meta)
         wgrad(dpre, packed, up, 0)
         dpacked = ws.rows(ws.ret)
         c.gemm_bf16(dpre, w_up, dpacked, False, True, 1.0, 0.0, None, False, 1, tile_expert, meta, None)

@@ -25,7 +25,7 @@ def _timed(fn, iters):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_mxfp8", "quantize", "gemm_wgrad", "grouped", "attn_fwd", "attn_bwd", "rs_muon", "ce", "rmsnorm", "rope", "rope_bwd", "ep_dispatch", "ep_combine", "rmsnorm_bwd", "attn_fwd_mla", "attn_bwd_mla", "gemm_xxt", "gemm_xxt_full", "polar"])
+    ap.add_argument("case", choices=["gemm", "gemm_mxfp8", "quantize", "gemm_wgrad", "grouped", "attn_fwd", "attn_bwd", "rs_muon", "ce", "rmsnorm", "rope", "rope_bwd", "ep_dispatch", "ep_combine", "rmsnorm_bwd", "attn_fwd_mla", "attn_bwd_mla", "gemm_xxt", "gemm_xxt_full", "polar", "gemm_big", "gemm_mxfp8_big", "gemm_mxfp8_down", "quantize_weight"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     from gpt_moe_b200.ops import attention_tc, cuda_ops
@@ -44,6 +44,25 @@ def main() -> None:
         d = torch.empty(32768, 2304, device=dev, dtype=torch.bfloat16)
         fn = lambda: c.gemm_mxfp8(aq, asf, bq, bsf, d)
         flops = 2 * 32768 * 2304 * 768
+    elif args.case in ("gemm_big", "gemm_mxfp8_big"):   # long contraction: the main loop dominates, the epilogue is amortised over 64 K blocks
+        a = torch.randn(8192, 8192, device=dev).bfloat16(); b = torch.randn(8192, 8192, device=dev).bfloat16()
+        d = torch.empty(8192, 8192, device=dev, dtype=torch.bfloat16)
+        if args.case == "gemm_big":
+            fn = lambda: c.gemm_bf16(a, b, d)
+        else:
+            aq, asf = c.mxfp8_quantize(a); bq, bsf = c.mxfp8_quantize(b)
+            fn = lambda: c.gemm_mxfp8(aq, asf, bq, bsf, d)
+        flops = 2 * 8192 ** 3
+    elif args.case == "gemm_mxfp8_down":         # expert down-projection shape: [32768, 3072] x [768, 3072]^T
+        a = torch.randn(32768, 3072, device=dev).bfloat16(); b = torch.randn(768, 3072, device=dev).bfloat16()
+        aq, asf = c.mxfp8_quantize(a); bq, bsf = c.mxfp8_quantize(b)
+        d = torch.empty(32768, 768, device=dev, dtype=torch.bfloat16)
+        fn = lambda: c.gemm_mxfp8(aq, asf, bq, bsf, d)
+        flops = 2 * 32768 * 768 * 3072
+    elif args.case == "quantize_weight":         # both quantised layouts of 96 expert up-projection weights in one pass
+        w = torch.randn(96, 6144, 768, device=dev).bfloat16()
+        fn = lambda: c.mxfp8_quantize_weight(w)
+        bytes_ = 96 * 6144 * 768 * 4 + 2 * 96 * 6144 * 768 // 32
     elif args.case == "quantize":                # bf16 -> e4m3 + scale records, 256 MB in
         a = torch.randn(65536, 2048, device=dev).bfloat16()
         fn = lambda: c.mxfp8_quantize(a)
@@ -57,7 +76,7 @@ def main() -> None:
         idx = torch.randint(0, 8, (32768, 1), device=dev)
         dest, src, seg, counts, tiles, meta = c.route(idx, 8)
         hidden = torch.randn(32768, 768, device=dev).bfloat16()
-        packed = c.gather_rows(hidden, src, meta, 1)
+        (packed,) = c.gather_rows(hidden, src, meta, 1)
         w = torch.randn(8, 6144, 768, device=dev).bfloat16()
         out = torch.empty(packed.shape[0], 6144, device=dev, dtype=torch.bfloat16)
         fn = lambda: c.gemm_bf16(packed, w, out, False, False, 1.0, 0.0, None, False, 1, tiles, meta, None)

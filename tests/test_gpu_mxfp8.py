@@ -43,12 +43,91 @@ def test_quantize_matches_emulation(ops, rows, cols):
     want_q, want_s = ref.mxfp8_quantize(x.float(), -1)
     assert torch.equal(unpack_scales(sf[0], rows, cols), want_s)
     assert torch.equal(q.view(torch.float8_e4m3fn).float(), want_q.float())
-    # transposed: blocks run along the original rows
+    # both weight layouts from one pass: row-wise (blocks along the columns) and transposed (blocks along the original rows)
     if rows % 32 == 0:
-        qt, sft = ops.ext().mxfp8_quantize_transposed(x)
+        q2, sf2, qt, sft = ops.ext().mxfp8_quantize_weight(x)
+        assert torch.equal(q2, q) and torch.equal(unpack_scales(sf2[0], rows, cols), want_s)
         want_q, want_s = ref.mxfp8_quantize(x.float().t().contiguous(), -1)
         assert torch.equal(unpack_scales(sft[0], cols, rows), want_s)
         assert torch.equal(qt.view(torch.float8_e4m3fn).float(), want_q.float())
+
+
+def test_quantize_weight_batched(ops):
+    torch.manual_seed(5)
+    w = (torch.randn(3, 256, 384, device="cuda") * 0.05).bfloat16()
+    q, sf, qt, sft = ops.ext().mxfp8_quantize_weight(w)
+    for z in range(3):
+        want_q, want_s = ref.mxfp8_quantize(w[z].float(), -1)
+        assert torch.equal(q[z].view(torch.float8_e4m3fn).float(), want_q.float())
+        assert torch.equal(unpack_scales(sf[z], 256, 384), want_s)
+        want_q, want_s = ref.mxfp8_quantize(w[z].float().t().contiguous(), -1)
+        assert torch.equal(qt[z].view(torch.float8_e4m3fn).float(), want_q.float())
+        assert torch.equal(unpack_scales(sft[z], 384, 256), want_s)
+
+
+def _check_copy(q, sf, bf16_rows, rows):
+    """The emitted copy equals the reference quantisation of the bf16 tensor the kernel wrote, bit for bit."""
+    cols = bf16_rows.shape[1]
+    want_q, want_s = ref.mxfp8_quantize(bf16_rows[:rows].float(), -1)
+    assert torch.equal(unpack_scales(sf, rows, cols), want_s)
+    assert torch.equal(q[:rows].view(torch.float8_e4m3fn).float(), want_q.float())
+
+
+def test_producers_emit_the_quantised_copy_of_what_they_write(ops):
+    """RMSNorm (+ residual), expert gather, activation forward / backward, combine backward and the RoPE / QK-norm backward
+    write e4m3 payload + scale records of exactly their bf16 output (oracle: `ops.reference.mxfp8_quantize`)."""
+    c = ops.ext()
+    torch.manual_seed(6)
+    tokens, d, experts, top_k, h = 777, 256, 4, 2, 384
+    # RMSNorm with the residual update
+    x = torch.randn(tokens, d, device="cuda")
+    branch = torch.randn(tokens, d, device="cuda").bfloat16()
+    w = torch.rand(d, device="cuda") + 0.5
+    beta = torch.tensor([0.7], device="cuda")
+    y, _, _, yq, ysf = c.rmsnorm_fwd(x, w, 1e-6, branch, None, beta, True)
+    y_plain = c.rmsnorm_fwd(x, w, 1e-6, branch, None, beta)[0]
+    assert torch.equal(y, y_plain)
+    _check_copy(yq, ysf, y, tokens)
+    # routing + gather
+    idx = torch.randint(0, experts, (tokens, top_k), device="cuda")
+    idx[:, 0] = torch.where(idx[:, 0] == 2, torch.zeros_like(idx[:, 0]), idx[:, 0])          # expert 2 mostly empty
+    dest, src, seg, counts, tiles, meta = c.route(idx, experts)
+    hidden = torch.randn(tokens, d, device="cuda").bfloat16()
+    packed, pq, psf = c.gather_rows(hidden, src, meta, top_k, True)
+    used = int(meta[1].item())
+    assert torch.equal(packed[:used], c.gather_rows(hidden, src, meta, top_k)[0][:used])
+    _check_copy(pq, psf, packed, used)
+    # activations on the padded rows (SwiGLU and relu^2)
+    for name, in_w in (("swiglu", 2 * h), ("relu2", h)):
+        pre = torch.randn(packed.shape[0], in_w, device="cuda").bfloat16()
+        act, aq, asf = c.activation_fwd(pre, name, meta, True)
+        assert torch.equal(act[:used], c.activation_fwd(pre, name, meta)[0][:used])
+        _check_copy(aq, asf, act, used)
+        dact = torch.randn(packed.shape[0], h, device="cuda").bfloat16()
+        dpre, dq, dsf = c.activation_bwd(dact, pre, name, meta, True)
+        assert torch.equal(dpre[:used], c.activation_bwd(dact, pre, name, meta)[0][:used])
+        _check_copy(dq, dsf, dpre, used)
+    # combine backward
+    gates = torch.rand(tokens, top_k, device="cuda")
+    yrows = torch.randn(packed.shape[0], d, device="cuda").bfloat16()
+    dout = torch.randn(tokens, d, device="cuda").bfloat16()
+    dy, dg, gq, gsf = c.combine_bwd(dout, yrows, src, gates, meta, True)
+    dy2, dg2 = c.combine_bwd(dout, yrows, src, gates, meta)
+    assert torch.equal(dy[:used], dy2[:used]) and torch.equal(dg, dg2)
+    _check_copy(gq, gsf, dy, used)
+    # RoPE / QK-norm backward on packed [q | k | v] gradient rows, in place
+    t, hq, hk, hd = 512, 4, 2, 64
+    width = (hq + 2 * hk) * hd
+    qkv = torch.randn(t, width, device="cuda").bfloat16()
+    pos = torch.arange(256, device="cuda").float()[:, None] * (10000.0 ** (-torch.arange(hd // 2, device="cuda").float() / (hd // 2)))[None, :]
+    cos, sin = pos.cos().contiguous(), pos.sin().contiguous()
+    qs, ks = torch.rand(hq, device="cuda") + 0.5, torch.rand(hk, device="cuda") + 0.5
+    g = torch.randn(t, width, device="cuda").bfloat16()
+    g_ref = g.clone()
+    (ds_ref,) = c.rope_qknorm_bwd(qkv, g_ref, g_ref, cos, sin, qs, ks, 256, hq, hk, hd, 1e-6, True, -3e38, 5.0)
+    ds, gq, gsf = c.rope_qknorm_bwd(qkv, g, g, cos, sin, qs, ks, 256, hq, hk, hd, 1e-6, True, -3e38, 5.0, None, True)
+    assert torch.equal(g, g_ref) and torch.equal(ds, ds_ref)
+    _check_copy(gq, gsf, g, t)
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (1000, 768, 768), (4096, 2304, 768), (200, 1000, 256)])
@@ -77,17 +156,17 @@ def test_gemm_mxfp8_batched_and_grouped(ops):
     c.gemm_mxfp8(aq, asf, bq, bsf, d, 0.5)
     want = torch.stack([0.5 * ref.mxfp8_linear(a[i].float(), b[i].float()) for i in range(3)])
     assert rel(d, want) < 4e-3
-    counts, e, n, k = [0, 128, 384, 256], 4, 512, 256
+    counts, e, n, k = [0, 256, 512, 256], 4, 640, 256                     # expert segments are padded to the 256 rows of a CTA pair
     rows = sum(counts)
-    x = torch.randn(rows + 128, k, device="cuda").bfloat16()          # one spare tile beyond the routed rows
+    x = torch.randn(rows + 256, k, device="cuda").bfloat16()          # one spare pair tile beyond the routed rows
     w = torch.randn(e, n, k, device="cuda").bfloat16()
-    tiles = torch.tensor(sum([[i] * (cnt // 128) for i, cnt in enumerate(counts)], []) + [0], dtype=torch.int32, device="cuda")
+    tiles = torch.tensor(sum([[i] * (cnt // 128) for i, cnt in enumerate(counts)], []) + [0, 0], dtype=torch.int32, device="cuda")
     meta = torch.tensor([rows // 128, rows], dtype=torch.int32, device="cuda")
     xq, xsf = c.mxfp8_quantize(x, meta[1:2])
     wq, wsf = c.mxfp8_quantize(w)
-    y = torch.zeros(rows + 128, n, device="cuda", dtype=torch.bfloat16)
+    y = torch.zeros(rows + 256, n, device="cuda", dtype=torch.bfloat16)
     c.gemm_mxfp8(xq, xsf, wq, wsf, y, 1.0, tiles, meta)
-    starts = [0, 0, 128, 512]
+    starts = [0, 0, 256, 768]
     want = torch.cat([ref.mxfp8_linear(x[s:s + cnt].float(), w[i].float()) for i, (s, cnt) in enumerate(zip(starts, counts))])
     assert rel(y[:rows], want) < 4e-3
     assert y[rows:].abs().max().item() == 0.0                           # tiles beyond num_m_tiles are not written

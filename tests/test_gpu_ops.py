@@ -212,6 +212,43 @@ def test_polar_express_gemms(ops):
         assert rel(folded, same_regime) < 5e-2, shape
 
 
+def test_polar_express_on_router_sized_matrices(ops):
+    """Matrices far below one tile (a router: experts x hidden) run through the same batched tcgen05 iteration; the fused
+    engine relies on it to keep routers off the host path."""
+    torch.manual_seed(16)
+    for shape in [(12, 8, 768), (5, 64, 1024), (3, 16, 256)]:
+        g = torch.randn(shape, device="cuda")
+        raw = (g * 1e-3).bfloat16()
+        sumsq = raw.float().pow(2).sum(dim=(-2, -1))
+        got = ops.polar_express_bf16(raw.clone(), sumsq)
+        want = ref.polar_express(raw.float(), dtype=torch.float32)
+        assert got.shape == raw.shape and torch.isfinite(got.float()).all()
+        assert rel(got, want) < 1.5e-1, (shape, rel(got, want))
+
+
+def test_adamw_sharded_tracks_torch_adamw_over_a_thousand_steps(ops):
+    """The sharded AdamW kernel (IEEE division and square root, fp32 moments) against `torch.optim.AdamW` on the same
+    gradient stream for 1000 steps: parameters stay within float rounding of each other."""
+    c = ops.ext()
+    torch.manual_seed(17)
+    n = 4096
+    p = torch.randn(n, device="cuda") * 0.02
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref_p], lr=3e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    grads = torch.zeros(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    decay = torch.full((n,), 0.1, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(18)
+    for step in range(1, 1001):
+        g = torch.randn(n, device="cuda", generator=gen) * (1.0 + 0.5 * torch.sin(torch.tensor(step / 50.0)).item())
+        grads.copy_(g)
+        ref_p.grad = g.clone()
+        opt.step()
+        c.adamw_sharded(p, grads, m, v, decay, 0, n, 3e-3, 0.9, 0.95, 1e-8, step, [0], [0])
+    err = (p - ref_p.detach()).abs().max().item()
+    assert err < 2e-5, err
+
+
 def test_adamw_and_muon_steps(ops):
     from gpt_moe_b200.optim import AdamW, Muon
     torch.manual_seed(7)
