@@ -20,6 +20,8 @@ struct AttnParams {
     float softcap;                  // > 0: logits are soft-capped, z = softcap * tanh(scale * s / softcap), before the softmax
     void* out;                      // forward: O [tokens, heads*64] bf16
     long long out_stride;
+    uint8_t* out_q;                 // optional MXFP8 copy of O (row pitch heads*64): e4m3 payload ...
+    uint8_t* out_sf;                // ... and its scale records (the output projection's GEMM operand, written by the epilogue)
     float* lse;                     // [batch, heads, seq] natural-log LSE of the scaled scores
     // backward
     const float* delta;             // [batch, heads, seq] rowsum(dO * O)

@@ -18,6 +18,7 @@
 // Reference counterpart: FlexAttention with the causal + sliding-window BlockMask (model/gpt.py:311-687,
 // model/attention/self_attention.py:250-255); here the window test is exact per token in every tile.
 #include "../common/ptx.cuh"
+#include "../common/mxfp8.cuh"
 #include "attn.h"
 
 namespace gm {
@@ -292,6 +293,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 w.z = pack_bf16x2(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
                 w.w = pack_bf16x2(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
                 *reinterpret_cast<uint4*>(out + 8 * q) = w;
+            }
+            if (p.out_q != nullptr) {
+                // the thread's 32 output columns are exactly one MXFP8 block of the token-major row: quantise the bf16 values just
+                // stored (reference: attention output quantised straight from its own layout, model/linear/fp8/custom/output_projection.py:16-49)
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) { o[i] = round_bf16(o[i] * inv); amax = fmaxf(amax, fabsf(o[i])); }
+                const uint32_t e8 = e8m0_from_amax(amax);
+                const float qs = inv_scale_from_e8m0(e8);
+                const int width = p.heads * AT_D, col = head * AT_D + half * 32;
+                uint8_t* dst = p.out_q + token * width + col;
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    uint4 w;
+                    w.x = pack_e4m3x4(o[16 * q] * qs, o[16 * q + 1] * qs, o[16 * q + 2] * qs, o[16 * q + 3] * qs);
+                    w.y = pack_e4m3x4(o[16 * q + 4] * qs, o[16 * q + 5] * qs, o[16 * q + 6] * qs, o[16 * q + 7] * qs);
+                    w.z = pack_e4m3x4(o[16 * q + 8] * qs, o[16 * q + 9] * qs, o[16 * q + 10] * qs, o[16 * q + 11] * qs);
+                    w.w = pack_e4m3x4(o[16 * q + 12] * qs, o[16 * q + 13] * qs, o[16 * q + 14] * qs, o[16 * q + 15] * qs);
+                    *reinterpret_cast<uint4*>(dst + 16 * q) = w;
+                }
+                p.out_sf[sf_offset(token, col >> 5, (width + 127) >> 7)] = static_cast<uint8_t>(e8);
             }
             // natural-log LSE of the scaled scores, layout [batch, head, seq]
             if (half == 0) p.lse[(static_cast<long long>(batch) * p.heads + head) * p.seq_len + qpos] = m * 0.69314718056f + __logf(l);

@@ -321,66 +321,56 @@ quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ 
 // Both quantised copies of a weight in one pass over it: w[rows, cols] bf16 (batched over z) ->
 //   q  [rows, cols] e4m3, scales per 32 consecutive columns (the forward GEMM contracts over the columns), and
 //   qt [cols, rows] e4m3 = the transpose, scales per 32 consecutive ORIGINAL rows (the input-gradient GEMM contracts over them).
-// Block = 32 rows x 128 columns, 256 threads; thread (tx, ty) holds columns 4*tx..4*tx+3 of rows ty, ty+8, ty+16, ty+24, so a
-// row block of 32 columns is 8 adjacent lanes (shuffle reduction) and a column block is the tile's 32 rows (shared memory).
+// Block = 32 rows x 128 columns, 256 threads.  Row layout: thread (tx, ty) holds columns 4*tx..4*tx+3 of rows ty, ty+8, ty+16,
+// ty+24, a 32-column block is 8 adjacent lanes (shuffle reduction).  The values also go to a shared-memory tile, from which
+// thread (col = t / 2, half = t % 2) reads 16 rows of one column: the column's 32 rows are the pair's two halves (one
+// shuffle), and each thread stores 16 consecutive bytes of the transposed copy (a pair of lanes fills a 32-byte sector).
 __global__ void __launch_bounds__(256)
 quantize_weight_dual_kernel(const __nv_bfloat16* __restrict__ w, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, uint8_t* __restrict__ qt,
                             uint8_t* __restrict__ sft, int rows, int cols, long long batch_stride, long long sf_batch_stride,
                             long long sft_batch_stride) {
-    __shared__ float colmax[8][128];
-    __shared__ uint32_t cole8[128];
-    __shared__ __align__(16) uint8_t tt[128][32];
+    __shared__ __align__(16) float tile[32][132];
     const int z = blockIdx.z;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int c0 = blockIdx.x * 128, r0 = blockIdx.y * 32;
     const int c = c0 + 4 * tx;
     const __nv_bfloat16* src = w + z * batch_stride;
     const int kb_row = (cols + 127) >> 7, kb_col = (rows + 127) >> 7;
-    float v[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int r = r0 + ty + 8 * i;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
         if (r < rows && c < cols) {
             const uint2 raw = *reinterpret_cast<const uint2*>(src + static_cast<long long>(r) * cols + c);
             const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
             const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-            v[i][0] = a.x; v[i][1] = a.y; v[i][2] = b.x; v[i][3] = b.y;
-        } else {
-            v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f;
+            v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
         }
+        *reinterpret_cast<float4*>(&tile[ty + 8 * i][4 * tx]) = make_float4(v[0], v[1], v[2], v[3]);
         uint32_t out[1];
-        const uint32_t e8 = quantize_block_lanes<4>(v[i], out);
+        const uint32_t e8 = quantize_block_lanes<4>(v, out);
         if (r < rows && c < cols) {
             *reinterpret_cast<uint32_t*>(q + z * batch_stride + static_cast<long long>(r) * cols + c) = out[0];
             if ((tx & 7) == 0) sf[z * sf_batch_stride + sf_offset(r, c >> 5, kb_row)] = static_cast<uint8_t>(e8);
         }
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-        colmax[ty][4 * tx + j] = fmaxf(fmaxf(fabsf(v[0][j]), fabsf(v[1][j])), fmaxf(fabsf(v[2][j]), fabsf(v[3][j])));
     __syncthreads();
-    if (threadIdx.x < 128) {
-        float m = 0.f;
+    const int col = threadIdx.x >> 1, hf = threadIdx.x & 1;
+    float u[16];
+    float amax = 0.f;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) m = fmaxf(m, colmax[k][threadIdx.x]);
-        const uint32_t e8 = e8m0_from_amax(m);
-        cole8[threadIdx.x] = e8;
-        if (c0 + threadIdx.x < cols) sft[z * sft_batch_stride + sf_offset(c0 + threadIdx.x, r0 >> 5, kb_col)] = static_cast<uint8_t>(e8);
-    }
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const float inv = inv_scale_from_e8m0(cole8[4 * tx + j]);
-        const uint32_t packed = pack_e4m3x4(v[0][j] * inv, v[1][j] * inv, v[2][j] * inv, v[3][j] * inv);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) tt[4 * tx + j][ty + 8 * i] = static_cast<uint8_t>(packed >> (8 * i));
-    }
-    __syncthreads();
-    {
-        const int col = threadIdx.x >> 1, hf = threadIdx.x & 1;
-        if (c0 + col < cols && r0 + hf * 16 < rows)
-            *reinterpret_cast<uint4*>(qt + z * batch_stride + static_cast<long long>(c0 + col) * rows + r0 + hf * 16) =
-                *reinterpret_cast<const uint4*>(&tt[col][hf * 16]);
+    for (int k = 0; k < 16; ++k) { u[k] = tile[hf * 16 + k][col]; amax = fmaxf(amax, fabsf(u[k])); }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    const uint32_t e8 = e8m0_from_amax(amax);
+    const float inv = inv_scale_from_e8m0(e8);
+    if (c0 + col < cols && r0 + hf * 16 < rows) {
+        uint4 o;
+        o.x = pack_e4m3x4(u[0] * inv, u[1] * inv, u[2] * inv, u[3] * inv);
+        o.y = pack_e4m3x4(u[4] * inv, u[5] * inv, u[6] * inv, u[7] * inv);
+        o.z = pack_e4m3x4(u[8] * inv, u[9] * inv, u[10] * inv, u[11] * inv);
+        o.w = pack_e4m3x4(u[12] * inv, u[13] * inv, u[14] * inv, u[15] * inv);
+        *reinterpret_cast<uint4*>(qt + z * batch_stride + static_cast<long long>(c0 + col) * rows + r0 + hf * 16) = o;
+        if (hf == 0) sft[z * sft_batch_stride + sf_offset(c0 + col, r0 >> 5, kb_col)] = static_cast<uint8_t>(e8);
     }
 }
 

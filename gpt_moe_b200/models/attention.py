@@ -138,7 +138,7 @@ class SelfAttention(nn.Module):
             y = mxfp8.qkv_rope_attention(
                 x, weights, cos, sin, self.q_scale if self.use_qk_norm else None, self.k_scale if self.use_qk_norm else None,
                 b, t, hq, hk, d, self.qk_eps, self.qk_norm_type == "rms", self.qk_scale_min, self.qk_scale_max, window, None,
-                self.softcap, doc_start)
+                self.softcap, doc_start, quantize_out=self.out_proj.precision in ("mxfp8", "fp8"))
             if y is not None:
                 return y
         qkv = cuda_ops.linear_multi(x, weights, self.q_proj.precision)
@@ -150,7 +150,10 @@ class SelfAttention(nn.Module):
         b, t, _ = x.shape
         y = self._fused_rope_attention(x, ctx)
         if y is not None:
-            return self.out_proj(y.reshape(b, t, self.attn_dim))
+            merged = y.reshape(b, t, self.attn_dim)
+            if getattr(y, "mxq", None) is not None:           # MXFP8 copy written by the attention kernel's epilogue
+                merged.mxq = y.mxq
+            return self.out_proj(merged)
         q, k, v = self.project_qkv(x)
         y = api.attention(
             q, k, v, causal=self.is_causal,

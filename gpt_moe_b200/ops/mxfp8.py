@@ -13,8 +13,8 @@ payload and scale records next to the bf16 tensor (which the bf16 weight-gradien
   gated-combine backward      -> dY of the down projection              (`combine_bwd(quantize=True)`)
   activation backward         -> dY of the up projection                (`activation_bwd(quantize=True)`)
   RoPE / QK-norm backward     -> dY of the QKV projection               (`rope_qknorm_bwd(quantize=True)`)
-Only the attention output (input of the output projection) and the output projection's dY are quantised by
-`mxfp8_quantize`, one pass over a [tokens, hidden] matrix each.  Quantised weights — row-wise for the forward GEMM and
+  attention forward epilogue  -> input of the output projection         (`attn_fwd(quantize=True)`)
+Only the output projection's dY is quantised by `mxfp8_quantize`, one pass over a [tokens, hidden] matrix.  Quantised weights — row-wise for the forward GEMM and
 transposed for the input-gradient GEMM, both from one pass over the bf16 weight — are cached until the parameters change.
 The oracle is `ops.reference.mxfp8_linear` / `mxfp8_quantize`.
 
@@ -154,7 +154,7 @@ class _MXFP8QKVAttentionFn(torch.autograd.Function):
     def forward(ctx, x: Tensor, xq: Optional[Tensor], xsf: Optional[Tensor], cos, sin, q_scale, k_scale, cfg: tuple, doc_start,
                 *weights: Tensor):
         c = co.ext()
-        batch, seq_len, hq, hk, d, eps, rms, smin, smax, window, scale, softcap = cfg
+        batch, seq_len, hq, hk, d, eps, rms, smin, smax, window, scale, softcap, quant_out = cfg
         x2 = co._as_bf16_2d(x)
         w, wq, wsf, wqt, wsft = _quantized_weight(weights, stack=False)
         if xq is None:
@@ -169,7 +169,8 @@ class _MXFP8QKVAttentionFn(torch.autograd.Function):
         q = packed[..., : hq * d].unflatten(-1, (hq, d))
         k = packed[..., hq * d: (hq + hk) * d].unflatten(-1, (hk, d))
         v = packed[..., (hq + hk) * d:].unflatten(-1, (hk, d))
-        o, lse = c.attn_fwd(q, k, v, window, scale, softcap, doc_start)
+        res = c.attn_fwd(q, k, v, window, scale, softcap, doc_start, quant_out)
+        o, lse = res[0], res[1]
         empty = qkv.new_empty(0)
         ctx.save_for_backward(x2, qkv, out, o, lse, cos if cos is not None else empty, sin if sin is not None else empty,
                               qs if qs is not None else empty, ks if ks is not None else empty, wqt, wsft)
@@ -178,13 +179,16 @@ class _MXFP8QKVAttentionFn(torch.autograd.Function):
         ctx.meta = (x.shape, x.dtype, tuple(w.shape))
         ctx.scale_shapes = (None if q_scale is None else (q_scale.shape, q_scale.dtype),
                             None if k_scale is None else (k_scale.shape, k_scale.dtype))
-        return o
+        if quant_out:                             # MXFP8 copy of the attention output, written by the kernel's epilogue
+            ctx.mark_non_differentiable(res[2], res[3])
+            return o, res[2], res[3]
+        return o, None, None
 
     @staticmethod
-    def backward(ctx, d_out: Tensor):
+    def backward(ctx, d_out: Tensor, _dq=None, _dsf=None):
         c = co.ext()
         x2, qkv, out, o, lse, cos, sin, qs, ks, wqt, wsft = ctx.saved_tensors
-        batch, seq_len, hq, hk, d, eps, rms, smin, smax, window, scale, softcap = ctx.cfg
+        batch, seq_len, hq, hk, d, eps, rms, smin, smax, window, scale, softcap, _ = ctx.cfg
         has_rope, has_norm = ctx.flags
         x_shape, x_dtype, w_shape = ctx.meta
         packed = out.view(batch, seq_len, -1)
@@ -218,17 +222,22 @@ class _MXFP8QKVAttentionFn(torch.autograd.Function):
 
 def qkv_rope_attention(x: Tensor, weights: Sequence[Tensor], cos, sin, q_scale, k_scale, batch: int, seq_len: int, hq: int, hk: int,
                        d: int, eps: float, rms: bool, smin: float, smax: float, window: Optional[int], scale: Optional[float],
-                       softcap: float = 0.0, doc_start: Optional[Tensor] = None) -> Optional[Tensor]:
-    """x [batch, seq_len, hidden] -> attention output [batch, seq_len, hq, 64]; None when the projection shape is not covered."""
+                       softcap: float = 0.0, doc_start: Optional[Tensor] = None, quantize_out: bool = False) -> Optional[Tensor]:
+    """x [batch, seq_len, hidden] -> attention output [batch, seq_len, hq, 64]; None when the projection shape is not covered.
+    `quantize_out`: an MXFP8 projection consumes the output; its quantised copy then comes attached as `.mxq`."""
     k_dim, n = weights[0].shape[1], sum(w.shape[0] for w in weights)
     if not supported(k_dim, n) or n % 32:
         return None
     smin, smax = max(smin, -3.0e38), min(smax, 3.0e38)
     w = seq_len if window is None else int(window)
-    cfg = (batch, seq_len, hq, hk, d, eps, rms, smin, smax, w, d ** -0.5 if scale is None else float(scale), float(softcap))
+    quant = bool(quantize_out and (hq * 64) % 128 == 0)
+    cfg = (batch, seq_len, hq, hk, d, eps, rms, smin, smax, w, d ** -0.5 if scale is None else float(scale), float(softcap), quant)
     co.count_path("attention:tcgen05")
     xq, xsf = _attached_copy(x)
-    return _MXFP8QKVAttentionFn.apply(x, xq, xsf, cos, sin, q_scale, k_scale, cfg, doc_start, *weights)
+    o, oq, osf = _MXFP8QKVAttentionFn.apply(x, xq, xsf, cos, sin, q_scale, k_scale, cfg, doc_start, *weights)
+    if quant:
+        o.mxq = (oq, osf)
+    return o
 
 
 class _MXFP8MoEExpertsFn(torch.autograd.Function):

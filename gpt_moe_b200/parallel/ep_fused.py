@@ -84,7 +84,11 @@ def release_workspaces() -> None:
 
 class _FusedEPMoEFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, hidden: Tensor, gates: Tensor, top_idx: Tensor, activation: str, ws: EPWorkspace, layer_key: int, *weights: Tensor):
+    def forward(ctx, hidden: Tensor, gates: Tensor, top_idx: Tensor, activation: str, ws: EPWorkspace, layer_key: int, mx: bool,
+                *weights: Tensor):
+        """`mx`: the expert projections are MXFP8 — forward and input-gradient grouped GEMMs read e4m3 operands (received rows and
+        received gradients are quantised where they land, activations by the kernel that writes them); weight gradients stay
+        bf16 x bf16 -> fp32."""
         c = co.ext()
         n_local = ws.per_rank
         up, down = weights[:n_local], weights[n_local:]
@@ -100,17 +104,29 @@ class _FusedEPMoEFn(torch.autograd.Function):
         c.ep_zero_pads(packed, seg_ends, valid_ends)
         (route_row,) = c.ep_dispatch(h2, idx, dest, local_seg_ends, my_base, None, None, packed, recv_buf.deltas, n_local)
         ws.barrier()
-        w_up, w_down = co.stacked_weight(up), co.stacked_weight(down)
-        pre = torch.empty((ws.cap_rows, w_up.shape[1]), dtype=BF16, device=hidden.device)
-        c.gemm_bf16(packed, w_up, pre, False, False, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
-        (act,) = c.activation_fwd(pre, activation, meta)
         y = ws.rows(ws.ret)
-        c.gemm_bf16(act, w_down, y, False, False, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
+        if mx:
+            from ..ops import mxfp8
+            w_up, uq, usf, uqt, usft = mxfp8._quantized_weight(up, stack=True)
+            w_down, dq, dsf, dqt, dsft = mxfp8._quantized_weight(down, stack=True)
+            pq, psf = c.mxfp8_quantize(packed, meta[1:2])
+            pre = torch.empty((ws.cap_rows, w_up.shape[1]), dtype=BF16, device=hidden.device)
+            c.gemm_mxfp8(pq, psf, uq, usf, pre, 1.0, tile_expert, meta)
+            act, aq, asf = c.activation_fwd(pre, activation, meta, quantize=True)
+            c.gemm_mxfp8(aq, asf, dq, dsf, y, 1.0, tile_expert, meta)
+            w_up, w_down = (uqt, usft), (dqt, dsft)            # what the backward needs of the weights
+        else:
+            w_up, w_down = co.stacked_weight(up), co.stacked_weight(down)
+            pre = torch.empty((ws.cap_rows, w_up.shape[1]), dtype=BF16, device=hidden.device)
+            c.gemm_bf16(packed, w_up, pre, False, False, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
+            (act,) = c.activation_fwd(pre, activation, meta)
+            c.gemm_bf16(act, w_down, y, False, False, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
+            w_up, w_down = (w_up,), (w_down,)
         ws.barrier()
         out, y_rows = c.ep_combine(y, idx, route_row, gates32, True, ws.ret.deltas, n_local)
         ctx.save_for_backward(packed, pre, act, y_rows, idx, dest, local_seg_ends, my_base, route_row, seg_ends, valid_ends, tile_expert, meta,
-                              gates32, w_up, w_down)
-        ctx.activation, ctx.ws, ctx.weights = activation, ws, weights
+                              gates32, *w_up, *w_down)
+        ctx.activation, ctx.ws, ctx.weights, ctx.mx = activation, ws, weights, mx
         ctx.hidden_meta = (hidden.shape, hidden.dtype, gates.dtype)
         ctx.mark_non_differentiable(top_idx)
         return out.view(*hidden.shape[:-1], out.shape[-1]).to(hidden.dtype)
@@ -118,8 +134,10 @@ class _FusedEPMoEFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout: Tensor):
         c = co.ext()
-        (packed, pre, act, y_rows, idx, dest, local_seg_ends, my_base, route_row, seg_ends, valid_ends, tile_expert, meta, gates32,
-         w_up, w_down) = ctx.saved_tensors
+        (packed, pre, act, y_rows, idx, dest, local_seg_ends, my_base, route_row, seg_ends, valid_ends, tile_expert, meta,
+         gates32) = ctx.saved_tensors[:14]
+        saved_w = ctx.saved_tensors[14:]
+        mx = ctx.mx
         ws: EPWorkspace = ctx.ws
         e = ws.per_rank
         up, down = ctx.weights[:e], ctx.weights[e:]
@@ -130,7 +148,13 @@ class _FusedEPMoEFn(torch.autograd.Function):
         _, dgates = c.ep_dispatch(d2, idx, dest, local_seg_ends, my_base, gates32, y_rows, dy, ws.grad_recv.deltas, e)
         ws.barrier()
         dact = torch.empty_like(act)
-        c.gemm_bf16(dy, w_down, dact, False, True, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
+        if mx:
+            uqt, usft, dqt, dsft = saved_w
+            gq, gsf = c.mxfp8_quantize(dy, meta[1:2])
+            c.gemm_mxfp8(gq, gsf, dqt, dsft, dact, 1.0, tile_expert, meta)
+        else:
+            w_up, w_down = saved_w
+            c.gemm_bf16(dy, w_down, dact, False, True, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
         grads: List[Optional[Tensor]] = [None] * (2 * e)
         ends = seg_ends
 
@@ -146,13 +170,17 @@ class _FusedEPMoEFn(torch.autograd.Function):
                 grads[offset + i] = dw[i].to(p.dtype)
 
         wgrad(dy, act, down, e)
-        (dpre,) = c.activation_bwd(dact, pre, ctx.activation, meta)
+        res = c.activation_bwd(dact, pre, ctx.activation, meta, quantize=mx)
+        dpre = res[0]
         wgrad(dpre, packed, up, 0)
         dpacked = ws.rows(ws.ret)
-        c.gemm_bf16(dpre, w_up, dpacked, False, True, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
+        if mx:
+            c.gemm_mxfp8(res[1], res[2], uqt, usft, dpacked, 1.0, tile_expert, meta)
+        else:
+            c.gemm_bf16(dpre, w_up, dpacked, False, True, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
         ws.barrier()
         (dhidden,) = c.ep_combine(dpacked, idx, route_row, None, False, ws.ret.deltas, e)
-        return (dhidden.view(shape).to(dtype), dgates.to(gdtype), None, None, None, None) + tuple(grads)
+        return (dhidden.view(shape).to(dtype), dgates.to(gdtype), None, None, None, None, None) + tuple(grads)
 
 
 def fused_expert_parallel_moe(moe, hidden: Tensor, top_idx: Tensor, gates: Tensor, args: dict) -> Tensor:
@@ -161,7 +189,10 @@ def fused_expert_parallel_moe(moe, hidden: Tensor, top_idx: Tensor, gates: Tenso
         raise NotImplementedError("expert biases are not supported by the fused expert-parallel path")
     h2 = hidden.reshape(-1, hidden.shape[-1])
     ws = workspace_for(moe.ep_group, top_idx.numel(), h2.shape[-1], moe.num_experts, hidden.device, float(getattr(moe, "ep_capacity_factor", 0.0)))
-    return _FusedEPMoEFn.apply(h2, gates, top_idx, args["activation"], ws, id(moe), *args["up_weights"], *args["down_weights"])
+    up, down = args["up_weights"], args["down_weights"]
+    wants_mx = args.get("up_precision") in ("mxfp8", "fp8") or args.get("down_precision") in ("mxfp8", "fp8")
+    mx = bool(wants_mx and up[0].shape[1] % 128 == 0 and up[0].shape[0] % 128 == 0 and down[0].shape[1] % 128 == 0 and down[0].shape[0] % 128 == 0)
+    return _FusedEPMoEFn.apply(h2, gates, top_idx, args["activation"], ws, id(moe), mx, *up, *down)
 
 
 def supported(moe, hidden: Tensor) -> bool:

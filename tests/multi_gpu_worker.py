@@ -90,6 +90,18 @@ def check_expert_parallel_ops():
         for i in local:
             errs.append(((got[i].float() - want[i].float()).norm() / (want[i].float().norm() + 1e-6)).item())
         worst = max(worst, max(errs))
+    # the same exchange with MXFP8 expert projections: against all experts computed locally with MXFP8 projections
+    want_out = cuda_ops.moe_experts(hidden, top_idx, gates, ups, downs, None, None, "swiglu", "mxfp8", "mxfp8")
+    want = grads_of(want_out)
+    for t in want[2:]:
+        dist.all_reduce(t)
+    args_mx = dict(args, up_precision="mxfp8", down_precision="mxfp8")
+    out = expert_parallel_moe(_Shard(dist.group.WORLD, world, experts, True), hidden, top_idx, gates, args_mx)
+    got = grads_of(out)
+    errs = [((out.float() - want_out.float()).norm() / want_out.float().norm()).item()]
+    for i in [0, 1] + [2 + lo + i for i in range(n)] + [2 + experts + lo + i for i in range(n)]:
+        errs.append(((got[i].float() - want[i].float()).norm() / (want[i].float().norm() + 1e-6)).item())
+    worst = max(worst, max(errs))
     cuda_ops.check_status()
     return worst
 

@@ -128,6 +128,16 @@ def test_producers_emit_the_quantised_copy_of_what_they_write(ops):
     ds, gq, gsf = c.rope_qknorm_bwd(qkv, g, g, cos, sin, qs, ks, 256, hq, hk, hd, 1e-6, True, -3e38, 5.0, None, True)
     assert torch.equal(g, g_ref) and torch.equal(ds, ds_ref)
     _check_copy(gq, gsf, g, t)
+    # attention forward: the epilogue writes the copy of the token-major output rows (operand of the output projection)
+    b_, t_, h_ = 2, 256, 4
+    packed_qkv = torch.randn(b_, t_, 3 * h_ * 64, device="cuda").bfloat16()
+    qh = packed_qkv[..., : h_ * 64].unflatten(-1, (h_, 64))
+    kh = packed_qkv[..., h_ * 64: 2 * h_ * 64].unflatten(-1, (h_, 64))
+    vh = packed_qkv[..., 2 * h_ * 64:].unflatten(-1, (h_, 64))
+    out, lse, oq, osf = c.attn_fwd(qh, kh, vh, 100, 0.125, 0.0, None, True)
+    out_plain, _ = c.attn_fwd(qh, kh, vh, 100, 0.125)
+    assert torch.equal(out, out_plain)
+    _check_copy(oq, osf, out.reshape(b_ * t_, h_ * 64), b_ * t_)
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (1000, 768, 768), (4096, 2304, 768), (200, 1000, 256)])
