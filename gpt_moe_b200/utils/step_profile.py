@@ -1,4 +1,4 @@
-"""Per-kernel breakdown of one training step: `python -m gpt_moe_b200.utils.step_profile [--preset small] [--rows 40] [--set k=v ...]`.
+"""Per-kernel breakdown of one training step: `python -m gpt_moe_b200.utils.step_profile [--preset small] [--precision mxfp8|default] [--rows 40] [--set k=v ...]`.
 
 Runs a few warm-up steps of the preset on synthetic data, records one step with `torch.profiler` (CUPTI kernel
 timings, no replay) and prints the kernels sorted by total device time together with the step's wall time.  Shares of the
@@ -16,12 +16,13 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--preset", default="small")
     ap.add_argument("--rows", type=int, default=40)
+    ap.add_argument("--precision", default="mxfp8", choices=["default", "mxfp8"])
     ap.add_argument("--set", dest="overrides", action="append", default=[])
     args = ap.parse_args()
     from torch.profiler import ProfilerActivity, profile
     from gpt_moe_b200.config import apply_overrides, get_preset
     from gpt_moe_b200.runtime.trainer import Trainer
-    gpt_config, training_config = get_preset(args.preset)
+    gpt_config, training_config = get_preset(args.preset, precision=args.precision)
     apply_overrides(gpt_config, training_config, args.overrides)
     training_config.kernel_warmup_train_steps = 0
     trainer = Trainer(gpt_config, training_config, device_type="cuda", quiet=True)
