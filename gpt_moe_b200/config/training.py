@@ -16,7 +16,7 @@ import math
 import os
 from dataclasses import dataclass, field
 from datetime import datetime
-from typing import Any, Dict, List, Tuple
+from typing import Any, Dict, List, Optional, Tuple
 
 import torch.nn as nn
 
@@ -201,8 +201,9 @@ class TrainingConfig:
     use_fused_collectives: bool = True  # peer-memory kernels; False = NCCL calls (the measured baseline)
     use_cuda_graphs: bool = True        # fused engine: forward+backward of a training step is captured once per (shape, window) and replayed
     nvtx_ranges: bool = False           # NVTX ranges around the phases of a training step (forward+backward per micro-step, optimizer)
-    overlap_grad_reduce: bool = False   # fused engine: a block's gradient reduce (+ momentum, pack) runs on a second stream beside the
-                                        # backward of the earlier blocks; orthogonalisation and the weight push follow the backward pass
+    overlap_grad_reduce: Optional[bool] = None   # fused engine: a block's gradient reduce (+ momentum, pack) runs on a second stream beside
+                                        # the backward of the earlier blocks; orthogonalisation and the weight push follow the backward
+                                        # pass.  None = on from 4 ranks up (with two the hidden transfer is smaller than the cost)
     allow_nccl_fallback: bool = False   # fused engine requested but symmetric memory unavailable: fall back to NCCL instead of raising
     ep_capacity_factor: float = 0.0     # fused expert parallelism: receive buffers hold this many times a rank's own slots (0 = worst case)
     step_deadline_s: float = 0.0      # >0 arms the host watchdog: abort the job if a step exceeds it

@@ -87,8 +87,17 @@ extern "C" int gm_residual_bwd_noalloc(const float* dxn, const void* branch, con
     // same block count as the allocating path, so both sum in the same order
     const long long want = n / 4 / 256 + 1;
     const int blocks = static_cast<int>(want < kMaxBlocks ? want : kMaxBlocks);
-    residual_bwd_noalloc_kernel<<<blocks, 256, 0, s>>>(dxn, static_cast<const __nv_bfloat16*>(branch), beta,
-                                                       static_cast<__nv_bfloat16*>(dbranch), scratch, n);
-    residual_bwd_noalloc_finish<<<1, 256, 0, s>>>(scratch, dbeta, blocks);
-    return cudaGetLastError() == cudaSuccess ? 0 : 2;
+    // launch errors are returned by the launch that caused them (cudaPeekAtLastError after each would also show an error left
+    // by earlier work and cudaGetLastError would clear it: neither is this function's business)
+    void* args1[] = {&dxn, &branch, &beta, &dbranch, &scratch, &n};
+    if (cudaLaunchKernel(reinterpret_cast<const void*>(residual_bwd_noalloc_kernel), dim3(blocks), dim3(256), args1, 0, s) != cudaSuccess) return 2;
+    int blocks_arg = blocks;
+    const float* partial = scratch;
+    void* args2[] = {&partial, &dbeta, &blocks_arg};
+    if (cudaLaunchKernel(reinterpret_cast<const void*>(residual_bwd_noalloc_finish), dim3(1), dim3(256), args2, 0, s) != cudaSuccess) return 2;
+    return 0;
+}
+
+extern "C" void gm_residual_bwd_noalloc_forget(void) {
+    for (int d = 0; d < kMaxDevices; ++d) g_scratch_address[d] = nullptr;
 }

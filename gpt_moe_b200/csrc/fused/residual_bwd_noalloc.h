@@ -25,9 +25,20 @@ extern "C" {
 // The first call on each device looks up the array's device address (one cudaGetSymbolAddress, no allocation); make that
 // first call outside any stream capture.  No call allocates or frees device memory, in this library or in torch.
 //
-// Returns 0 on success, 1 for an invalid size or null pointer, 2 if the set-up or the launch reported a CUDA error.
+// Threads: the looked-up address is cached per device ordinal in a plain host array.  Two host threads that make the first
+// call on one device at the same time both look the address up and store the same value, which is harmless; after that the
+// cache is only read.  What the threads must not do is let their launches overlap on the GPU (see "Scratch" above).
+// Device reset: the cache is keyed by the device ordinal, not by the context.  After cudaDeviceReset (or with a second
+// context on the same ordinal) the cached address belongs to a context that no longer exists; call
+// gm_residual_bwd_noalloc_forget() after a reset so that the next call looks the address up again.
+//
+// Returns 0 on success, 1 for an invalid size or null pointer, 2 if the set-up or one of THIS call's two launches reported a
+// CUDA error (an error left pending by earlier work on the device is neither reported nor cleared by this function).
 int gm_residual_bwd_noalloc(const float* dxn, const void* branch, const float* beta, void* dbranch, float* dbeta,
                             long long n, void* stream);
+
+// Drop the cached scratch addresses of every device (after a cudaDeviceReset).  Allocates nothing.
+void gm_residual_bwd_noalloc_forget(void);
 
 #define GM_RESIDUAL_BWD_NOALLOC_SCRATCH_FLOATS 1184
 #define GM_RESIDUAL_BWD_NOALLOC_MAX_ELEMS (1LL << 34)

@@ -225,7 +225,8 @@ class FusedEngine:
         # stream the owner of a matrix waits (bounded) for the block's flags of all ranks and then sums the block's gradients
         # out of the peers' buffers (with momentum and the bf16 pack) while the main stream continues with the earlier
         # blocks.  Orthogonalisation and the weight push stay behind the backward pass, where every bucket runs as one batch.
-        self.overlap = bool(self.world > 1 and getattr(training_config, "overlap_grad_reduce", False))
+        wanted = getattr(training_config, "overlap_grad_reduce", None)
+        self.overlap = bool(self.world > 1 and (self.world >= 4 if wanted is None else wanted))
         layers = sorted({l for b in self.shared_buckets for l in b.layers} | {self._layer_of(n) for n, _ in shared})
         self.layer_slot = {layer: i for i, layer in enumerate(layers)}
         self.layer_span: Dict[int, Tuple[int, int]] = {}      # element range of a block's matrices in the flat Muon buffers
