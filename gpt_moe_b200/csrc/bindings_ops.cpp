@@ -145,6 +145,46 @@ std::vector<Tensor> rope_qknorm_bwd(const Tensor& x, const Tensor& dy, Tensor& d
     return {dscale};
 }
 
+// Router after the logits GEMM: (top_idx int64 [T, k], gates fp32 [T, k]) and, with `want_balance`, (balance fp32 [1], counts fp32 [E]).
+// renormalise: gates = softmax over the selected logits; otherwise the full-softmax probability of each selected expert.
+std::vector<Tensor> router_fwd(const Tensor& logits, int64_t top_k, bool renormalise, bool want_balance) {
+    c10::cuda::CUDAGuard guard(logits.device());
+    GM_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous() &&
+             (logits.scalar_type() == torch::kBFloat16 || logits.scalar_type() == torch::kFloat32), "router logits: contiguous [tokens, experts] bf16 or fp32");
+    const int tokens = logits.size(0), experts = logits.size(1);
+    auto f32 = logits.options().dtype(torch::kFloat32);
+    Tensor top_idx = torch::empty({tokens, top_k}, logits.options().dtype(torch::kInt64));
+    Tensor gates = torch::empty({tokens, top_k}, f32);
+    Tensor partial, sums, balance;
+    if (want_balance) {
+        partial = torch::empty({2, router_blocks(tokens), experts}, f32);
+        sums = torch::empty({2, experts}, f32);
+        balance = torch::empty({1}, f32);
+    }
+    GM_CHECK(launch_router_fwd(logits.data_ptr(), logits.scalar_type() == torch::kBFloat16, top_idx.data_ptr<int64_t>() ? reinterpret_cast<long long*>(top_idx.data_ptr<int64_t>()) : nullptr,
+                               gates.data_ptr<float>(), want_balance ? partial[0].data_ptr<float>() : nullptr,
+                               want_balance ? partial[1].data_ptr<float>() : nullptr, want_balance ? sums[0].data_ptr<float>() : nullptr,
+                               want_balance ? sums[1].data_ptr<float>() : nullptr, want_balance ? balance.data_ptr<float>() : nullptr, tokens,
+                               experts, top_k, renormalise, stream()),
+             "router kernel: at most 128 experts, top-k at most 8");
+    if (want_balance) return {top_idx, gates, balance, sums[1]};
+    return {top_idx, gates};
+}
+
+// d logits from d gates (optional), d balance (optional, fp32 [1]) and the expert counts of the forward pass.
+Tensor router_bwd(const Tensor& logits, const Tensor& top_idx, const OptTensor& dgates, const OptTensor& dbalance, const OptTensor& counts,
+                  bool renormalise) {
+    c10::cuda::CUDAGuard guard(logits.device());
+    const int tokens = logits.size(0), experts = logits.size(1), top_k = top_idx.size(1);
+    if (dgates.has_value()) GM_CHECK(dgates->scalar_type() == torch::kFloat32 && dgates->is_contiguous() && dgates->numel() == static_cast<int64_t>(tokens) * top_k, "dgates: contiguous fp32 [tokens, k]");
+    if (dbalance.has_value()) GM_CHECK(dbalance->scalar_type() == torch::kFloat32 && dbalance->numel() == 1 && counts.has_value(), "dbalance: one fp32 value, with the forward's counts");
+    Tensor dlogits = torch::empty_like(logits);
+    GM_CHECK(launch_router_bwd(logits.data_ptr(), logits.scalar_type() == torch::kBFloat16, reinterpret_cast<const long long*>(top_idx.data_ptr<int64_t>()),
+                               fptr(dgates), fptr(dbalance), fptr(counts), dlogits.data_ptr(), tokens, experts, top_k, renormalise, stream()),
+             "router kernel: at most 128 experts, top-k at most 8");
+    return dlogits;
+}
+
 // Counted routing.  Returns (dest[S], src_of_row[cap], seg_ends[E], counts[E], tile_expert[cap/128], meta[2]).
 std::vector<Tensor> route(const Tensor& top_idx, int64_t experts) {
     c10::cuda::CUDAGuard guard(top_idx.device());
@@ -156,7 +196,7 @@ std::vector<Tensor> route(const Tensor& top_idx, int64_t experts) {
     Tensor hist = torch::empty({2, chunks, experts}, opt);
     Tensor dest = torch::empty({slots}, opt), src = torch::empty({cap}, opt);
     Tensor seg = torch::empty({experts}, opt), counts = torch::empty({experts}, opt);
-    Tensor tiles = torch::zeros({cap / 128}, opt), meta = torch::empty({2}, opt);
+    Tensor tiles = torch::empty({cap / 128}, opt), meta = torch::empty({2}, opt);      // entries beyond meta[0] are never read
     GM_CHECK(launch_route(top_idx.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(top_idx.data_ptr<int64_t>()) : nullptr, slots,
                           experts, hist[0].data_ptr<int>(), hist[1].data_ptr<int>(), counts.data_ptr<int>(), seg.data_ptr<int>(),
                           tiles.data_ptr<int>(), meta.data_ptr<int>(), dest.data_ptr<int>(), src.data_ptr<int>(), stream()),
@@ -193,7 +233,7 @@ std::vector<Tensor> combine_bwd(const Tensor& dout, const Tensor& y, const Tenso
     check_bf16(y, "y");
     const int top_k = gates.size(1), d = y.size(-1), cap = src_of_row.numel();
     Tensor dy = torch::empty_like(y);
-    Tensor dgates = torch::zeros_like(gates);
+    Tensor dgates = torch::empty_like(gates);                     // every (token, slot) has exactly one live row that writes it
     QuantOut qo = alloc_quant(quantize, cap, d, y);
     launch_combine_bwd(dout.data_ptr(), y.data_ptr(), src_of_row.data_ptr<int>(), gates.data_ptr<float>(), meta.data_ptr<int>(),
                        dy.data_ptr(), dgates.data_ptr<float>(), qo.qp, qo.sp, d, top_k, cap, stream());
@@ -481,6 +521,8 @@ void register_kernels(pybind11::module_& m) {
     m.def("rope_qknorm_bwd", &rope_qknorm_bwd, py::arg("x"), py::arg("dy"), py::arg("dx"), py::arg("cos"), py::arg("sin"), py::arg("q_scale"),
           py::arg("k_scale"), py::arg("seq_len"), py::arg("q_heads"), py::arg("k_heads"), py::arg("head_dim"), py::arg("eps"), py::arg("rms"),
           py::arg("smin"), py::arg("smax"), py::arg("dq32") = py::none(), py::arg("quantize") = false);
+    m.def("router_fwd", &router_fwd);
+    m.def("router_bwd", &router_bwd);
     m.def("route", &route);
     m.def("gather_rows", &gather_rows, py::arg("hidden"), py::arg("src_of_row"), py::arg("meta"), py::arg("top_k"), py::arg("quantize") = false);
     m.def("combine_fwd", &combine_fwd);

@@ -36,6 +36,13 @@ void launch_activation_fwd(const void* pre, void* act, const int* meta, void* q,
 void launch_activation_bwd(const void* dact, const void* pre, void* dpre, const int* meta, void* q, void* sf, int rows, int h, int kind,
                            cudaStream_t s);
 
+// fused/router.cu
+int router_blocks(int tokens);
+bool launch_router_fwd(const void* logits, bool bf16, long long* top_idx, float* gates, float* prob_partial, float* count_partial,
+                       float* prob_sums, float* counts, float* balance, int tokens, int experts, int top_k, int renormalise, cudaStream_t s);
+bool launch_router_bwd(const void* logits, bool bf16, const long long* top_idx, const float* dgates, const float* dbalance, const float* counts,
+                       void* dlogits, int tokens, int experts, int top_k, int renormalise, cudaStream_t s);
+
 // fused/loss_optim.cu
 void launch_ce_fwd_bwd(void* logits, const long long* targets, float* loss, const float* grad_scale, int rows, int vocab,
                        long long row_stride, long long ignore_index, int write_grad, cudaStream_t s);

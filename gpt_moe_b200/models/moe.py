@@ -55,10 +55,8 @@ class MoE(nn.Module):
         shape = x.shape
         hidden = x.reshape(-1, shape[-1])
         logits = self.router(hidden)
-        top_idx, gates, probs = ref.router_gates(logits, self.top_k, self.full_softmax_gating)
-        balance = None
-        if self.training and self.load_balance_weight > 0:
-            balance = ref.load_balance_loss(probs, top_idx, self.num_experts)
+        want_balance = bool(self.training and self.load_balance_weight > 0)
+        top_idx, gates, balance = api.router(logits, self.top_k, self.full_softmax_gating, want_balance, self.num_experts)
         experts = self.local_experts()
         first = experts[0]
         args = dict(

@@ -116,6 +116,16 @@ def attention(q, k, v, *, causal=True, window=None, scale=None, softcap_value=0.
                          tanh_backend=tanh_backend, attn_mask=attn_mask, document_ids=document_ids)
 
 
+def router(logits: Tensor, top_k: int, full_softmax: bool, want_balance: bool, num_experts: int):
+    """Router decisions from logits [tokens, experts]: (top_idx [T, k], gates fp32 [T, k], balance loss or None).
+    fp32 softmax; top-1 / full-softmax gates are the chosen experts' probabilities, otherwise the softmax renormalised over the
+    selection; balance = E * sum_e f_e * mean_prob_e (reference `model/feedforward/moe.py:55-88`)."""
+    if logits.is_cuda:
+        return _cuda().router(logits, top_k, full_softmax, want_balance, num_experts)
+    top_idx, gates, probs = ref.router_gates(logits, top_k, full_softmax)
+    return top_idx, gates, (ref.load_balance_loss(probs, top_idx, num_experts) if want_balance else None)
+
+
 def moe_experts(hidden: Tensor, top_idx: Tensor, gates: Tensor, up_weights: Sequence[Tensor],
                 down_weights: Sequence[Tensor], up_biases, down_biases, activation: str,
                 up_precision: str, down_precision: str) -> Tensor:

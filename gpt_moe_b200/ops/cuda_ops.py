@@ -546,6 +546,42 @@ def activate(x: Tensor, name: str) -> Tensor:
     return _ActivationFn.apply(x, name)
 
 
+# ---- router ---------------------------------------------------------------------------------------------------------------------
+class _RouterFn(torch.autograd.Function):
+    """fp32 softmax over the router logits, top-k, gate weights and the load-balance loss in one kernel (one more backward)."""
+
+    @staticmethod
+    def forward(ctx, logits: Tensor, top_k: int, renormalise: bool, want_balance: bool):
+        lg = logits if logits.is_contiguous() else logits.contiguous()
+        res = ext().router_fwd(lg, top_k, renormalise, want_balance)
+        top_idx, gates = res[0], res[1]
+        balance, counts = (res[2], res[3]) if want_balance else (None, None)
+        ctx.save_for_backward(lg, top_idx, counts if counts is not None else lg.new_empty(0))
+        ctx.cfg = (renormalise, want_balance)
+        ctx.mark_non_differentiable(top_idx)
+        return top_idx, gates, (balance.reshape(()) if want_balance else None)
+
+    @staticmethod
+    def backward(ctx, _didx, dgates: Optional[Tensor], dbalance: Optional[Tensor]):
+        lg, top_idx, counts = ctx.saved_tensors
+        renormalise, want_balance = ctx.cfg
+        dg = None if dgates is None else dgates.float().contiguous()
+        db = None if (dbalance is None or not want_balance) else dbalance.float().reshape(1).contiguous()
+        if dg is None and db is None:
+            return None, None, None, None
+        return ext().router_bwd(lg, top_idx, dg, db, counts if db is not None else None, renormalise), None, None, None
+
+
+def router(logits: Tensor, top_k: int, full_softmax: bool, want_balance: bool, num_experts: int):
+    """(top_idx int64 [T, k], gates fp32 [T, k], balance loss or None) from router logits [T, E] (bf16 or fp32)."""
+    if num_experts > 128 or top_k > 8 or logits.dtype not in (BF16, torch.float32):
+        count_path("router:torch")
+        top_idx, gates, probs = ref.router_gates(logits, top_k, full_softmax)
+        return top_idx, gates, (ref.load_balance_loss(probs, top_idx, num_experts) if want_balance else None)
+    renormalise = not (top_k == 1 or full_softmax)
+    return _RouterFn.apply(logits, top_k, renormalise, want_balance)
+
+
 # ---- mixture of experts -------------------------------------------------------------------------------------------------------
 class _MoEExpertsFn(torch.autograd.Function):
     """route -> gather -> grouped up GEMM -> activation -> grouped down GEMM -> gated combine, with a hand-written backward."""

@@ -212,6 +212,35 @@ def test_polar_express_gemms(ops):
         assert rel(folded, same_regime) < 5e-2, shape
 
 
+@pytest.mark.parametrize("experts,top_k,full_softmax,dtype", [(8, 1, False, torch.bfloat16), (32, 2, False, torch.bfloat16),
+                                                               (64, 1, False, torch.float32), (16, 4, True, torch.float32),
+                                                               (100, 8, False, torch.float32)])
+def test_router_kernel_matches_torch_router(ops, experts, top_k, full_softmax, dtype):
+    """softmax + top-k + gates + load-balance loss in one kernel, and its backward, against the torch-op router."""
+    torch.manual_seed(21)
+    tokens = 1111
+    # every row is a permutation of distinct values: the top-k choice has no ties in either precision
+    base = torch.linspace(-3.0, 3.0, experts, device="cuda")
+    order = torch.rand(tokens, experts, device="cuda").argsort(dim=1)
+    logits = base[order].to(dtype).requires_grad_()
+    top_idx, gates, balance = ops.router(logits, top_k, full_softmax, True, experts)
+    want = logits.detach().clone().requires_grad_()
+    w_idx, w_gates, w_probs = ref.router_gates(want, top_k, full_softmax)
+    w_balance = ref.load_balance_loss(w_probs, w_idx, experts)
+    assert torch.equal(top_idx, w_idx)
+    assert torch.allclose(gates, w_gates, atol=1e-6, rtol=1e-5)
+    assert torch.allclose(balance, w_balance, atol=1e-6, rtol=1e-5)
+    dg = torch.randn_like(gates)
+    (gates * dg).sum().add(balance * 0.37).backward()
+    (w_gates * dg).sum().add(w_balance * 0.37).backward()
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    assert rel(logits.grad, want.grad) < tol
+    # no balance loss requested: nothing but the gates flows back
+    logits.grad = None
+    i2, g2, b2 = ops.router(logits, top_k, full_softmax, False, experts)
+    assert b2 is None and torch.equal(i2, top_idx)
+
+
 def test_polar_express_on_router_sized_matrices(ops):
     """Matrices far below one tile (a router: experts x hidden) run through the same batched tcgen05 iteration; the fused
     engine relies on it to keep routers off the host path."""
