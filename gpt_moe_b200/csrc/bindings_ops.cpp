@@ -185,6 +185,34 @@ Tensor router_bwd(const Tensor& logits, const Tensor& top_idx, const OptTensor& 
     return dlogits;
 }
 
+// Absorbed-weight MLA decode over the latent cache (see attention/mla_decode.cu).  q_latent [B,T,H,r] fp32, q_rope [B,T,H,dr] fp32,
+// latent [B,S,r] / rope [B,S,dr] / key_gain [B,S,Hkv] bf16 (views of a longer cache are fine: only the batch stride may differ from
+// the packed one).  window < 0: none.  Returns the context in latent space [B,T,H,r] fp32.
+Tensor mla_decode(const Tensor& q_latent, const Tensor& q_rope, const Tensor& latent, const Tensor& rope, const Tensor& key_gain,
+                  int64_t start, double scale, double softcap, int64_t window) {
+    c10::cuda::CUDAGuard guard(q_latent.device());
+    GM_CHECK(q_latent.scalar_type() == torch::kFloat32 && q_rope.scalar_type() == torch::kFloat32 && q_latent.is_contiguous() && q_rope.is_contiguous() &&
+             q_latent.dim() == 4 && q_rope.dim() == 4, "mla_decode: contiguous fp32 queries [B, T, H, r] and [B, T, H, dr]");
+    const int B = q_latent.size(0), T = q_latent.size(1), H = q_latent.size(2), r = q_latent.size(3), dr = q_rope.size(3);
+    const int S = latent.size(1), Hkv = key_gain.size(2);
+    for (const Tensor* c : {&latent, &rope, &key_gain})
+        GM_CHECK(c->is_cuda() && c->scalar_type() == torch::kBFloat16 && c->dim() == 3 && c->size(0) == B && c->size(1) == S && c->stride(2) == 1 &&
+                 c->stride(1) == c->size(2), "mla_decode: bf16 cache tensors [B, S, width] with packed rows");
+    GM_CHECK(latent.size(2) == r && rope.size(2) == dr && mla_decode_supported(H, Hkv, r, dr),
+             "mla_decode: latent rank 256/512/768/1024, 8/16/32 heads (rank/32 * heads/8 <= 64), rope width even and <= 64");
+    const int splits = mla_decode_splits(B, T, S);
+    Tensor part_ctx = torch::empty({B, T, H, splits, r}, q_latent.options());
+    Tensor part_ml = torch::empty({B, T, H, splits, 2}, q_latent.options());
+    Tensor context = torch::empty({B, T, H, r}, q_latent.options());
+    GM_CHECK(launch_mla_decode(q_latent.data_ptr<float>(), q_rope.data_ptr<float>(), latent.data_ptr(), rope.data_ptr(), key_gain.data_ptr(),
+                               latent.stride(0), rope.stride(0), key_gain.stride(0), part_ctx.data_ptr<float>(), part_ml.data_ptr<float>(),
+                               context.data_ptr<float>(), B, T, H, Hkv, r, dr, S, splits, start, window, static_cast<float>(scale),
+                               static_cast<float>(softcap), stream()), "mla_decode: unsupported shape");
+    return context;
+}
+
+bool mla_decode_ok(int64_t H, int64_t Hkv, int64_t r, int64_t dr) { return mla_decode_supported(H, Hkv, r, dr); }
+
 // Counted routing.  Returns (dest[S], src_of_row[cap], seg_ends[E], counts[E], tile_expert[cap/128], meta[2]).
 std::vector<Tensor> route(const Tensor& top_idx, int64_t experts) {
     c10::cuda::CUDAGuard guard(top_idx.device());
@@ -521,6 +549,8 @@ void register_kernels(pybind11::module_& m) {
     m.def("rope_qknorm_bwd", &rope_qknorm_bwd, py::arg("x"), py::arg("dy"), py::arg("dx"), py::arg("cos"), py::arg("sin"), py::arg("q_scale"),
           py::arg("k_scale"), py::arg("seq_len"), py::arg("q_heads"), py::arg("k_heads"), py::arg("head_dim"), py::arg("eps"), py::arg("rms"),
           py::arg("smin"), py::arg("smax"), py::arg("dq32") = py::none(), py::arg("quantize") = false);
+    m.def("mla_decode", &mla_decode);
+    m.def("mla_decode_ok", &mla_decode_ok);
     m.def("router_fwd", &router_fwd);
     m.def("router_bwd", &router_bwd);
     m.def("route", &route);

@@ -36,6 +36,13 @@ void launch_activation_fwd(const void* pre, void* act, const int* meta, void* q,
 void launch_activation_bwd(const void* dact, const void* pre, void* dpre, const int* meta, void* q, void* sf, int rows, int h, int kind,
                            cudaStream_t s);
 
+// attention/mla_decode.cu
+int mla_decode_splits(int B, int T, int S);
+bool mla_decode_supported(int H, int Hkv, int r, int dr);
+bool launch_mla_decode(const float* q_latent, const float* q_rope, const void* latent, const void* rope, const void* key_gain,
+                       long long latent_bs, long long rope_bs, long long gain_bs, float* part_ctx, float* part_ml, float* context, int B, int T,
+                       int H, int Hkv, int r, int dr, int S, int splits, int start, int window, float scale, float softcap, cudaStream_t s);
+
 // fused/router.cu
 int router_blocks(int tokens);
 bool launch_router_fwd(const void* logits, bool bf16, long long* top_idx, float* gates, float* prob_partial, float* count_partial,

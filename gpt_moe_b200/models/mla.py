@@ -221,6 +221,16 @@ def api_mla_decode(q_latent: Tensor, q_rope: Tensor, latent: Tensor, rope: Tenso
     s_len = latent.shape[1]
     hkv = key_gain.shape[-1]
     g = h // hkv
+    if (q_latent.is_cuda and latent.dtype == torch.bfloat16 and rope.dtype == torch.bfloat16 and key_gain.dtype == torch.bfloat16
+            and (softcap_value <= 0.0 or tanh_backend == "exact")):
+        # split-K decode kernel over the latent cache with a log-sum-exp merge (csrc/attention/mla_decode.cu)
+        from ..ops import cuda_ops
+        c = cuda_ops.ext()
+        if c.mla_decode_ok(h, hkv, r, q_rope.shape[-1]):
+            cuda_ops.count_path("mla_decode:kernel")
+            return c.mla_decode(q_latent.float().contiguous(), q_rope.float().contiguous(), latent, rope, key_gain, int(start_pos),
+                                float(scale), float(softcap_value), -1 if window is None else int(window))
+        cuda_ops.count_path("mla_decode:torch")
     lat, rp = latent.float(), rope.float()
     score = torch.einsum("bthr,bsr->bhts", q_latent.float(), lat) + torch.einsum("bthd,bsd->bhts", q_rope.float(), rp)
     gain = key_gain.float().permute(0, 2, 1).repeat_interleave(g, dim=1)[:, :, None, :]

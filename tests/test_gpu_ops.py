@@ -492,3 +492,22 @@ def test_attention_kernels_with_document_masking(ops, dqk, window):
     assert rel(out, want) < 1e-2
     for name, got, exp in (("dq", q.grad, rq.grad), ("dk", k.grad, rk.grad), ("dv", v.grad, rv.grad)):
         assert rel(got, exp) < 2e-2, name
+
+
+@pytest.mark.parametrize("t,hkv,r,dr,window,softcap", [(1, 16, 512, 64, None, 0.0), (3, 4, 512, 64, 100, 0.0), (2, 16, 256, 16, None, 30.0),
+                                                       (1, 8, 768, 16, 37, 0.0)])
+def test_mla_decode_kernel_matches_torch_decode(ops, t, hkv, r, dr, window, softcap):
+    """Split-K latent-cache decode + log-sum-exp merge against the torch formulation of the same absorbed-weight attention."""
+    from gpt_moe_b200.models.mla import api_mla_decode
+    torch.manual_seed(31)
+    b, h, s_len, start = 2, 16, 333, 333 - t
+    q_latent = torch.randn(b, t, h, r, device="cuda") * 0.2
+    q_rope = torch.randn(b, t, h, dr, device="cuda") * 0.2
+    cache = torch.randn(b, 400, r, device="cuda").bfloat16()                 # the views below are shorter than the cache
+    rope = torch.randn(b, 400, dr, device="cuda").bfloat16()
+    gain = (torch.rand(b, 400, hkv, device="cuda") + 0.5).bfloat16()
+    args = (start, 0.11, softcap, "exact", window)
+    got = api_mla_decode(q_latent, q_rope, cache[:, :s_len], rope[:, :s_len], gain[:, :s_len], *args)
+    want = api_mla_decode(q_latent, q_rope, cache[:, :s_len].float(), rope[:, :s_len].float(), gain[:, :s_len].float(), *args)
+    assert ops.path_counts().get("mla_decode:kernel", 0) >= 1
+    assert got.shape == want.shape and rel(got, want) < 2e-3, rel(got, want)
