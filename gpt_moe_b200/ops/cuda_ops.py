@@ -791,12 +791,12 @@ def muon_polar_step(work: List[Tuple[Tensor, Tensor, Tensor]], lr: float, moment
         buckets.setdefault((tuple(w.shape), w.stride(0), g.stride(0), buf.stride(0)), []).append((w, g, buf))
     for (shape, ws, gs, bs), items in buckets.items():
         rows, cols = shape
-        small = min(rows, cols) < 128 or rows % 8 or cols % 8
+        small = min(rows, cols) < 8 or rows % 8 or cols % 8       # rows the kernels cannot address as 16-byte pieces
         for start in range(0, len(items), max_batch):
             batch = items[start: start + max_batch]
             n = len(batch)
             alpha = -lr * max(rows, cols) ** 0.5
-            if small:        # e.g. the router [E, hidden]: too small for 128-row tiles
+            if small:        # e.g. a router with an odd expert count
                 for w, g, buf in batch:
                     buf.mul_(momentum).add_(g)
                 grads = torch.stack([g.add(buf, alpha=momentum) if nesterov else buf for _, g, buf in batch])

@@ -117,11 +117,11 @@ def main():
     worst = ("", 0.0)
     for n in fused_params:
         err = (fused_params[n] - nccl_params[n]).norm().item() / (nccl_params[n].norm().item() + 1e-3)
-        # the tiny router matrices go through a bf16 Polar Express whose result is sensitive to summation order
-        err = err / 4 if "router" in n else err
         if err > worst[1]:
             worst = (n, err)
-    ok = ok and worst[1] < 5e-2 and ep_ok
+    # both engines run the same kernels on the same reduced gradients; what differs is the summation order of the reduction
+    # (and bf16 Polar Express amplifies that for the small router matrices): a few parts in a thousand after four steps
+    ok = ok and worst[1] < 2e-2 and ep_ok
     flag = torch.tensor([1.0 if ok else 0.0], device=trainer.device)
     torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
     if trainer.rank == 0:

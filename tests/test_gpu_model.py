@@ -27,43 +27,42 @@ def test_forward_backward_matches_cpu_oracle():
     torch.manual_seed(0)
     gc, tc = _tiny()
     cpu = GPT(gc, tc)
-    with torch.no_grad():
-        for block in cpu.transformer.h:       # decisive routing: bf16 rounding of the logits must not flip the top-1 choice
-            block.mlp.router.weight.mul_(40.0)
     gpu = copy.deepcopy(cpu).cuda()
     cpu.set_sliding_window(128); gpu.set_sliding_window(128)
     ids = torch.randint(0, gc.vocab_size, (2, 257))
     x, y = ids[:, :-1], ids[:, 1:]
     # The GPU routes on bf16 logits, the oracle on fp32 logits: a handful of near-tie tokens would pick different
-    # experts and dominate the comparison.  Record the GPU's choices and make the oracle use the same ones.
+    # experts and dominate the comparison.  Record the GPU router's choices and make the oracle take the same ones; gates and
+    # the balance loss are still computed by each side from its own logits.
+    import gpt_moe_b200.models.moe as moe_module
     import gpt_moe_b200.ops.reference as ref
-    original, choices = ref.router_gates, []
+    original, choices = moe_module.api.router, []
 
-    def record(logits, top_k, full):
-        out = original(logits, top_k, full)
+    def record(logits, top_k, full, want_balance, experts):
+        out = original(logits, top_k, full, want_balance, experts)
         choices.append(out[0].cpu())
         return out
 
-    def replay(logits, top_k, full):
+    def replay(logits, top_k, full, want_balance, experts):
         idx = choices.pop(0)
         probs = torch.softmax(logits.float(), dim=-1)
         if top_k == 1 or full:
             gates = probs.gather(-1, idx)
         else:
             gates = torch.softmax(logits.float().gather(-1, idx), dim=-1)
-        return idx, gates, probs
+        return idx, gates, (ref.load_balance_loss(probs, idx, experts) if want_balance else None)
 
     try:
-        ref.router_gates = record
+        moe_module.api.router = record
         cuda_ops.set_loss_scale(1.0)
         loss_g, tok_g, bal_g = gpu(x.cuda(), y.cuda())
         loss_g.backward()
         cuda_ops.check_status()
-        ref.router_gates = replay
+        moe_module.api.router = replay
         loss_c, tok_c, bal_c = cpu(x, y)
         loss_c.backward()
     finally:
-        ref.router_gates = original
+        moe_module.api.router = original
     assert abs(loss_c.item() - loss_g.item()) < 2e-2
     assert abs(bal_c.item() - bal_g.item()) < 1e-3
     errors = {}
@@ -75,9 +74,10 @@ def test_forward_backward_matches_cpu_oracle():
         if denom < 2e-3:          # scalars whose gradient is at the bf16 noise floor of this tiny model
             continue
         errors[n] = (pg.grad.float().cpu() - pc.grad).norm().item() / denom
-    # the router weight's gradient flows only through the gates and the balance term and is the noisiest entry
-    bad = {n: e for n, e in errors.items() if e > (2.5e-1 if "router" in n else 1.5e-1)}
-    assert not bad, sorted(errors.items(), key=lambda kv: -kv[1])
+    # bf16 activations against an fp32 oracle: a few percent; the router weight's gradient flows only through the gates and
+    # the balance term (differences of nearly equal numbers) and is the noisiest entry
+    bad = {n: e for n, e in errors.items() if e > (1.2e-1 if "router" in n else 5e-2)}
+    assert not bad, sorted(errors.items(), key=lambda kv: -kv[1])[:8]
 
 
 def test_smoke_entry():
