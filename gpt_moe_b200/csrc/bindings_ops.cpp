@@ -240,18 +240,22 @@ std::vector<Tensor> gather_rows(const Tensor& hidden, const Tensor& src_of_row, 
     const int cap = src_of_row.numel();
     Tensor packed = torch::empty({cap, d}, hidden.options());
     QuantOut qo = alloc_quant(quantize, cap, d, hidden);
-    launch_gather_rows(hidden.data_ptr(), src_of_row.data_ptr<int>(), meta.data_ptr<int>(), packed.data_ptr(), qo.qp, qo.sp, d, top_k, cap, stream());
+    launch_gather_rows(hidden.data_ptr(), src_of_row.data_ptr<int>(), meta.data_ptr<int>(), packed.data_ptr(), qo.qp, qo.sp, d, top_k, cap,
+                       hidden.numel() / d, stream());
     if (quantize) return {packed, qo.q, qo.sf};
     return {packed};
 }
 
-Tensor combine_fwd(const Tensor& y, const Tensor& dest, const Tensor& gates) {
+// gates: fp32 [tokens, k], or none for unit gates (then `top_k` says how many rows each token sums)
+Tensor combine_fwd(const Tensor& y, const Tensor& dest, const OptTensor& gates, int64_t top_k_if_no_gates) {
     c10::cuda::CUDAGuard guard(y.device());
     check_bf16(y, "y");
-    GM_CHECK(gates.scalar_type() == torch::kFloat32 && gates.is_contiguous(), "gates must be contiguous fp32");
-    const int tokens = gates.size(0), top_k = gates.size(1), d = y.size(-1);
+    if (gates.has_value()) GM_CHECK(gates->scalar_type() == torch::kFloat32 && gates->is_contiguous(), "gates must be contiguous fp32");
+    const int top_k = gates.has_value() ? gates->size(1) : static_cast<int>(top_k_if_no_gates);
+    GM_CHECK(top_k >= 1 && dest.numel() % top_k == 0, "combine_fwd: slots must be a multiple of top_k");
+    const int tokens = dest.numel() / top_k, d = y.size(-1);
     Tensor out = torch::empty({tokens, d}, y.options());
-    launch_combine_fwd(y.data_ptr(), dest.data_ptr<int>(), gates.data_ptr<float>(), out.data_ptr(), tokens, d, top_k, stream());
+    launch_combine_fwd(y.data_ptr(), dest.data_ptr<int>(), fptr(gates), out.data_ptr(), tokens, d, top_k, y.numel() / d, stream());
     return out;
 }
 
@@ -264,7 +268,7 @@ std::vector<Tensor> combine_bwd(const Tensor& dout, const Tensor& y, const Tenso
     Tensor dgates = torch::empty_like(gates);                     // every (token, slot) has exactly one live row that writes it
     QuantOut qo = alloc_quant(quantize, cap, d, y);
     launch_combine_bwd(dout.data_ptr(), y.data_ptr(), src_of_row.data_ptr<int>(), gates.data_ptr<float>(), meta.data_ptr<int>(),
-                       dy.data_ptr(), dgates.data_ptr<float>(), qo.qp, qo.sp, d, top_k, cap, stream());
+                       dy.data_ptr(), dgates.data_ptr<float>(), qo.qp, qo.sp, d, top_k, cap, dout.numel() / d, stream());
     if (quantize) return {dy, dgates, qo.q, qo.sf};
     return {dy, dgates};
 }
@@ -537,6 +541,20 @@ std::vector<Tensor> ep_combine(const Tensor& ret, const Tensor& top_idx, const T
     return {out};
 }
 
+// bounds-checked build: the first out-of-range index any kernel met since the last call (0 = none); always 0 in the normal build
+int64_t read_bounds_status() {
+    for (int v : {read_bounds_moe(), read_bounds_loss(), read_bounds_router()})
+        if (v != 0) return v;
+    return 0;
+}
+bool bounds_checked() {
+#ifdef GM_CHECK_BOUNDS
+    return true;
+#else
+    return false;
+#endif
+}
+
 void register_kernels(pybind11::module_& m) {
     namespace py = pybind11;
     m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("eps"), py::arg("branch") = py::none(),
@@ -555,7 +573,9 @@ void register_kernels(pybind11::module_& m) {
     m.def("router_bwd", &router_bwd);
     m.def("route", &route);
     m.def("gather_rows", &gather_rows, py::arg("hidden"), py::arg("src_of_row"), py::arg("meta"), py::arg("top_k"), py::arg("quantize") = false);
-    m.def("combine_fwd", &combine_fwd);
+    m.def("combine_fwd", &combine_fwd, py::arg("y"), py::arg("dest"), py::arg("gates"), py::arg("top_k_if_no_gates") = 1);
+    m.def("read_bounds_status", &read_bounds_status);
+    m.def("bounds_checked", &bounds_checked);
     m.def("combine_bwd", &combine_bwd, py::arg("dout"), py::arg("y"), py::arg("src_of_row"), py::arg("gates"), py::arg("meta"), py::arg("quantize") = false);
     m.def("activation_fwd", &activation_fwd, py::arg("pre"), py::arg("name"), py::arg("meta") = py::none(), py::arg("quantize") = false);
     m.def("activation_bwd", &activation_bwd, py::arg("dact"), py::arg("pre"), py::arg("name"), py::arg("meta") = py::none(), py::arg("quantize") = false);

@@ -90,7 +90,7 @@ def build(verbose: bool = False) -> str:
     abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
     ext_name = "_C_checked" if CHECKED else "_C"
     cxx_flags = ["-O2", "-std=c++17", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={abi}", f"-DTORCH_EXTENSION_NAME={ext_name}",
-                 "-DTORCH_API_INCLUDE_EXTENSION_H", "-Wno-deprecated-declarations"]
+                 "-DTORCH_API_INCLUDE_EXTENSION_H", "-Wno-deprecated-declarations"] + (["-DGM_CHECK_BOUNDS=1"] if CHECKED else [])
     jobs, objects = [], []
     for src in cu:
         obj = os.path.join(BUILD, os.path.relpath(src, CSRC).replace(os.sep, "_") + ".o")

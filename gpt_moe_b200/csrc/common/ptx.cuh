@@ -13,6 +13,30 @@ namespace gm {
 
 constexpr long long kWaitBudgetCycles = 2000000000LL;   // ~1 s at B200 clocks
 
+// ---- bounds-checked build ------------------------------------------------------------------------
+// With -DGM_CHECK_BOUNDS=1 (the `_C_checked` build, GM_CHECK_BOUNDS=1 in the environment) every data-dependent index that a
+// kernel takes from a tensor (an expert id, a routed row, a target class) is tested before it is used:
+//     if (!GM_IN_BOUNDS(0 <= e && e < experts, 901)) continue;
+// A failing test records its code in the translation unit's word (first failure wins) and evaluates to false, so the caller
+// SKIPS the access: nothing traps, the context stays usable, and the host reads the code through `read_bounds_status`.  In the
+// normal build the macro is the constant `true` and costs nothing.  Codes: 901 expert id in routing, 902 gathered token,
+// 903 combined row, 904 combine-backward token, 905 cross-entropy target, 906 router-backward expert id.
+#ifdef GM_CHECK_BOUNDS
+static __device__ int gm_bounds_word = 0;
+#define GM_IN_BOUNDS(cond, code) ((cond) ? true : (atomicCAS(&gm_bounds_word, 0, (code)), false))
+#define GM_DEFINE_BOUNDS_READER(name)                                           \
+    int read_bounds_##name() {                                                  \
+        int v = 0, zero = 0;                                                    \
+        cudaMemcpyFromSymbol(&v, gm_bounds_word, sizeof(int));                  \
+        if (v != 0) cudaMemcpyToSymbol(gm_bounds_word, &zero, sizeof(int));     \
+        return v;                                                               \
+    }
+#else
+#define GM_IN_BOUNDS(cond, code) (true)
+#define GM_DEFINE_BOUNDS_READER(name) \
+    int read_bounds_##name() { return 0; }
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -26,7 +26,8 @@ ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restric
     __shared__ float red_m[16], red_s[16];
     const long long row = blockIdx.x;
     __nv_bfloat16* p = logits + row * row_stride;
-    const long long tgt = targets[row];
+    long long tgt = targets[row];
+    if (!GM_IN_BOUNDS(tgt == ignore_index || (tgt >= 0 && tgt < vocab), 905)) tgt = ignore_index;      // checked build: the row is ignored
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int vec = vocab / 8;
     if (tgt == ignore_index) {
@@ -98,7 +99,8 @@ ce_fwd_bwd_reg_kernel(__nv_bfloat16* __restrict__ logits, const long long* __res
     __shared__ float bcast;
     const long long row = blockIdx.x;
     uint4* p = reinterpret_cast<uint4*>(logits + row * row_stride);
-    const long long tgt = targets[row];
+    long long tgt = targets[row];
+    if (!GM_IN_BOUNDS(tgt == ignore_index || (tgt >= 0 && tgt < vocab), 905)) tgt = ignore_index;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int vec = vocab / 8;
     if (tgt == ignore_index) {
@@ -367,5 +369,7 @@ void launch_cast_bf16(const float* src, void* dst, long long n, cudaStream_t s) 
     const int blocks = static_cast<int>(std::min<long long>((n / 4 + 255) / 256 + 1, 2368LL));
     cast_bf16_kernel<<<blocks, 256, 0, s>>>(src, static_cast<__nv_bfloat16*>(dst), n);
 }
+
+GM_DEFINE_BOUNDS_READER(loss)
 
 }  // namespace gm

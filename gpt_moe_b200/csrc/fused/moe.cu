@@ -27,7 +27,10 @@ route_count_kernel(const long long* __restrict__ idx, int* __restrict__ chunk_hi
     for (int e = threadIdx.x; e < experts; e += blockDim.x) hist[e] = 0;
     __syncthreads();
     const int slot = blockIdx.x * ROUTE_CHUNK + threadIdx.x;
-    if (slot < slots) atomicAdd(&hist[static_cast<int>(idx[slot])], 1);
+    if (slot < slots) {
+        const int e = static_cast<int>(idx[slot]);
+        if (GM_IN_BOUNDS(e >= 0 && e < experts, 901)) atomicAdd(&hist[e], 1);
+    }
     __syncthreads();
     for (int e = threadIdx.x; e < experts; e += blockDim.x) chunk_hist[blockIdx.x * experts + e] = hist[e];
 }
@@ -77,7 +80,8 @@ route_place_kernel(const long long* __restrict__ idx, const int* __restrict__ ch
     for (int i = threadIdx.x; i < 32 * MAX_EXPERTS; i += blockDim.x) (&warp_count[0][0])[i] = 0;
     __syncthreads();
     const int slot = blockIdx.x * ROUTE_CHUNK + threadIdx.x;
-    const int e = slot < slots ? static_cast<int>(idx[slot]) : experts;     // `experts` = sentinel for idle lanes
+    int e = slot < slots ? static_cast<int>(idx[slot]) : experts;           // `experts` = sentinel for idle lanes
+    if (!GM_IN_BOUNDS(e >= 0 && e <= experts, 901)) e = experts;           // checked build: an id out of range places nothing
     const unsigned same = __match_any_sync(0xffffffffu, e);
     const int rank = __popc(same & ((1u << lane) - 1u));
     if (e < experts && rank == 0) warp_count[warp][e] = __popc(same);
@@ -130,12 +134,14 @@ __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
 // packed[row] = hidden[src_of_row[row] / k] (zeros for pad rows); one warp per row, 16-byte vectors
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const __nv_bfloat16* __restrict__ hidden, const int* __restrict__ src_of_row, const int* __restrict__ meta,
-                   __nv_bfloat16* __restrict__ packed, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int d, int top_k, int cap_rows) {
+                   __nv_bfloat16* __restrict__ packed, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int d, int top_k, int cap_rows,
+                   int tokens) {
     const int lane = threadIdx.x & 31;
     const int total = min(meta[1], cap_rows);
     const int vecs = d / 8, k_blocks = (d + 127) >> 7;
     for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total; row += gridDim.x * 8) {
-        const int src = src_of_row[row];
+        int src = src_of_row[row];
+        if (!GM_IN_BOUNDS(src < 0 || src / top_k < tokens, 902)) src = -1;                    // checked build: treated as a pad row
         uint4* out = reinterpret_cast<uint4*>(packed + static_cast<long long>(row) * d);
         const uint4* in = reinterpret_cast<const uint4*>(hidden + static_cast<long long>(src < 0 ? 0 : src / top_k) * d);
         for (int base = 0; base < vecs; base += 32) {                  // warp-uniform trip count: the quantiser shuffles
@@ -158,23 +164,25 @@ gather_rows_kernel(const __nv_bfloat16* __restrict__ hidden, const int* __restri
 }
 
 void launch_gather_rows(const void* hidden, const int* src_of_row, const int* meta, void* packed, void* q, void* sf, int d, int top_k,
-                        int cap_rows, cudaStream_t s) {
+                        int cap_rows, int tokens, cudaStream_t s) {
     gather_rows_kernel<<<1184, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(hidden), src_of_row, meta,
                                             static_cast<__nv_bfloat16*>(packed), static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), d, top_k,
-                                            cap_rows);
+                                            cap_rows, tokens);
 }
 
 // out[t] = sum_k gates[t,k] * y[dest[t*k+k']]   (fp32 accumulation, bf16 result); one warp per token
 __global__ void __launch_bounds__(256)
 combine_fwd_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ dest, const float* __restrict__ gates,
-                   __nv_bfloat16* __restrict__ out, int tokens, int d, int top_k) {
+                   __nv_bfloat16* __restrict__ out, int tokens, int d, int top_k, int y_rows) {
     const int lane = threadIdx.x & 31;
     for (int t = blockIdx.x * 8 + (threadIdx.x >> 5); t < tokens; t += gridDim.x * 8) {
         for (int i = lane; i < d / 8; i += 32) {
             float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             for (int k = 0; k < top_k; ++k) {
-                const float g = gates[t * top_k + k];
-                const uint4 raw = *reinterpret_cast<const uint4*>(y + static_cast<long long>(dest[t * top_k + k]) * d + i * 8);
+                const float g = gates ? gates[t * top_k + k] : 1.f;
+                const int row = dest[t * top_k + k];
+                if (!GM_IN_BOUNDS(row >= 0 && row < y_rows, 903)) continue;
+                const uint4 raw = *reinterpret_cast<const uint4*>(y + static_cast<long long>(row) * d + i * 8);
                 const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -195,12 +203,14 @@ combine_fwd_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ 
 __global__ void __launch_bounds__(256)
 combine_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ y, const int* __restrict__ src_of_row,
                    const float* __restrict__ gates, const int* __restrict__ meta, __nv_bfloat16* __restrict__ dy,
-                   float* __restrict__ dgates, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int d, int top_k, int cap_rows) {
+                   float* __restrict__ dgates, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int d, int top_k, int cap_rows,
+                   int tokens) {
     const int lane = threadIdx.x & 31;
     const int total = min(meta[1], cap_rows);
     const int vecs = d / 8, k_blocks = (d + 127) >> 7;
     for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total; row += gridDim.x * 8) {
-        const int src = src_of_row[row];
+        int src = src_of_row[row];
+        if (!GM_IN_BOUNDS(src < 0 || src / top_k < tokens, 904)) src = -1;
         const bool live = src >= 0;
         uint4* o = reinterpret_cast<uint4*>(dy + static_cast<long long>(row) * d);
         const float g = live ? gates[src] : 0.f;
@@ -241,14 +251,14 @@ combine_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* 
     }
 }
 
-void launch_combine_fwd(const void* y, const int* dest, const float* gates, void* out, int tokens, int d, int top_k, cudaStream_t s) {
-    combine_fwd_kernel<<<1184, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(y), dest, gates, static_cast<__nv_bfloat16*>(out), tokens, d, top_k);
+void launch_combine_fwd(const void* y, const int* dest, const float* gates, void* out, int tokens, int d, int top_k, int y_rows, cudaStream_t s) {
+    combine_fwd_kernel<<<1184, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(y), dest, gates, static_cast<__nv_bfloat16*>(out), tokens, d, top_k, y_rows);
 }
 void launch_combine_bwd(const void* dout, const void* y, const int* src_of_row, const float* gates, const int* meta, void* dy,
-                        float* dgates, void* q, void* sf, int d, int top_k, int cap_rows, cudaStream_t s) {
+                        float* dgates, void* q, void* sf, int d, int top_k, int cap_rows, int tokens, cudaStream_t s) {
     combine_bwd_kernel<<<1184, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(y), src_of_row,
                                             gates, meta, static_cast<__nv_bfloat16*>(dy), dgates, static_cast<uint8_t*>(q),
-                                            static_cast<uint8_t*>(sf), d, top_k, cap_rows);
+                                            static_cast<uint8_t*>(sf), d, top_k, cap_rows, tokens);
 }
 
 // ---- activations ---------------------------------------------------------------------------------------
@@ -383,5 +393,7 @@ void launch_activation_bwd(const void* dact, const void* pre, void* dpre, const 
         activation_bwd_kernel<false><<<2368, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dact), static_cast<const __nv_bfloat16*>(pre),
                                                           static_cast<__nv_bfloat16*>(dpre), meta, qp, sp, rows, h, kind);
 }
+
+GM_DEFINE_BOUNDS_READER(moe)
 
 }  // namespace gm

@@ -181,6 +181,7 @@ router_bwd_kernel(const T* __restrict__ logits, const long long* __restrict__ to
             for (int s2 = 0; s2 < ROUTER_MAX_K; ++s2) {
                 if (s2 < top_k) {
                     idx[s2] = static_cast<int>(top_idx[static_cast<long long>(t) * top_k + s2]);
+                    if (!GM_IN_BOUNDS(idx[s2] >= 0 && idx[s2] < experts, 906)) idx[s2] = 0;
                     dg[s2] = dgates[static_cast<long long>(t) * top_k + s2];
                     zs[s2] = __shfl_sync(0xffffffffu, get4(z, (idx[s2] >> 5) & 3), idx[s2] & 31);
                 }
@@ -249,5 +250,7 @@ bool launch_router_bwd(const void* logits, bool bf16, const long long* top_idx, 
                                                                      static_cast<float*>(dlogits), tokens, experts, top_k, renormalise);
     return true;
 }
+
+GM_DEFINE_BOUNDS_READER(router)
 
 }  // namespace gm

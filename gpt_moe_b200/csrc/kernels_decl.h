@@ -28,10 +28,15 @@ bool launch_route(const long long* idx, int slots, int experts, int* chunk_hist,
                   int* tile_expert, int* meta, int* dest, int* src_of_row, cudaStream_t s);
 // q / sf (optional, every launcher below that has them): MXFP8 copy of the bf16 matrix the kernel writes, emitted in the same pass
 void launch_gather_rows(const void* hidden, const int* src_of_row, const int* meta, void* packed, void* q, void* sf, int d, int top_k,
-                        int cap_rows, cudaStream_t s);
-void launch_combine_fwd(const void* y, const int* dest, const float* gates, void* out, int tokens, int d, int top_k, cudaStream_t s);
+                        int cap_rows, int tokens, cudaStream_t s);
+// gates == nullptr: unit gates
+void launch_combine_fwd(const void* y, const int* dest, const float* gates, void* out, int tokens, int d, int top_k, int y_rows, cudaStream_t s);
 void launch_combine_bwd(const void* dout, const void* y, const int* src_of_row, const float* gates, const int* meta, void* dy,
-                        float* dgates, void* q, void* sf, int d, int top_k, int cap_rows, cudaStream_t s);
+                        float* dgates, void* q, void* sf, int d, int top_k, int cap_rows, int tokens, cudaStream_t s);
+// bounds-checked build: first recorded code of each translation unit (0 = none; reading clears it); always 0 in the normal build
+int read_bounds_moe();
+int read_bounds_loss();
+int read_bounds_router();
 void launch_activation_fwd(const void* pre, void* act, const int* meta, void* q, void* sf, int rows, int h, int kind, cudaStream_t s);
 void launch_activation_bwd(const void* dact, const void* pre, void* dpre, const int* meta, void* q, void* sf, int rows, int h, int kind,
                            cudaStream_t s);

@@ -38,7 +38,8 @@ class _CountingExtension:
         if fn is None:
             target = getattr(self._module, name)
 
-            launches = name not in ("read_status", "reset_status", "status_word_tensor")     # bookkeeping calls launch nothing
+            launches = name not in ("read_status", "reset_status", "status_word_tensor", "read_bounds_status", "bounds_checked",
+                                    "mla_decode_ok")     # bookkeeping calls launch nothing
 
             def fn(*args, _target=target, _launches=launches, **kwargs):
                 self.calls += _launches
@@ -86,6 +87,10 @@ def check_status() -> None:
     if code != 0:
         ext().reset_status()
         raise RuntimeError(f"a device-side bounded wait gave up (status {code}); the step is invalid")
+    if ext().bounds_checked():                 # GM_CHECK_BOUNDS=1 build: a kernel met an out-of-range index and skipped the access
+        code = ext().read_bounds_status()
+        if code != 0:
+            raise RuntimeError(f"bounds-checked build: a kernel skipped an out-of-range index (code {code})")
 
 
 _status_host: dict = {}
@@ -640,7 +645,7 @@ class _MoEExpertsFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dpacked = torch.empty_like(packed)
             c.gemm_bf16(dpre, w_up, dpacked, False, True, 1.0, 0.0, None, False, 1, tile_expert, meta, None)
-            dhidden = c.combine_fwd(dpacked, dest, torch.ones_like(gates32)).view(shape).to(dtype)
+            dhidden = c.combine_fwd(dpacked, dest, None, gates32.shape[1]).view(shape).to(dtype)
         return (dhidden, dgates.to(gdtype), None, None, None) + tuple(grads)
 
 

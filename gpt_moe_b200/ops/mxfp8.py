@@ -301,7 +301,7 @@ class _MXFP8MoEExpertsFn(torch.autograd.Function):
         if need_dx:
             dpacked = torch.empty_like(packed)
             c.gemm_mxfp8(res[1], res[2], uqt, usft, dpacked, 1.0, tile_expert, meta)
-            dhidden = c.combine_fwd(dpacked, dest, torch.ones_like(gates32)).view(shape).to(dtype)
+            dhidden = c.combine_fwd(dpacked, dest, None, gates32.shape[1]).view(shape).to(dtype)
         return (dhidden, dgates.to(gdtype), None, None, None) + tuple(grads)
 
 

@@ -511,3 +511,28 @@ def test_mla_decode_kernel_matches_torch_decode(ops, t, hkv, r, dr, window, soft
     want = api_mla_decode(q_latent, q_rope, cache[:, :s_len].float(), rope[:, :s_len].float(), gain[:, :s_len].float(), *args)
     assert ops.path_counts().get("mla_decode:kernel", 0) >= 1
     assert got.shape == want.shape and rel(got, want) < 2e-3, rel(got, want)
+
+
+def test_bounds_checked_build_skips_bad_indices(ops):
+    """Only in the bounds-checked build (GM_CHECK_BOUNDS=1 selects `_C_checked.so`): an expert id, a routed row or a target class
+    outside its range is not used as an address; the kernel skips the access, records a code, and the context stays usable."""
+    c = ops.ext()
+    if not c.bounds_checked():
+        pytest.skip("normal build: indices are not checked (run with GM_CHECK_BOUNDS=1)")
+    assert c.read_bounds_status() == 0
+    idx = torch.randint(0, 4, (512, 1), device="cuda")
+    idx[7, 0] = 9                                            # four experts: 9 does not exist
+    c.route(idx, 4)
+    torch.cuda.synchronize()
+    assert c.read_bounds_status() == 901
+    assert c.read_bounds_status() == 0                       # reading clears the word
+    logits = torch.randn(64, 512, device="cuda").bfloat16()
+    targets = torch.randint(0, 512, (64,), device="cuda")
+    targets[3] = 512                                         # one past the last class: treated as an ignored row
+    loss = c.ce_fwd_bwd(logits, targets, torch.ones(1, device="cuda"), -100, True)
+    torch.cuda.synchronize()
+    assert c.read_bounds_status() == 905 and torch.isfinite(loss).all() and loss[3].item() == 0.0
+    a = torch.randn(128, 64, device="cuda").bfloat16()
+    d = torch.empty(128, 128, device="cuda", dtype=torch.bfloat16)
+    c.gemm_bf16(a, a, d)                                     # kernels still run afterwards
+    assert rel(d, a.float() @ a.float().t()) < BF16_TOL
