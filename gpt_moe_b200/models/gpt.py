@@ -32,8 +32,15 @@ from .block import Block, apply_norm, make_norm
 from .linear import Linear
 
 
-def validate_linear_config(linear_config, use_moe: bool) -> None:
-    """Reject unsupported precision/backend combinations with the role named (reference `model/gpt.py:68-86`)."""
+def validate_linear_config(linear_config, use_moe: bool) -> List[str]:
+    """Reject unsupported precision/backend combinations with the role named (reference `model/gpt.py:68-86`).
+
+    Backends: "custom" is this framework's MXFP8 path.  "te" names the reference's Transformer Engine block-scaled linear
+    (`model/linear/fp8/transformer_engine.py:10-34`: e4m3 with 1x128 activation and 128x128 weight blocks); Transformer Engine
+    is not part of this framework, so an fp8 role with backend "te" runs on the same MXFP8 kernels (32-element E8M0 blocks:
+    finer scaling than TE's recipe, same operand format) — the returned list names those `phase.role` entries so the caller
+    can say so in the log instead of switching silently."""
+    remapped: List[str] = []
     for phase in PHASES:
         for role in ROLES:
             policy = linear_config[phase][role]
@@ -44,6 +51,9 @@ def validate_linear_config(linear_config, use_moe: bool) -> None:
                 raise ValueError(f"unsupported linear backend for {phase}.{role}: {backend}")
             if precision != "default" and role == "router":
                 raise ValueError(f"{phase}.{role}: the router stays in fp32/bf16; use precision='default'")
+            if precision != "default" and backend == "te":
+                remapped.append(f"{phase}.{role}")
+    return remapped
 
 
 class GPT(nn.Module):
@@ -71,7 +81,7 @@ class GPT(nn.Module):
         self.keep_fp32_loss = training_config.keep_fp32_loss
         self.use_liger_loss = training_config.use_liger_loss
         self.linear_config = training_config.linear_config
-        validate_linear_config(self.linear_config, gpt_config.use_moe)
+        self.te_roles_on_mxfp8 = validate_linear_config(self.linear_config, gpt_config.use_moe)
         self.moe_load_balance_weight = training_config.moe_load_balance_weight
         self.num_moe_layers = gpt_config.n_layers if gpt_config.use_moe else 0
 

@@ -115,6 +115,9 @@ class Trainer:
             du.barrier()
         else:
             self.raw_gpt_model = factory()
+        if getattr(self.raw_gpt_model, "te_roles_on_mxfp8", None):
+            self._log("linear backend 'te' (Transformer Engine block scaling) is served by the MXFP8 kernels (e4m3, 32-element E8M0 "
+                      "blocks) for: " + ", ".join(self.raw_gpt_model.te_roles_on_mxfp8))
         self.raw_gpt_model.to(self.device)
         if cfg.use_all_bf16_and_null_ctx or cfg.use_bf16_weights_params_or_scales:
             convert_to_bf16(self.raw_gpt_model, cfg.bf16_weights_params_and_scales, cfg.keep_1d_weights_params_and_scales_in_fp32)
