@@ -357,12 +357,13 @@ class FusedEngine:
 
     def _graph_eligible(self, model, x, document_ids) -> bool:
         """Graph replay needs a step whose launches do not depend on host-side state: one micro-step per step (the
-        first-write / accumulate choice of the weight-gradient GEMMs is then fixed), no expert-parallel exchange (its
-        workspaces are looked up on the host), no document ids, the plain chain of blocks (no activation checkpointing
-        or offloading).  The overlapped gradient reduction is part of the graph: its flags take their value from a device
-        word, and the second stream forks from and joins the capturing stream."""
+        first-write / accumulate choice of the weight-gradient GEMMs is then fixed), no document ids, the plain chain of
+        blocks (no activation checkpointing or offloading).  Cross-rank pieces are part of the graph: the overlapped gradient
+        reduction (its flags take their value from a device word, the second stream forks from and joins the capturing
+        stream) and the expert-parallel exchange (symmetric workspaces allocated during the eager warm-up steps, barriers
+        whose epoch lives on the device, all sizes on the device)."""
         raw = self.model
-        return (self.use_graphs and x.is_cuda and document_ids is None and self.cfg.grad_accum_mini_steps == 1 and self.ep_size == 1
+        return (self.use_graphs and x.is_cuda and document_ids is None and self.cfg.grad_accum_mini_steps == 1
                 and raw.training and torch.is_grad_enabled()
                 and not getattr(raw, "use_activation_checkpointing", False) and getattr(raw, "activation_offloader", None) is None)
 
@@ -524,6 +525,16 @@ class FusedEngine:
         from ..ops import reference as ref
         c = cuda_ops.ext()
         muon, adamw = self.optimizers.get("muon"), self.optimizers["adamw"]
+        # a matrix whose GEMM ran outside the kernels (a shape they do not cover, e.g. a router with fewer than 8 experts goes
+        # through torch) has its gradient in `.grad`: move it into the flat buffer, where the reduction looks for it
+        for _, p in self.big + self.small:
+            if p.grad is not None:
+                if p.grad_ready:
+                    p.main_grad.add_(p.grad)
+                else:
+                    p.main_grad.copy_(p.grad)
+                    p.grad_ready = True
+                p.grad = None
         if self.wire_bf16 and muon is not None:
             # peers read a bf16 shadow of the gradients; blocks handled beside the backward pass were cast there
             todo = [self.layer_span[l] for l in self.layer_span if l not in self._early_layers]

@@ -36,6 +36,7 @@ def run(fused: bool, steps: int = 4, ep: int = 1):
     if hasattr(trainer.engine, "sync_masters"):
         trainer.engine.sync_masters()
     params = {n: p.detach().float().cpu().clone() for n, p in trainer.raw_gpt_model.named_parameters()}
+    trainer.momentum = {k: v["momentum_buffer"].float() for k, v in trainer.engine.full_optimizer_state_dicts()["muon"]["state"].items()}
     return trainer, losses, params
 
 
@@ -107,6 +108,18 @@ def check_expert_parallel_ops():
 
 
 def main():
+    # One step from identical weights: the momentum buffers then hold the reduced gradients themselves.  Both engines ran the
+    # same kernels on the same data, so they may differ only by the summation order of the cross-rank reduction.
+    one_fused, _, _ = run(True, steps=1)
+    one_nccl, _, _ = run(False, steps=1)
+    from gpt_moe_b200.checkpointing.checkpoint import _optimizer_layout
+    names = [n for group in _optimizer_layout(one_nccl.raw_gpt_model, one_nccl.optimizers["muon"])[1] for n in group]
+    per_key = sorted(((one_fused.momentum[k] - one_nccl.momentum[k]).norm().item() / (one_nccl.momentum[k].norm().item() + 1e-12),
+                      names[k], one_fused.momentum[k].norm().item(), one_nccl.momentum[k].norm().item()) for k in one_nccl.momentum)
+    grad_err = per_key[-1][0]
+    if one_nccl.rank == 0:
+        print("reduced gradients, three worst (relative difference, name, |fused|, |nccl|):", per_key[-3:])
+    grads_ok = set(one_fused.momentum) == set(one_nccl.momentum) and grad_err < 1e-4
     trainer, fused_losses, fused_params = run(True)
     _, nccl_losses, nccl_params = run(False)
     ep_err = check_expert_parallel_ops()
@@ -121,13 +134,22 @@ def main():
             worst = (n, err)
     # both engines run the same kernels on the same reduced gradients; what differs is the summation order of the reduction
     # (and bf16 Polar Express amplifies that for the small router matrices): a few parts in a thousand after four steps
-    ok = ok and worst[1] < 2e-2 and ep_ok
+    worst_router = max([(n, (fused_params[n] - nccl_params[n]).norm().item() / (nccl_params[n].norm().item() + 1e-3))
+                        for n in fused_params if "router" in n], key=lambda kv: kv[1], default=("", 0.0))
+    worst_other = max([(n, (fused_params[n] - nccl_params[n]).norm().item() / (nccl_params[n].norm().item() + 1e-3))
+                       for n in fused_params if "router" not in n], key=lambda kv: kv[1], default=("", 0.0))
+    # After several Muon steps the weights are a poor yardstick: orthogonalisation lifts every singular value of the update to
+    # about one, the noise directions of a small batch included, so summation-order differences of 1e-6 in the reduced gradient
+    # come back as percents of the update (most of all in the 4 x 256 routers).  The tight check is the one on the reduced
+    # gradients above; here only gross divergence is excluded.
+    ok = ok and grads_ok and worst_other[1] < 5e-2 and worst_router[1] < 1.5e-1 and ep_ok
     flag = torch.tensor([1.0 if ok else 0.0], device=trainer.device)
     torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
     if trainer.rank == 0:
         print("fused losses", fused_losses)
         print("nccl  losses", nccl_losses)
-        print("worst parameter difference", worst)
+        print("reduced gradients after one step: worst relative difference", grad_err)
+        print("worst parameter difference (router)", worst_router, "(other)", worst_other)
         print("expert-parallel ops: worst relative error", ep_err)
         print("expert-parallel fused losses", ep_fused_losses)
         print("expert-parallel nccl  losses", ep_nccl_losses)
