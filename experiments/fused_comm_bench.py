@@ -52,10 +52,11 @@ def timed(fn, iters: int, warmup: int = 3) -> float:
 
 def bench_rs_ag(args, results):
     from gpt_moe_b200.ops import cuda_ops
-    from gpt_moe_b200.parallel.fused_engine import SymmetricBuffer
+    from gpt_moe_b200.parallel.fused_engine import PeerBarrier, SymmetricBuffer
     c = cuda_ops.ext()
     world, rank = dist.get_world_size(), dist.get_rank()
     dev = torch.device("cuda", torch.cuda.current_device())
+    barrier = PeerBarrier(dev)                   # the engine's bounded device-side barrier: it is part of what the fused arm costs
     rows, cols = 768, 768
     sizes_mb = [1, 16, 256] if args.quick else [1, 4, 16, 64, 256, 1024]
     for mb in sizes_mb:
@@ -64,6 +65,7 @@ def bench_rs_ag(args, results):
         mine = n_mats // world
         numel = n_mats * per_mat
         grads = SymmetricBuffer(numel, torch.float32, dev)
+        shadow = SymmetricBuffer(numel, torch.bfloat16, dev)          # bf16 wire format: peers read this copy of the gradients
         weights = SymmetricBuffer(numel, torch.bfloat16, dev)
         grads.tensor.normal_(0, 1e-3)
         lo = rank * mine
@@ -84,9 +86,16 @@ def bench_rs_ag(args, results):
         iters = 20 if mb <= 64 else 6
 
         def rs_fused():
-            grads.barrier()
+            barrier.sync()
             sumsq.zero_()
             c.rs_muon_prepare(gp, bp, packed, sumsq, rows, cols, cols, cols, 0.95, True, False, grads.deltas)
+
+        def rs_fused_bf16():
+            c.cast_bf16(grads.tensor[:numel], shadow.tensor[:numel])
+            barrier.sync()
+            sumsq.zero_()
+            c.rs_muon_prepare(gp, bp, packed, sumsq, rows, cols, cols, cols, 0.95, True, False, shadow.deltas,
+                              grad_base=grads.tensor, shadow=shadow.tensor)
 
         def rs_nccl():
             dist.reduce_scatter_tensor(shard, grads.tensor[:numel], op=dist.ReduceOp.AVG)
@@ -95,7 +104,7 @@ def bench_rs_ag(args, results):
 
         def ag_fused():
             c.muon_apply_push(mp, wp, packed, rows, cols, cols, cols, -0.01, False, weights.deltas)
-            weights.barrier()
+            barrier.sync()
 
         def ag_nccl():
             c.muon_apply_push(mp, lp, packed, rows, cols, cols, cols, -0.01, False, [0])
@@ -111,9 +120,14 @@ def bench_rs_ag(args, results):
             roof_ms = max(link / (LINK_GBS * 1e6), hbm / 6552.6e6)
             results.append({"part": name, "bucket_mb": mb, "matrices": n_mats, "world": world, "fused_ms": tf, "nccl_ms": tn,
                             "speedup": tn / tf, "roofline_ms": roof_ms, "fraction_of_roofline": roof_ms / tf})
+            if name == "rs" and world > 1:
+                # bf16 on the wire (cast pass included): half the NVLink bytes, roofline likewise
+                tb = timed(rs_fused_bf16, iters)
+                roof_b = max(link / 2 / (LINK_GBS * 1e6), hbm / 6552.6e6)
+                results[-1].update(fused_bf16_wire_ms=tb, speedup_bf16_wire=tn / tb, fraction_of_roofline_bf16_wire=roof_b / tb)
             if rank == 0:
                 print(json.dumps(results[-1]), flush=True)
-        del grads, weights
+        del grads, weights, shadow
 
 
 class _Shard:
@@ -144,7 +158,7 @@ def bench_ep(args, results):
         gates = torch.full((tokens, top_k), 1.0 / top_k, device=dev).requires_grad_()
         g = torch.randn(tokens, d, device=dev).bfloat16()
         margs = dict(up_weights=ups, down_weights=downs, up_biases=None, down_biases=None, activation="swiglu",
-                     up_precision="default", down_precision="default")
+                     up_precision=args.ep_precision, down_precision=args.ep_precision)
 
         shards = {True: _Shard(world, experts, True), False: _Shard(world, experts, False)}     # the fused path keys its receive buffer on the layer object
 
@@ -162,7 +176,7 @@ def bench_ep(args, results):
         remote = slots * (world - 1) / world                                      # expected share of slots owned by another rank
         link = 4 * remote * d * 2                                                 # dispatch, combine, and both again in the backward
         roof_ms = max(flops / (GEMM_TFLOPS * 1e9), link / (LINK_GBS * 1e6))
-        results.append({"part": "ep", "tokens_per_gpu": tokens, "d_model": d, "experts": experts, "top_k": top_k, "hidden": h, "world": world,
+        results.append({"part": "ep", "precision": args.ep_precision, "tokens_per_gpu": tokens, "d_model": d, "experts": experts, "top_k": top_k, "hidden": h, "world": world,
                         "fused_ms": tf, "nccl_ms": tn, "speedup": tn / tf, "roofline_ms": roof_ms, "fraction_of_roofline": roof_ms / tf})
         if rank == 0:
             print(json.dumps(results[-1]), flush=True)
@@ -173,6 +187,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--part", default="all", choices=["rs", "ag", "ep", "all"])
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--ep-precision", default="default", choices=["default", "mxfp8"], help="precision of the expert projections in the ep part")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
