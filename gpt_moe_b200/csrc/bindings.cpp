@@ -55,8 +55,11 @@ struct MapKeyHash {
         return h;
     }
 };
-const CUtensorMap& cached_map(const void* ptr, int elem_bytes, uint64_t cols, uint64_t rows, uint64_t batch,
-                              uint64_t row_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_cols, uint32_t box_rows, int swizzle) {
+// Returned BY VALUE: the cache is emptied when it grows past its limit (runs whose shapes change every step, e.g. the NCCL
+// expert-parallel path with its variable row counts, keep adding keys), and a reference handed out earlier in the same call
+// would then dangle.
+CUtensorMap cached_map(const void* ptr, int elem_bytes, uint64_t cols, uint64_t rows, uint64_t batch,
+                       uint64_t row_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_cols, uint32_t box_rows, int swizzle) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     MapKey key;
     std::memset(&key, 0, sizeof(key));
@@ -74,7 +77,7 @@ const CUtensorMap& cached_map(const void* ptr, int elem_bytes, uint64_t cols, ui
 }
 
 // operand map for the bf16 GEMM: `t` is [rows, cols] or [batch, rows, cols] with cols contiguous
-const CUtensorMap& operand_map(const torch::Tensor& t, bool mn_major, int tile_rows_k_major) {
+CUtensorMap operand_map(const torch::Tensor& t, bool mn_major, int tile_rows_k_major) {
     GM_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16, "GEMM operands must be CUDA bf16 tensors");
     GM_CHECK(t.dim() == 2 || t.dim() == 3, "GEMM operands must be 2-D or 3-D");
     GM_CHECK(t.stride(-1) == 1, "GEMM operands must have a contiguous last dimension");
@@ -247,7 +250,7 @@ void gemm_mxfp8(const torch::Tensor& a, const torch::Tensor& sfa, const torch::T
 }
 
 // map over a [B, T, H, 64] bf16 view whose tokens are rows of a wider matrix (e.g. the packed QKV projection output)
-const CUtensorMap& head_map(const torch::Tensor& t, int box_rows) {
+CUtensorMap head_map(const torch::Tensor& t, int box_rows) {
     GM_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 4, "attention operands must be [B, T, H, D] bf16 CUDA tensors");
     GM_CHECK(t.stride(3) == 1 && t.stride(2) == t.size(3) && t.stride(0) == t.size(1) * t.stride(1),
              "attention operands must be token-major with contiguous heads");

@@ -221,14 +221,14 @@ std::vector<Tensor> route(const Tensor& top_idx, int64_t experts) {
     const int cap = (slots + 255) / 256 * 256 + experts * 256;      // every expert segment is padded to 256 rows
     const int chunks = (slots + 1023) / 1024;
     auto opt = top_idx.options().dtype(torch::kInt32);
-    Tensor hist = torch::empty({2, chunks, experts}, opt);
+    Tensor hist = torch::empty({2, chunks > 0 ? chunks : 1, experts}, opt);
     Tensor dest = torch::empty({slots}, opt), src = torch::empty({cap}, opt);
     Tensor seg = torch::empty({experts}, opt), counts = torch::empty({experts}, opt);
     Tensor tiles = torch::empty({cap / 128}, opt), meta = torch::empty({2}, opt);      // entries beyond meta[0] are never read
     GM_CHECK(launch_route(top_idx.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(top_idx.data_ptr<int64_t>()) : nullptr, slots,
                           experts, hist[0].data_ptr<int>(), hist[1].data_ptr<int>(), counts.data_ptr<int>(), seg.data_ptr<int>(),
                           tiles.data_ptr<int>(), meta.data_ptr<int>(), dest.data_ptr<int>(), src.data_ptr<int>(), stream()),
-             "routing supports at most 128 experts");
+             "routing supports at most 128 experts");      // zero slots are fine: every segment is then empty
     return {dest, src, seg, counts, tiles, meta};
 }
 

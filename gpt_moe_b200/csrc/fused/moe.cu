@@ -104,11 +104,12 @@ route_place_kernel(const long long* __restrict__ idx, const int* __restrict__ ch
 
 bool launch_route(const long long* idx, int slots, int experts, int* chunk_hist, int* chunk_start, int* counts, int* seg_ends,
                   int* tile_expert, int* meta, int* dest, int* src_of_row, cudaStream_t s) {
-    if (experts > MAX_EXPERTS || slots <= 0) return false;
+    if (experts > MAX_EXPERTS || slots < 0) return false;
+    // slots == 0 (an expert-parallel rank that received no rows this step): the plan alone yields empty segments and zero tiles
     const int chunks = (slots + ROUTE_CHUNK - 1) / ROUTE_CHUNK;
-    route_count_kernel<<<chunks, ROUTE_CHUNK, 0, s>>>(idx, chunk_hist, slots, experts);
+    if (chunks > 0) route_count_kernel<<<chunks, ROUTE_CHUNK, 0, s>>>(idx, chunk_hist, slots, experts);
     route_plan_kernel<<<1, 128, 0, s>>>(chunk_hist, chunk_start, counts, seg_ends, tile_expert, meta, src_of_row, chunks, experts);
-    route_place_kernel<<<chunks, ROUTE_CHUNK, 0, s>>>(idx, chunk_start, dest, src_of_row, slots, experts);
+    if (chunks > 0) route_place_kernel<<<chunks, ROUTE_CHUNK, 0, s>>>(idx, chunk_start, dest, src_of_row, slots, experts);
     return true;
 }
 
