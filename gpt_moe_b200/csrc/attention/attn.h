@@ -30,9 +30,15 @@ struct AttnParams {
     void* dv;
     long long dkv_stride, dv_stride;
     int* status;
+    int single_tile;                // forward: 1 keeps the call on the kernel with one query tile per CTA
 };
 
 cudaError_t launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t stream);
+
+// Forward with two query tiles per CTA (attn_fwd_dual.cu): 64-wide heads, no document masking, sequence length a multiple of 256.
+// launch_attn_fwd picks it when it applies and `single_tile` is 0.
+bool attn_fwd_dual_supported(const AttnParams& p);
+cudaError_t launch_attn_fwd_dual(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t stream);
 
 cudaError_t launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                             const CUtensorMap& tdq, const AttnParams& p, const void* d_out, const void* out, long long do_stride,

@@ -20,6 +20,7 @@
 #include "../common/ptx.cuh"
 #include "../common/mxfp8.cuh"
 #include "attn.h"
+#include "attn_math.cuh"
 
 namespace gm {
 
@@ -28,29 +29,7 @@ constexpr int AT_THREADS = 288;
 constexpr int SLAB_BYTES = AT_BM * 64 * 2;          // 128 rows x 64 bf16 columns (one 128-byte-swizzled TMA box)
 constexpr int V_BYTES = AT_BN * AT_D * 2;
 constexpr uint32_t AT_TMEM_COLS = 256;
-constexpr int POLY_PER_8 = 3;     // of every 8 exponentials, how many run on the FMA pipe instead of MUFU
 constexpr int KV_STAGES = 2;      // key/value tiles in flight: the global->shared latency of a strided tile spans more than one tile of work
-
-// 2^x for x <= 0 on the FMA pipe: split x into integer and fraction, cubic minimax polynomial for 2^frac (max relative
-// error about 1e-4, below bf16 resolution), exponent added through the float's bit pattern.  The MUFU unit evaluates
-// only 16 exponentials per clock per SM, which for head size 64 is slower than the tensor cores; evaluating part of
-// every row here lets both pipes work at once.
-__device__ __forceinline__ float exp2_poly(float x) {
-    x = fmaxf(x, -125.f);
-    const float shifted = x + 12582912.f;                       // 1.5 * 2^23: the integer part lands in the low mantissa bits
-    const float xi = shifted - 12582912.f;
-    const float f = x - xi;                                     // f in [-0.5, 0.5]
-    float pl = fmaf(f, 0.0555041086f, 0.2402265069f);
-    pl = fmaf(pl, f, 0.6931471806f);
-    pl = fmaf(pl, f, 1.0f);
-    return __int_as_float(__float_as_int(pl) + (__float_as_int(shifted) << 23));
-}
-
-__device__ __forceinline__ float tanh_approx(float x) {
-    float y;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 
 __device__ __forceinline__ void tma_load_2d_as3d(void* dst, const void* tmap, uint64_t* bar, int col, int row) {
     tma_load_3d(dst, tmap, bar, col, row, 0);
@@ -350,6 +329,7 @@ static cudaError_t launch_fwd_variant(const CUtensorMap& tq, const CUtensorMap& 
 }
 
 cudaError_t launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t stream) {
+    if (!p.single_tile && attn_fwd_dual_supported(p)) return launch_attn_fwd_dual(tq, tk, tv, p, stream);
     const bool capped = p.softcap > 0.f;
     if (p.qk_dim == 128) return capped ? launch_fwd_variant<128, true>(tq, tk, tv, p, stream) : launch_fwd_variant<128, false>(tq, tk, tv, p, stream);
     return capped ? launch_fwd_variant<64, true>(tq, tk, tv, p, stream) : launch_fwd_variant<64, false>(tq, tk, tv, p, stream);

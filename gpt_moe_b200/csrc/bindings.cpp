@@ -266,8 +266,9 @@ const int* doc_start_ptr(const c10::optional<torch::Tensor>& doc_start, int64_t 
 }
 
 // `quantize`: also return the MXFP8 copy of out (payload uint8 [B*T, H*64], scale records), written by the kernel's epilogue.
+// `single_tile`: keep the call on the kernel with one query tile per CTA (the other kernel is checked against it).
 std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, int64_t window, double scale,
-                                    double softcap, const c10::optional<torch::Tensor>& doc_start, bool quantize) {
+                                    double softcap, const c10::optional<torch::Tensor>& doc_start, bool quantize, bool single_tile) {
     c10::cuda::CUDAGuard guard(q.device());
     const int B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
     GM_CHECK((D == 64 || D == 128) && k.size(3) == D && v.size(3) == 64 && T % 128 == 0 && H % Hkv == 0,
@@ -292,6 +293,7 @@ std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor&
         p.out_sf = osf.data_ptr<uint8_t>();
     }
     p.status = status_tensor(q.device().index()).data_ptr<int>();
+    p.single_tile = single_tile ? 1 : 0;
     cudaError_t e = gm::launch_attn_fwd(head_map(q, 128), head_map(k, 128), head_map(v, 128), p, current_stream());
     GM_CHECK(e == cudaSuccess, cudaGetErrorString(e));
     if (quantize) return {out, lse, oq, osf};
@@ -354,7 +356,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_mxfp8", &gemm_mxfp8, py::arg("a"), py::arg("sfa"), py::arg("b"), py::arg("sfb"), py::arg("d"), py::arg("alpha") = 1.0,
           py::arg("tile_expert") = py::none(), py::arg("num_m_tiles") = py::none());
     m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0,
-          py::arg("doc_start") = py::none(), py::arg("quantize") = false);
+          py::arg("doc_start") = py::none(), py::arg("quantize") = false, py::arg("single_tile") = false);
     m.def("attn_bwd", &attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("d_out"), py::arg("lse"), py::arg("dk"),
           py::arg("dv"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0, py::arg("doc_start") = py::none());
     gm::register_kernels(m);

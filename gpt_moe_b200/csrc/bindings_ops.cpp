@@ -211,6 +211,17 @@ Tensor mla_decode(const Tensor& q_latent, const Tensor& q_rope, const Tensor& la
     return context;
 }
 
+// (issue clocks, completion clocks) of `count` chained tcgen05.mma instructions of shape code `shape` (csrc/bench/mma_issue.cu)
+std::vector<int64_t> mma_issue_bench(int64_t shape, int64_t count) {
+    GM_CHECK(count > 0 && count % 4 == 0 && count <= 4096, "mma_issue_bench: count must be a multiple of 4, at most 4096");
+    auto out = torch::zeros({2}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA));
+    cudaError_t e = launch_mma_issue(static_cast<int>(shape), reinterpret_cast<long long*>(out.data_ptr<int64_t>()), static_cast<int>(count),
+                                     status_word(out.device().index()), stream());
+    GM_CHECK(e == cudaSuccess, cudaGetErrorString(e));
+    auto host = out.cpu();
+    return {host[0].item<int64_t>(), host[1].item<int64_t>()};
+}
+
 bool mla_decode_ok(int64_t H, int64_t Hkv, int64_t r, int64_t dr) { return mla_decode_supported(H, Hkv, r, dr); }
 
 // Counted routing.  Returns (dest[S], src_of_row[cap], seg_ends[E], counts[E], tile_expert[cap/128], meta[2]).
@@ -569,6 +580,7 @@ void register_kernels(pybind11::module_& m) {
           py::arg("smin"), py::arg("smax"), py::arg("dq32") = py::none(), py::arg("quantize") = false);
     m.def("mla_decode", &mla_decode);
     m.def("mla_decode_ok", &mla_decode_ok);
+    m.def("mma_issue_bench", &mma_issue_bench, py::arg("shape"), py::arg("count") = 64);
     m.def("router_fwd", &router_fwd);
     m.def("router_bwd", &router_bwd);
     m.def("route", &route);

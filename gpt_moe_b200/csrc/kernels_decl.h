@@ -97,4 +97,7 @@ bool launch_ep_dispatch(const void* src, const long long* idx, const int* dest, 
 bool launch_ep_combine(const void* ret, const long long* idx, const int* route_row, const float* gates, void* out, void* keep_rows,
                        const long long* deltas, int world, int tokens, int d, int top_k, int per_rank, int cap_rows, cudaStream_t s);
 
+// csrc/bench/mma_issue.cu: clocks to issue / to complete `count` chained tcgen05.mma instructions of one shape (see the file)
+cudaError_t launch_mma_issue(int shape, long long* out, int count, int* status, cudaStream_t s);
+
 }  // namespace gm

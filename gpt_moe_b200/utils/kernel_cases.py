@@ -25,13 +25,21 @@ def _timed(fn, iters):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_mxfp8", "quantize", "gemm_wgrad", "grouped", "attn_fwd", "attn_bwd", "rs_muon", "ce", "rmsnorm", "rope", "rope_bwd", "ep_dispatch", "ep_combine", "rmsnorm_bwd", "attn_fwd_mla", "attn_bwd_mla", "gemm_xxt", "gemm_xxt_full", "polar", "gemm_big", "gemm_mxfp8_big", "gemm_mxfp8_down", "quantize_weight"])
+    ap.add_argument("case", choices=["gemm", "gemm_mxfp8", "quantize", "gemm_wgrad", "grouped", "attn_fwd", "attn_fwd_full", "attn_bwd", "attn_bwd_full", "rs_muon", "ce", "rmsnorm", "rope", "rope_bwd", "ep_dispatch", "ep_combine", "rmsnorm_bwd", "attn_fwd_mla", "attn_bwd_mla", "gemm_xxt", "gemm_xxt_full", "polar", "gemm_big", "gemm_mxfp8_big", "gemm_mxfp8_down", "quantize_weight", "mma_issue"])
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--single-tile", action="store_true", help="attention forward: the kernel with one query tile per CTA")
     args = ap.parse_args()
     from gpt_moe_b200.ops import attention_tc, cuda_ops
     c = cuda_ops.ext()
     dev = "cuda"
     torch.manual_seed(0)
+    if args.case == "mma_issue":                 # device clocks of chained tcgen05.mma instructions, one CTA (csrc/bench/mma_issue.cu)
+        names = ["M128 N128", "M128 N256", "M128 N64", "M128 N16", "M128 N64, A in TMEM, B MN-major", "M128 N256, A in TMEM",
+                 "M64 N256, A MN-major", "M64 N128, A MN-major"]
+        for shape, name in enumerate(names):
+            issue, done = c.mma_issue_bench(shape, 64)
+            print(f"mma_issue: {name}: 64 instructions issued in {issue} clk, complete after {done} clk = {done / 64:.1f} clk each")
+        return
     flops = bytes_ = 0
     if args.case == "gemm":                      # QKV projection shape: [32768, 768] x [2304, 768]^T
         a = torch.randn(32768, 768, device=dev).bfloat16(); b = torch.randn(2304, 768, device=dev).bfloat16()
@@ -81,13 +89,13 @@ def main() -> None:
         out = torch.empty(packed.shape[0], 6144, device=dev, dtype=torch.bfloat16)
         fn = lambda: c.gemm_bf16(packed, w, out, False, False, 1.0, 0.0, None, False, 1, tiles, meta, None)
         flops = 2 * 32768 * 6144 * 768
-    elif args.case in ("attn_fwd", "attn_bwd"):  # 4 x 2048 tokens, 12 heads, window 1024
-        b_, t, h, d = 4, 2048, 12, 64
+    elif args.case in ("attn_fwd", "attn_fwd_full", "attn_bwd", "attn_bwd_full"):  # 4 (full: 16) x 2048 tokens, 12 heads, window 1024
+        b_, t, h, d = (16 if args.case.endswith("_full") else 4), 2048, 12, 64
         packed = torch.randn(b_, t, 3 * h * d, device=dev).bfloat16().requires_grad_()
         q, k, v = cuda_ops.split_qkv(packed, h, h, d)
         keys = sum(min(i, 1024) + 1 for i in range(t))
-        if args.case == "attn_fwd":
-            fn = lambda: c.attn_fwd(q.detach(), k.detach(), v.detach(), 1024, d ** -0.5)
+        if not args.case.startswith("attn_bwd"):
+            fn = lambda: c.attn_fwd(q.detach(), k.detach(), v.detach(), 1024, d ** -0.5, single_tile=args.single_tile)
             flops = 4 * d * keys * b_ * h
         else:
             out = attention_tc.attention(q, k, v, window=1024, scale=None)

@@ -138,6 +138,9 @@ def test_producers_emit_the_quantised_copy_of_what_they_write(ops):
     out_plain, _ = c.attn_fwd(qh, kh, vh, 100, 0.125)
     assert torch.equal(out, out_plain)
     _check_copy(oq, osf, out.reshape(b_ * t_, h_ * 64), b_ * t_)
+    # the same through the kernel with one query tile per CTA (sequence lengths that are not a multiple of 256, document masks)
+    out1, _, oq1, osf1 = c.attn_fwd(qh, kh, vh, 100, 0.125, 0.0, None, True, True)
+    _check_copy(oq1, osf1, out1.reshape(b_ * t_, h_ * 64), b_ * t_)
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (1000, 768, 768), (4096, 2304, 768), (200, 1000, 256)])

@@ -332,6 +332,36 @@ def test_attention_forward_kernel(ops, t, window, hq, hk):
     assert torch.allclose(lse, torch.logsumexp(s.masked_fill(~keep, float("-inf")), dim=-1), atol=2e-2)
 
 
+@pytest.mark.parametrize("t,window,hq,hk,gain,softcap", [
+    (256, 1000, 2, 2, 1.0, 0.0), (512, 128, 4, 2, 1.0, 0.0), (1024, 300, 2, 1, 1.0, 0.0), (2048, 1024, 2, 1, 1.0, 0.0), (512, 0, 2, 2, 1.0, 0.0),
+    (768, 77, 2, 2, 1.0, 0.0), (2048, 5000, 1, 1, 1.0, 0.0), (1024, 500, 2, 2, 6.0, 0.0), (2048, 1024, 2, 2, 12.0, 0.0), (512, 200, 2, 1, 3.0, 20.0)])
+def test_attention_forward_two_query_tiles_per_cta(ops, t, window, hq, hk, gain, softcap):
+    """The forward kernel that shares key/value tiles between two query tiles and keeps O in TMEM: against the fp32 reference and
+    against the single-tile kernel.  `gain` scales the queries so that row maxima keep growing from tile to tile (the row's
+    reference maximum moves and O is rescaled in TMEM) or stay within the slack (a stale reference is used)."""
+    torch.manual_seed(11)
+    b, d = 2, 64
+    packed = torch.randn(b, t, (hq + 2 * hk) * d, device="cuda")
+    packed[..., : hq * d] *= gain
+    packed = packed.bfloat16()
+    q = packed[..., : hq * d].unflatten(-1, (hq, d))
+    k = packed[..., hq * d: (hq + hk) * d].unflatten(-1, (hk, d))
+    v = packed[..., (hq + hk) * d:].unflatten(-1, (hk, d))
+    c = ops.ext()
+    out, lse = c.attn_fwd(q, k, v, window, d ** -0.5, softcap)
+    one, lse_one = c.attn_fwd(q, k, v, window, d ** -0.5, softcap, None, False, True)
+    ops.check_status()
+    want = ref.attention(q.float(), k.float(), v.float(), causal=True, window=window, softcap_value=softcap, tanh_backend="exact")
+    assert rel(out, want) < 1e-2
+    assert rel(out, one) < 6e-3
+    assert torch.allclose(lse, lse_one, atol=2e-2, rtol=1e-3)
+    if softcap == 0.0:
+        rep = hq // hk
+        s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float().repeat_interleave(rep, dim=2)) * d ** -0.5
+        keep = ref.attention_mask(t, "cuda", True, window)
+        assert torch.allclose(lse, torch.logsumexp(s.masked_fill(~keep, float("-inf")), dim=-1), atol=2e-2, rtol=1e-3)
+
+
 @pytest.mark.parametrize("t,window,hq,hk", [(256, 1000, 2, 2), (512, 128, 4, 2), (1024, 300, 2, 1), (384, 0, 2, 2)])
 def test_attention_backward_kernel(ops, t, window, hq, hk):
     from gpt_moe_b200.ops import attention_tc
@@ -615,3 +645,13 @@ def test_quantised_weights_are_cached_across_micro_steps_and_refreshed_after_an_
     assert second[1] is not first[1]
     want_q, _ = ref.mxfp8_quantize(w.detach().bfloat16().float(), -1)
     assert torch.equal(second[1].view(torch.float8_e4m3fn).float(), want_q.float())
+
+
+def test_mma_issue_bench_reports_device_clocks(ops):
+    """The issue-rate probe runs, completes (bounded wait) and shows the instruction time growing with N only above the floor."""
+    c = ops.ext()
+    issue256, done256 = c.mma_issue_bench(1, 64)       # M128 N256
+    issue64, done64 = c.mma_issue_bench(2, 64)         # M128 N64
+    ops.check_status()
+    assert 0 < issue256 <= done256 and 0 < issue64 <= done64
+    assert done64 < done256 < 8 * done64
