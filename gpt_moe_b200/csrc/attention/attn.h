@@ -30,7 +30,8 @@ struct AttnParams {
     void* dv;
     long long dkv_stride, dv_stride;
     int* status;
-    int single_tile;                // forward: 1 keeps the call on the kernel with one query tile per CTA
+    int single_tile;                // 1 keeps the call on the basic kernel of its direction: one query tile per CTA (forward),
+                                    // score and gradient products in program order (backward)
 };
 
 cudaError_t launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t stream);
@@ -39,6 +40,11 @@ cudaError_t launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const 
 // launch_attn_fwd picks it when it applies and `single_tile` is 0.
 bool attn_fwd_dual_supported(const AttnParams& p);
 cudaError_t launch_attn_fwd_dual(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t stream);
+
+// Backward with the next tile's score products issued ahead of the current gradient products (attn_bwd_pipe.cu): 64-wide heads.
+// launch_attn_bwd picks it when it applies and `single_tile` is 0.
+cudaError_t launch_attn_bwd_pipe(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                                 const CUtensorMap& tdq, const AttnParams& p, cudaStream_t stream);
 
 cudaError_t launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                             const CUtensorMap& tdq, const AttnParams& p, const void* d_out, const void* out, long long do_stride,

@@ -300,11 +300,12 @@ std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor&
     return {out, lse};
 }
 
-// Backward.  q, k, v, out, d_out: [B,T,H(kv),64] bf16 views; lse [B,H,T].  dk, dv: [B,T,Hkv,64] bf16 views that are written
+// Backward.  `unpipelined`: keep the call on the kernel that issues its products in program order (the other is checked against it).
+// q, k, v, out, d_out: [B,T,H(kv),64] bf16 views; lse [B,H,T].  dk, dv: [B,T,Hkv,64] bf16 views that are written
 // (they may be column slices of a packed gradient buffer).  Returns dq as fp32 [B,T,H,64].
 torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, const torch::Tensor& out,
                        const torch::Tensor& d_out, const torch::Tensor& lse, torch::Tensor& dk, torch::Tensor& dv, int64_t window,
-                       double scale, double softcap, const c10::optional<torch::Tensor>& doc_start) {
+                       double scale, double softcap, const c10::optional<torch::Tensor>& doc_start, bool unpipelined) {
     c10::cuda::CUDAGuard guard(q.device());
     const int B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
     GM_CHECK((D == 64 || D == 128) && k.size(3) == D && v.size(3) == 64 && T % 128 == 0 && H % Hkv == 0,
@@ -327,6 +328,7 @@ torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const tor
     p.dq_accum = dq.data_ptr<float>();
     p.dk = dk.data_ptr(); p.dv = dv.data_ptr(); p.dkv_stride = dk.stride(1); p.dv_stride = dv.stride(1);
     p.status = status_tensor(q.device().index()).data_ptr<int>();
+    p.single_tile = unpipelined ? 1 : 0;
     const CUtensorMap& tdq = cached_map(dq.data_ptr(), 4, static_cast<uint64_t>(H) * D, static_cast<uint64_t>(B) * T, 1,
                                         static_cast<uint64_t>(H) * D * 4, 0, 32, 128, 128);
     cudaError_t e = gm::launch_attn_bwd(head_map(q, 128), head_map(k, 128), head_map(v, 128), head_map(d_out, 128), tdq, p,
@@ -358,6 +360,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0,
           py::arg("doc_start") = py::none(), py::arg("quantize") = false, py::arg("single_tile") = false);
     m.def("attn_bwd", &attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("d_out"), py::arg("lse"), py::arg("dk"),
-          py::arg("dv"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0, py::arg("doc_start") = py::none());
+          py::arg("dv"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0, py::arg("doc_start") = py::none(),
+          py::arg("unpipelined") = false);
     gm::register_kernels(m);
 }

@@ -27,7 +27,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["gemm", "gemm_mxfp8", "quantize", "gemm_wgrad", "grouped", "attn_fwd", "attn_fwd_full", "attn_bwd", "attn_bwd_full", "rs_muon", "ce", "rmsnorm", "rope", "rope_bwd", "ep_dispatch", "ep_combine", "rmsnorm_bwd", "attn_fwd_mla", "attn_bwd_mla", "gemm_xxt", "gemm_xxt_full", "polar", "gemm_big", "gemm_mxfp8_big", "gemm_mxfp8_down", "quantize_weight", "mma_issue"])
     ap.add_argument("--iters", type=int, default=3)
-    ap.add_argument("--single-tile", action="store_true", help="attention forward: the kernel with one query tile per CTA")
+    ap.add_argument("--single-tile", action="store_true", help="attention: the basic kernels (one query tile per CTA forward, unpipelined backward)")
     args = ap.parse_args()
     from gpt_moe_b200.ops import attention_tc, cuda_ops
     c = cuda_ops.ext()
@@ -97,10 +97,12 @@ def main() -> None:
         if not args.case.startswith("attn_bwd"):
             fn = lambda: c.attn_fwd(q.detach(), k.detach(), v.detach(), 1024, d ** -0.5, single_tile=args.single_tile)
             flops = 4 * d * keys * b_ * h
-        else:
-            out = attention_tc.attention(q, k, v, window=1024, scale=None)
+        else:                                        # the binding itself: delta pre-pass, zeroed fp32 dQ, the backward kernel
+            qd, kd, vd = q.detach(), k.detach(), v.detach()
+            out, lse = c.attn_fwd(qd, kd, vd, 1024, d ** -0.5)
             g = torch.randn_like(out)
-            fn = lambda: torch.autograd.grad(out, packed, g, retain_graph=True)
+            dk, dv = torch.empty_like(kd), torch.empty_like(vd)
+            fn = lambda: c.attn_bwd(qd, kd, vd, out, g, lse, dk, dv, 1024, d ** -0.5, 0.0, None, args.single_tile)
             flops = 10 * d * keys * b_ * h
     elif args.case in ("attn_fwd_mla", "attn_bwd_mla"):   # multi-head latent attention shape: 128-wide query/key heads, 64-wide values, causal 4096
         b_, t, h = 2, 4096, 16

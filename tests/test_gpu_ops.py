@@ -388,6 +388,38 @@ def test_attention_backward_kernel(ops, t, window, hq, hk):
             assert rel(got[..., sl], exp[..., sl]) < 2e-2, name
 
 
+@pytest.mark.parametrize("t,window,hq,hk,softcap,docs", [(256, 1000, 2, 2, 0.0, False), (512, 128, 4, 2, 0.0, False), (1024, 300, 2, 1, 0.0, False),
+                                                         (2048, 1024, 4, 2, 0.0, False), (384, 0, 2, 2, 0.0, False), (640, 77, 2, 1, 0.0, False),
+                                                         (1024, 400, 2, 2, 15.0, False), (1024, 5000, 2, 1, 0.0, True)])
+def test_attention_backward_pipelined_matches_unpipelined(ops, t, window, hq, hk, softcap, docs):
+    """The backward kernel that issues the next tile's score products ahead of the current gradient products forms the same
+    P and dS as the kernel that issues everything in program order; only the order of the fp32 additions into dQ differs."""
+    from gpt_moe_b200.ops import attention_tc
+    torch.manual_seed(12)
+    b, d = 2, 64
+    c = ops.ext()
+    packed = torch.randn(b, t, (hq + 2 * hk) * d, device="cuda").bfloat16()
+    q, k, v = ops.split_qkv(packed, hq, hk, d)
+    doc_start = None
+    if docs:
+        ids = torch.cumsum((torch.rand(b, t, device="cuda") < 0.01).long(), dim=1)
+        doc_start = attention_tc.document_starts(ids)
+    out, lse = c.attn_fwd(q, k, v, min(window, t), d ** -0.5, softcap, doc_start)
+    g = torch.randn_like(out)
+    results = []
+    for unpipelined in (False, True):
+        dk = torch.empty(b, t, hk, d, device="cuda", dtype=torch.bfloat16)
+        dv = torch.empty(b, t, hk, d, device="cuda", dtype=torch.bfloat16)
+        dq = c.attn_bwd(q, k, v, out, g, lse, dk, dv, min(window, t), d ** -0.5, softcap, doc_start, unpipelined)
+        ops.check_status()
+        results.append((dq, dk.float(), dv.float()))
+    for got, want, name in zip(results[0], results[1], ("dq", "dk", "dv")):
+        scale = want.abs().max().item()
+        assert (got - want).abs().max().item() <= 2e-2 * scale + 1e-6, name
+        if scale > 1e-6:
+            assert rel(got, want) < 2e-3, name
+
+
 @pytest.mark.parametrize("t,window,hq,hk", [(256, 1000, 2, 2), (512, 128, 4, 2), (1024, 2000, 2, 1)])
 def test_attention_kernels_wide_query_key_heads(ops, t, window, hq, hk):
     """Multi-head latent attention shape: 128-wide query / key heads (content + rotary), 64-wide value heads."""
