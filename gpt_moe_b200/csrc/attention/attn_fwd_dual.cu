@@ -57,22 +57,30 @@ __device__ __forceinline__ void dual_prepare32(uint32_t (&v32)[32], int kv0, int
 
 __device__ __forceinline__ void dual_max32(const uint32_t (&v32)[32], float (&mx)[4]) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v32[i]));
+    for (int i = 0; i < 32; i += 2) mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], __uint_as_float(v32[i]), __uint_as_float(v32[i + 1]));
 }
 
-// Exponentials of 32 prepared scores against `base`, packed to bf16 pairs and stored to 16 P columns.
-__device__ __forceinline__ void dual_exp32(const uint32_t (&v32)[32], uint32_t p_addr, float c, float base, float (&sum)[4]) {
+// Exponentials of 32 prepared scores against `base`, packed to bf16 pairs and stored to 16 P columns.  The scores are taken
+// two at a time: scale-and-shift, the polynomial and the row sum are packed f32x2 instructions (the softmax warps are short of
+// issue slots, not of arithmetic throughput); of every 8 exponentials POLY_PER_8 (one or two pairs) use the polynomial.
+__device__ __forceinline__ void dual_exp32(const uint32_t (&v32)[32], uint32_t p_addr, uint64_t c2, uint64_t neg_base2, uint64_t (&sum2)[2]) {
+    static_assert(POLY_PER_8 % 2 == 0, "pairs of scores share one form of the exponential");
     uint32_t packed[16];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
-        float e2[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const float arg = fmaf(__uint_as_float(v32[i + u]), c, -base);
-            e2[u] = ((i + u) % 8 < POLY_PER_8) ? exp2_poly(arg) : exp2f(arg);
-            sum[(i + u) & 3] += e2[u];
+        const uint64_t arg = fma2(pack2(__uint_as_float(v32[i]), __uint_as_float(v32[i + 1])), c2, neg_base2);
+        uint64_t e;
+        if (i % 8 < POLY_PER_8) {
+            e = exp2_poly2(arg);
+        } else {
+            float a0, a1;
+            unpack2(arg, a0, a1);
+            e = pack2(exp2f(a0), exp2f(a1));
         }
-        packed[i >> 1] = pack_bf16x2(e2[0], e2[1]);
+        sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], e);
+        float e0, e1;
+        unpack2(e, e0, e1);
+        packed[i >> 1] = pack_bf16x2(e0, e1);
     }
     tmem_st_32x32b_x16(p_addr, packed);
 }
@@ -147,27 +155,31 @@ __device__ __forceinline__ void dual_softmax_tile(uint32_t s_addr, uint32_t p_ad
         if (grow) m_ref = m_tile;
     }
     const float base = m_ref == -INFINITY ? 0.f : m_ref;       // a row may have no visible key yet
-    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint64_t c2 = pack2(c, c), neg_base2 = pack2(-base, -base);
+    uint64_t sum2[2] = {0ull, 0ull};                        // two packed pairs of partial row sums (bit pattern of 0.f, 0.f)
     uint32_t s2[32];
     tmem_ld_32x32b_x32(s_addr + 64, s2);
-    if (cls[0] != CHUNK_EMPTY) dual_exp32(s0, p_addr, c, base, sum); else dual_zero16(p_addr);
+    if (cls[0] != CHUNK_EMPTY) dual_exp32(s0, p_addr, c2, neg_base2, sum2); else dual_zero16(p_addr);
     tmem_ld_wait();
     tmem_ld_32x32b_x32(s_addr + 96, s0);
-    if (cls[1] != CHUNK_EMPTY) dual_exp32(s1, p_addr + 16, c, base, sum); else dual_zero16(p_addr + 16);
+    if (cls[1] != CHUNK_EMPTY) dual_exp32(s1, p_addr + 16, c2, neg_base2, sum2); else dual_zero16(p_addr + 16);
     if (cls[2] != CHUNK_EMPTY) {
         dual_prepare_chunk<CAP>(s2, cls[2], kv0 + 64, qpos, window, cap_a, cap_b);
-        dual_exp32(s2, p_addr + 32, c, base, sum);
+        dual_exp32(s2, p_addr + 32, c2, neg_base2, sum2);
     } else {
         dual_zero16(p_addr + 32);
     }
     tmem_ld_wait();
     if (cls[3] != CHUNK_EMPTY) {
         dual_prepare_chunk<CAP>(s0, cls[3], kv0 + 96, qpos, window, cap_a, cap_b);
-        dual_exp32(s0, p_addr + 48, c, base, sum);
+        dual_exp32(s0, p_addr + 48, c2, neg_base2, sum2);
     } else {
         dual_zero16(p_addr + 48);
     }
-    l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+    float t0, t1, t2, t3;
+    unpack2(sum2[0], t0, t1);
+    unpack2(sum2[1], t2, t3);
+    l += (t0 + t1) + (t2 + t3);
 }
 
 template <bool CAPPED>
