@@ -37,6 +37,8 @@ constexpr int DU_STAGES = 4;
 constexpr int DU_TILE_BYTES = 128 * 64 * 2;             // a 128 x 64 bf16 tile (one 128-byte-swizzled TMA box)
 constexpr uint32_t DU_TMEM_COLS = 512;
 constexpr uint32_t DU_COL_S = 0, DU_COL_P = 256, DU_COL_O = 384;
+constexpr int DU_POLY_PER_8 = 2;                         // exponentials of every 8 evaluated as a polynomial on the FMA pipe (0 or an even number;
+                                                         // 232 us with 2, 241 us with 0 on 16 x 2048 tokens, 12 heads, window 1024)
 constexpr float DU_RESCALE_STEP = 8.f;                   // log2 units the row maximum may outgrow its reference before O is rescaled
 
 // Capping and masking of 32 scores (columns kv0 .. kv0 + 31 of the key tile) in place.
@@ -62,15 +64,15 @@ __device__ __forceinline__ void dual_max32(const uint32_t (&v32)[32], float (&mx
 
 // Exponentials of 32 prepared scores against `base`, packed to bf16 pairs and stored to 16 P columns.  The scores are taken
 // two at a time: scale-and-shift, the polynomial and the row sum are packed f32x2 instructions (the softmax warps are short of
-// issue slots, not of arithmetic throughput); of every 8 exponentials POLY_PER_8 (one or two pairs) use the polynomial.
+// issue slots, not of arithmetic throughput); of every 8 exponentials DU_POLY_PER_8 use the polynomial.
 __device__ __forceinline__ void dual_exp32(const uint32_t (&v32)[32], uint32_t p_addr, uint64_t c2, uint64_t neg_base2, uint64_t (&sum2)[2]) {
-    static_assert(POLY_PER_8 % 2 == 0, "pairs of scores share one form of the exponential");
+    static_assert(DU_POLY_PER_8 % 2 == 0, "pairs of scores share one form of the exponential");
     uint32_t packed[16];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
         const uint64_t arg = fma2(pack2(__uint_as_float(v32[i]), __uint_as_float(v32[i + 1])), c2, neg_base2);
         uint64_t e;
-        if (i % 8 < POLY_PER_8) {
+        if (i % 8 < DU_POLY_PER_8) {
             e = exp2_poly2(arg);
         } else {
             float a0, a1;
