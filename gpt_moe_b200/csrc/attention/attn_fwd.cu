@@ -15,6 +15,8 @@
 // halves of a row exchange only their running maximum, through shared memory, once per key tile.  K and V each use a
 // two-deep ring of shared-memory tiles refilled as soon as the MMA reading a tile has committed; two CTAs fit per SM
 // (80 KB shared memory, 256 TMEM columns each), so one CTA's softmax overlaps the other's MMAs.
+// Calls with 64-wide heads, no document mask and a sequence length that is a multiple of 256 go to attn_fwd_dual.cu instead
+// (two query tiles per CTA); this kernel serves the rest and is the one that kernel is tested against.
 // Reference counterpart: FlexAttention with the causal + sliding-window BlockMask (model/gpt.py:311-687,
 // model/attention/self_attention.py:250-255); here the window test is exact per token in every tile.
 #include "../common/ptx.cuh"

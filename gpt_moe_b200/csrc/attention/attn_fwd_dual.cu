@@ -7,12 +7,12 @@
 //   warps 0-3   softmax of tile A: thread = query row, running maximum / sum in registers, P written to TMEM as packed bf16 pairs
 //   warps 4-7   the same for tile B
 //   warp  8, 9  MMA issue for tile A and for tile B (one thread each):  S_x = Q_x K^T  (M128 N128 K64),
-//               O_x += P_x V  (M128 N64 K128, A from TMEM).  Each query tile has its own issuing thread because issuing is the
-//               scarce resource at this head size: a tcgen05.mma takes about 60 clocks to issue whatever its N, a commit about
-//               130 and a wait on a barrier that is already complete about 100, so one thread serving both tiles spent 1850
-//               clocks per (query tile, key tile) against 512 clocks of tensor-core work.  The descriptors are formed once and
-//               advanced by adding to their address field; one commit per step signals both the PV product of the step
-//               and the S product of the next one
+//               O_x += P_x V  (M128 N64 K128, A from TMEM).  A thread serving both tiles in turn spent 1850 clocks per
+//               (query tile, key tile) - eight N = 64 instructions 960, four N = 128 instructions 275, four commits 130 each,
+//               waits on complete barriers 100 each - against 512 clocks of tensor-core work, so each tile has its own
+//               thread, the descriptors are formed once and advanced by adding to their address field, and one commit per
+//               step announces both the PV product of the step and the S product of the next one.  (The kernel time did
+//               not change with that alone: the softmax of a tile, 1700 clocks, is the longer part of its chain.)
 //   warp  10    TMA loads (one thread): Q once, then the K and V tile of a ring stage as it comes free
 // O stays in TMEM for the whole CTA and the PV product accumulates into it.  The running maximum a row's exponentials are
 // taken against is only moved when the row's maximum has grown by more than 2^8 since it was last moved; then (rarely
