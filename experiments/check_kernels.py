@@ -3,8 +3,9 @@
 every kernel with its plain-PyTorch definition — ragged and empty experts, widths that are not tile multiples,
 non-contiguous inputs, gradients requested for a subset of the inputs or outputs, quantised weights cached across
 accumulation micro-steps, top-k 1 and 2, attention windows, MXFP8 against its emulation — first on the normal build and
-then once more on the bounds-checked build (`GM_CHECK_BOUNDS=1`, every data-dependent index tested), and prints one summary
-line per pass.  Usage: `python experiments/check_kernels.py [--skip-checked]`.
+then on the bounds-checked build (`GM_CHECK_BOUNDS=1`, every data-dependent index tested), then on the same build with
+`GM_CANARIES=1` (guard bytes around every output and scratch buffer the bindings allocate, a device synchronisation after every
+call), and prints one summary line per pass.  Usage: `python experiments/check_kernels.py [--skip-checked]`.
 """
 from __future__ import annotations
 
@@ -22,4 +23,7 @@ if __name__ == "__main__":
         # the extension variant is chosen when it is first loaded: the checked pass runs in a fresh interpreter
         env = dict(os.environ, GM_CHECK_BOUNDS="1")
         code = subprocess.run([sys.executable, "-m", "pytest", "-q", "-m", "gpu"] + files[:2], env=env, cwd=root).returncode
+        if code == 0:
+            env["GM_CANARIES"] = "1"
+            code = subprocess.run([sys.executable, "-m", "pytest", "-q", "-m", "gpu"] + files[:2], env=env, cwd=root).returncode
     sys.exit(code)

@@ -8,6 +8,7 @@
 #include <list>
 #include <unordered_map>
 
+#include "guarded_alloc.h"
 #include "gemm/gemm.h"
 #include "attention/attn.h"
 #include "kernels.h"
@@ -179,9 +180,9 @@ std::vector<torch::Tensor> mxfp8_quantize(const torch::Tensor& x, const c10::opt
     GM_CHECK(x.stride(-1) == 1 && x.size(-1) % 32 == 0 && x.stride(-2) % 8 == 0, "mxfp8_quantize: last dimension contiguous, multiple of 32");
     const int64_t batch = x.dim() == 3 ? x.size(0) : 1, rows = x.size(-2), cols = x.size(-1);
     GM_CHECK(batch == 1 || rows % 128 == 0 || x.is_contiguous(), "mxfp8_quantize: batched input must be contiguous");
-    auto q = torch::empty(x.sizes(), x.options().dtype(torch::kUInt8));
+    auto q = gm::out_empty(x.sizes(), x.options().dtype(torch::kUInt8));
     // not cleared: bytes of rows that exist are all written; the rest belongs to rows the GEMM clips
-    auto sf = torch::empty({batch, sf_records(rows, cols) * 512}, x.options().dtype(torch::kUInt8));
+    auto sf = gm::out_empty({batch, sf_records(rows, cols) * 512}, x.options().dtype(torch::kUInt8));
     for (int64_t z = 0; z < batch; ++z) {
         const auto* src = static_cast<const at::BFloat16*>(x.data_ptr()) + (x.dim() == 3 ? z * x.stride(0) : 0);
         gm::launch_quantize_rows(src, q.data_ptr<uint8_t>() + z * rows * cols, sf.data_ptr<uint8_t>() + z * sf.stride(0), rows,
@@ -198,10 +199,10 @@ std::vector<torch::Tensor> mxfp8_quantize_weight(const torch::Tensor& w) {
     const int64_t batch = w.dim() == 3 ? w.size(0) : 1, rows = w.size(-2), cols = w.size(-1);
     GM_CHECK(rows % 32 == 0 && cols % 32 == 0, "mxfp8_quantize_weight: both dimensions must be multiples of 32");
     auto opt = w.options().dtype(torch::kUInt8);
-    auto q = torch::empty(w.sizes(), opt);
-    auto qt = w.dim() == 3 ? torch::empty({batch, cols, rows}, opt) : torch::empty({cols, rows}, opt);
-    auto sf = torch::empty({batch, sf_records(rows, cols) * 512}, opt);
-    auto sft = torch::empty({batch, sf_records(cols, rows) * 512}, opt);
+    auto q = gm::out_empty(w.sizes(), opt);
+    auto qt = w.dim() == 3 ? gm::out_empty({batch, cols, rows}, opt) : gm::out_empty({cols, rows}, opt);
+    auto sf = gm::out_empty({batch, sf_records(rows, cols) * 512}, opt);
+    auto sft = gm::out_empty({batch, sf_records(cols, rows) * 512}, opt);
     gm::launch_quantize_weight_dual(w.data_ptr(), q.data_ptr(), sf.data_ptr(), qt.data_ptr(), sft.data_ptr(), static_cast<int>(batch),
                                     static_cast<int>(rows), static_cast<int>(cols), sf.stride(0), sft.stride(0), current_stream());
     return {q, sf, qt, sft};
@@ -281,14 +282,14 @@ std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor&
     p.scale_log2e = static_cast<float>(scale * 1.4426950408889634);
     p.softcap = static_cast<float>(softcap);
     p.doc_start = doc_start_ptr(doc_start, static_cast<int64_t>(B) * T);
-    auto out = torch::empty({B, T, H, 64}, q.options());
-    auto lse = torch::empty({B, H, T}, q.options().dtype(torch::kFloat32));
+    auto out = gm::out_empty({B, T, H, 64}, q.options());
+    auto lse = gm::out_empty({B, H, T}, q.options().dtype(torch::kFloat32));
     p.out = out.data_ptr(); p.out_stride = H * 64; p.lse = lse.data_ptr<float>();
     torch::Tensor oq, osf;
     if (quantize) {
         const int64_t rows = static_cast<int64_t>(B) * T, cols = static_cast<int64_t>(H) * 64;
-        oq = torch::empty({rows, cols}, q.options().dtype(torch::kUInt8));
-        osf = torch::empty({sf_records(rows, cols) * 512}, q.options().dtype(torch::kUInt8));
+        oq = gm::out_empty({rows, cols}, q.options().dtype(torch::kUInt8));
+        osf = gm::out_empty({sf_records(rows, cols) * 512}, q.options().dtype(torch::kUInt8));
         p.out_q = oq.data_ptr<uint8_t>();
         p.out_sf = osf.data_ptr<uint8_t>();
     }
@@ -322,8 +323,8 @@ torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const tor
     p.softcap = static_cast<float>(softcap);
     p.doc_start = doc_start_ptr(doc_start, static_cast<int64_t>(B) * T);
     p.lse = const_cast<float*>(lse.data_ptr<float>());
-    auto delta = torch::empty({B, H, T}, lse.options());
-    auto dq = torch::zeros({B, T, H, D}, lse.options());
+    auto delta = gm::out_empty({B, H, T}, lse.options());
+    auto dq = gm::out_zeros({B, T, H, D}, lse.options());
     p.delta = delta.data_ptr<float>();
     p.dq_accum = dq.data_ptr<float>();
     p.dk = dk.data_ptr(); p.dv = dv.data_ptr(); p.dkv_stride = dk.stride(1); p.dv_stride = dv.stride(1);

@@ -4,6 +4,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include "guarded_alloc.h"
 #include "kernels.h"
 #include "kernels_decl.h"
 
@@ -28,8 +29,8 @@ QuantOut alloc_quant(bool wanted, int64_t rows, int64_t cols, const Tensor& like
     if (!wanted) return o;
     GM_CHECK(cols % 32 == 0, "MXFP8 copy: the row width must be a multiple of 32");
     auto opt = like.options().dtype(torch::kUInt8);
-    o.q = torch::empty({rows, cols}, opt);
-    o.sf = torch::empty({((rows + 127) / 128) * ((cols + 127) / 128) * 512}, opt);
+    o.q = gm::out_empty({rows, cols}, opt);
+    o.sf = gm::out_empty({((rows + 127) / 128) * ((cols + 127) / 128) * 512}, opt);
     o.qp = o.q.data_ptr<uint8_t>();
     o.sp = o.sf.data_ptr<uint8_t>();
     return o;
@@ -45,12 +46,12 @@ std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const OptTensor& w, double eps,
     const int d = x.size(-1);
     const int rows = x.numel() / d;
     GM_CHECK(norm_dim_supported(d), "rmsnorm width must be 128*{1,2,4,6,8,12,16}");
-    Tensor y = torch::empty(x.sizes(), x.options().dtype(torch::kBFloat16));
-    Tensor rstd = torch::empty({rows}, x.options().dtype(torch::kFloat32));
+    Tensor y = gm::out_empty(x.sizes(), x.options().dtype(torch::kBFloat16));
+    Tensor rstd = gm::out_empty({rows}, x.options().dtype(torch::kFloat32));
     Tensor x_new = x;
     if (branch.has_value()) {
         check_bf16(*branch, "branch");
-        x_new = torch::empty_like(x);
+        x_new = gm::out_empty_like(x);
     }
     QuantOut qo = alloc_quant(quantize, rows, d, x);
     launch_rmsnorm_fwd(x.data_ptr(), x.scalar_type() == torch::kFloat32, branch.has_value() ? branch->data_ptr() : nullptr,
@@ -66,11 +67,11 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const OptTens
     check_bf16(dy, "dy");
     const int d = x.size(-1);
     const int rows = x.numel() / d;
-    Tensor dx = torch::empty_like(x);
+    Tensor dx = gm::out_empty_like(x);
     Tensor dw, partial;
     if (w.has_value()) {
-        dw = torch::empty({d}, x.options().dtype(torch::kFloat32));
-        partial = torch::empty({rmsnorm_bwd_blocks(rows), d}, x.options().dtype(torch::kFloat32));
+        dw = gm::out_empty({d}, x.options().dtype(torch::kFloat32));
+        partial = gm::out_empty({rmsnorm_bwd_blocks(rows), d}, x.options().dtype(torch::kFloat32));
     }
     GM_CHECK(launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), x.scalar_type() == torch::kFloat32, fptr(w), rstd.data_ptr<float>(),
                                 dres.has_value() ? dres->data_ptr() : nullptr, dx.data_ptr(),
@@ -85,9 +86,9 @@ std::vector<Tensor> residual_bwd(const Tensor& dxn, const Tensor& branch, const 
     GM_CHECK(dxn.scalar_type() == torch::kFloat32 && dxn.is_contiguous() && dxn.numel() % 4 == 0, "dxn must be contiguous fp32");
     check_bf16(branch, "branch");
     GM_CHECK(beta.scalar_type() == torch::kFloat32 && beta.numel() == 1, "beta must be one fp32 value");
-    Tensor dbranch = torch::empty_like(branch);
-    Tensor partial = torch::empty({residual_bwd_blocks(dxn.numel())}, dxn.options());
-    Tensor dbeta = torch::empty({1}, dxn.options());
+    Tensor dbranch = gm::out_empty_like(branch);
+    Tensor partial = gm::out_empty({residual_bwd_blocks(dxn.numel())}, dxn.options());
+    Tensor dbeta = gm::out_empty({1}, dxn.options());
     launch_residual_bwd(dxn.data_ptr<float>(), branch.data_ptr(), beta.data_ptr<float>(), dbranch.data_ptr(), partial.data_ptr<float>(),
                         dbeta.data_ptr<float>(), dxn.numel(), stream());
     return {dbranch, dbeta};
@@ -123,7 +124,7 @@ std::vector<Tensor> rope_qknorm_bwd(const Tensor& x, const Tensor& dy, Tensor& d
     const long long tokens = x.size(0);
     const int heads = q_heads + k_heads;
     const int blocks = rope_blocks(tokens, heads);
-    Tensor partial = torch::empty({blocks, heads}, x.options().dtype(torch::kFloat32));
+    Tensor partial = gm::out_empty({blocks, heads}, x.options().dtype(torch::kFloat32));
     GM_CHECK(x.stride(0) == dx.stride(0), "dx must share x's row stride");
     if (dq32.has_value())
         GM_CHECK(dq32->scalar_type() == torch::kFloat32 && dq32->is_contiguous() && dq32->numel() == tokens * q_heads * head_dim,
@@ -139,7 +140,7 @@ std::vector<Tensor> rope_qknorm_bwd(const Tensor& x, const Tensor& dy, Tensor& d
                                 dq32.has_value() ? dq32->data_ptr<float>() : nullptr, dq32.has_value() ? q_heads * head_dim : 0,
                                 qo.qp, qo.sp, width, stream()),
              "unsupported head size for rope_qknorm");
-    Tensor dscale = torch::empty({heads}, partial.options());
+    Tensor dscale = gm::out_empty({heads}, partial.options());
     launch_column_sum(partial.data_ptr<float>(), dscale.data_ptr<float>(), blocks, heads, 0, stream());
     if (quantize) return {dscale, qo.q, qo.sf};
     return {dscale};
@@ -153,13 +154,13 @@ std::vector<Tensor> router_fwd(const Tensor& logits, int64_t top_k, bool renorma
              (logits.scalar_type() == torch::kBFloat16 || logits.scalar_type() == torch::kFloat32), "router logits: contiguous [tokens, experts] bf16 or fp32");
     const int tokens = logits.size(0), experts = logits.size(1);
     auto f32 = logits.options().dtype(torch::kFloat32);
-    Tensor top_idx = torch::empty({tokens, top_k}, logits.options().dtype(torch::kInt64));
-    Tensor gates = torch::empty({tokens, top_k}, f32);
+    Tensor top_idx = gm::out_empty({tokens, top_k}, logits.options().dtype(torch::kInt64));
+    Tensor gates = gm::out_empty({tokens, top_k}, f32);
     Tensor partial, sums, balance;
     if (want_balance) {
-        partial = torch::empty({2, router_blocks(tokens), experts}, f32);
-        sums = torch::empty({2, experts}, f32);
-        balance = torch::empty({1}, f32);
+        partial = gm::out_empty({2, router_blocks(tokens), experts}, f32);
+        sums = gm::out_empty({2, experts}, f32);
+        balance = gm::out_empty({1}, f32);
     }
     GM_CHECK(launch_router_fwd(logits.data_ptr(), logits.scalar_type() == torch::kBFloat16, top_idx.data_ptr<int64_t>() ? reinterpret_cast<long long*>(top_idx.data_ptr<int64_t>()) : nullptr,
                                gates.data_ptr<float>(), want_balance ? partial[0].data_ptr<float>() : nullptr,
@@ -178,7 +179,7 @@ Tensor router_bwd(const Tensor& logits, const Tensor& top_idx, const OptTensor& 
     const int tokens = logits.size(0), experts = logits.size(1), top_k = top_idx.size(1);
     if (dgates.has_value()) GM_CHECK(dgates->scalar_type() == torch::kFloat32 && dgates->is_contiguous() && dgates->numel() == static_cast<int64_t>(tokens) * top_k, "dgates: contiguous fp32 [tokens, k]");
     if (dbalance.has_value()) GM_CHECK(dbalance->scalar_type() == torch::kFloat32 && dbalance->numel() == 1 && counts.has_value(), "dbalance: one fp32 value, with the forward's counts");
-    Tensor dlogits = torch::empty_like(logits);
+    Tensor dlogits = gm::out_empty_like(logits);
     GM_CHECK(launch_router_bwd(logits.data_ptr(), logits.scalar_type() == torch::kBFloat16, reinterpret_cast<const long long*>(top_idx.data_ptr<int64_t>()),
                                fptr(dgates), fptr(dbalance), fptr(counts), dlogits.data_ptr(), tokens, experts, top_k, renormalise, stream()),
              "router kernel: at most 128 experts, top-k at most 8");
@@ -201,9 +202,9 @@ Tensor mla_decode(const Tensor& q_latent, const Tensor& q_rope, const Tensor& la
     GM_CHECK(latent.size(2) == r && rope.size(2) == dr && mla_decode_supported(H, Hkv, r, dr),
              "mla_decode: latent rank 256/512/768/1024, 8/16/32 heads (rank/32 * heads/8 <= 64), rope width even and <= 64");
     const int splits = mla_decode_splits(B, T, S);
-    Tensor part_ctx = torch::empty({B, T, H, splits, r}, q_latent.options());
-    Tensor part_ml = torch::empty({B, T, H, splits, 2}, q_latent.options());
-    Tensor context = torch::empty({B, T, H, r}, q_latent.options());
+    Tensor part_ctx = gm::out_empty({B, T, H, splits, r}, q_latent.options());
+    Tensor part_ml = gm::out_empty({B, T, H, splits, 2}, q_latent.options());
+    Tensor context = gm::out_empty({B, T, H, r}, q_latent.options());
     GM_CHECK(launch_mla_decode(q_latent.data_ptr<float>(), q_rope.data_ptr<float>(), latent.data_ptr(), rope.data_ptr(), key_gain.data_ptr(),
                                latent.stride(0), rope.stride(0), key_gain.stride(0), part_ctx.data_ptr<float>(), part_ml.data_ptr<float>(),
                                context.data_ptr<float>(), B, T, H, Hkv, r, dr, S, splits, start, window, static_cast<float>(scale),
@@ -214,7 +215,7 @@ Tensor mla_decode(const Tensor& q_latent, const Tensor& q_rope, const Tensor& la
 // (issue clocks, completion clocks) of `count` chained tcgen05.mma instructions of shape code `shape` (csrc/bench/mma_issue.cu)
 std::vector<int64_t> mma_issue_bench(int64_t shape, int64_t count) {
     GM_CHECK(count > 0 && count % 4 == 0 && count <= 4096, "mma_issue_bench: count must be a multiple of 4, at most 4096");
-    auto out = torch::zeros({2}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA));
+    auto out = gm::out_zeros({2}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA));
     cudaError_t e = launch_mma_issue(static_cast<int>(shape), reinterpret_cast<long long*>(out.data_ptr<int64_t>()), static_cast<int>(count),
                                      status_word(out.device().index()), stream());
     GM_CHECK(e == cudaSuccess, cudaGetErrorString(e));
@@ -232,10 +233,10 @@ std::vector<Tensor> route(const Tensor& top_idx, int64_t experts) {
     const int cap = (slots + 255) / 256 * 256 + experts * 256;      // every expert segment is padded to 256 rows
     const int chunks = (slots + 1023) / 1024;
     auto opt = top_idx.options().dtype(torch::kInt32);
-    Tensor hist = torch::empty({2, chunks > 0 ? chunks : 1, experts}, opt);
-    Tensor dest = torch::empty({slots}, opt), src = torch::empty({cap}, opt);
-    Tensor seg = torch::empty({experts}, opt), counts = torch::empty({experts}, opt);
-    Tensor tiles = torch::empty({cap / 128}, opt), meta = torch::empty({2}, opt);      // entries beyond meta[0] are never read
+    Tensor hist = gm::out_empty({2, chunks > 0 ? chunks : 1, experts}, opt);
+    Tensor dest = gm::out_empty({slots}, opt), src = gm::out_empty({cap}, opt);
+    Tensor seg = gm::out_empty({experts}, opt), counts = gm::out_empty({experts}, opt);
+    Tensor tiles = gm::out_empty({cap / 128}, opt), meta = gm::out_empty({2}, opt);      // entries beyond meta[0] are never read
     GM_CHECK(launch_route(top_idx.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(top_idx.data_ptr<int64_t>()) : nullptr, slots,
                           experts, hist[0].data_ptr<int>(), hist[1].data_ptr<int>(), counts.data_ptr<int>(), seg.data_ptr<int>(),
                           tiles.data_ptr<int>(), meta.data_ptr<int>(), dest.data_ptr<int>(), src.data_ptr<int>(), stream()),
@@ -249,7 +250,7 @@ std::vector<Tensor> gather_rows(const Tensor& hidden, const Tensor& src_of_row, 
     const int d = hidden.size(-1);
     GM_CHECK(d % 8 == 0, "row width must be a multiple of 8");
     const int cap = src_of_row.numel();
-    Tensor packed = torch::empty({cap, d}, hidden.options());
+    Tensor packed = gm::out_empty({cap, d}, hidden.options());
     QuantOut qo = alloc_quant(quantize, cap, d, hidden);
     launch_gather_rows(hidden.data_ptr(), src_of_row.data_ptr<int>(), meta.data_ptr<int>(), packed.data_ptr(), qo.qp, qo.sp, d, top_k, cap,
                        hidden.numel() / d, stream());
@@ -265,7 +266,7 @@ Tensor combine_fwd(const Tensor& y, const Tensor& dest, const OptTensor& gates, 
     const int top_k = gates.has_value() ? gates->size(1) : static_cast<int>(top_k_if_no_gates);
     GM_CHECK(top_k >= 1 && dest.numel() % top_k == 0, "combine_fwd: slots must be a multiple of top_k");
     const int tokens = dest.numel() / top_k, d = y.size(-1);
-    Tensor out = torch::empty({tokens, d}, y.options());
+    Tensor out = gm::out_empty({tokens, d}, y.options());
     launch_combine_fwd(y.data_ptr(), dest.data_ptr<int>(), fptr(gates), out.data_ptr(), tokens, d, top_k, y.numel() / d, stream());
     return out;
 }
@@ -275,8 +276,8 @@ std::vector<Tensor> combine_bwd(const Tensor& dout, const Tensor& y, const Tenso
     check_bf16(dout, "dout");
     check_bf16(y, "y");
     const int top_k = gates.size(1), d = y.size(-1), cap = src_of_row.numel();
-    Tensor dy = torch::empty_like(y);
-    Tensor dgates = torch::empty_like(gates);                     // every (token, slot) has exactly one live row that writes it
+    Tensor dy = gm::out_empty_like(y);
+    Tensor dgates = gm::out_empty_like(gates);                     // every (token, slot) has exactly one live row that writes it
     QuantOut qo = alloc_quant(quantize, cap, d, y);
     launch_combine_bwd(dout.data_ptr(), y.data_ptr(), src_of_row.data_ptr<int>(), gates.data_ptr<float>(), meta.data_ptr<int>(),
                        dy.data_ptr(), dgates.data_ptr<float>(), qo.qp, qo.sp, d, top_k, cap, dout.numel() / d, stream());
@@ -303,7 +304,7 @@ std::vector<Tensor> activation_fwd(const Tensor& pre, const std::string& name, c
     GM_CHECK(h % 8 == 0 && pre.is_contiguous(), "activation width must be a multiple of 8 (16-byte vectors) and rows contiguous");
     auto sizes = pre.sizes().vec();
     sizes.back() = h;
-    Tensor act = torch::empty(sizes, pre.options());
+    Tensor act = gm::out_empty(sizes, pre.options());
     GM_CHECK(!quantize || h % 32 == 0, "activation with an MXFP8 copy: width must be a multiple of 32");
     QuantOut qo = alloc_quant(quantize, rows, h, pre);
     launch_activation_fwd(pre.data_ptr(), act.data_ptr(), meta.has_value() ? meta->data_ptr<int>() : nullptr, qo.qp, qo.sp, rows, h, kind, stream());
@@ -318,7 +319,7 @@ std::vector<Tensor> activation_bwd(const Tensor& dact, const Tensor& pre, const 
     const int in_w = pre.size(-1), h = kind == 4 ? in_w / 2 : in_w;
     const int rows = pre.numel() / in_w;
     GM_CHECK(h % 8 == 0 && pre.is_contiguous() && dact.is_contiguous(), "activation width must be a multiple of 8 (16-byte vectors) and rows contiguous");
-    Tensor dpre = torch::empty_like(pre);
+    Tensor dpre = gm::out_empty_like(pre);
     GM_CHECK(!quantize || h % 32 == 0, "activation with an MXFP8 copy: width must be a multiple of 32");
     QuantOut qo = alloc_quant(quantize, rows, in_w, pre);
     launch_activation_bwd(dact.data_ptr(), pre.data_ptr(), dpre.data_ptr(), meta.has_value() ? meta->data_ptr<int>() : nullptr, qo.qp, qo.sp, rows, h, kind, stream());
@@ -333,7 +334,7 @@ Tensor ce_fwd_bwd(Tensor& logits, const Tensor& targets, const Tensor& grad_scal
              "logits must be [rows, vocab] bf16 with a row pitch that is a multiple of 8");
     GM_CHECK(targets.scalar_type() == torch::kInt64 && targets.is_contiguous(), "targets must be contiguous int64");
     const int rows = logits.size(0);
-    Tensor loss = torch::empty({rows}, logits.options().dtype(torch::kFloat32));
+    Tensor loss = gm::out_empty({rows}, logits.options().dtype(torch::kFloat32));
     launch_ce_fwd_bwd(logits.data_ptr(), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), loss.data_ptr<float>(),
                       grad_scale.data_ptr<float>(), rows, logits.size(1), logits.stride(0), ignore_index, write_grad, stream());
     return loss;
@@ -493,8 +494,8 @@ std::vector<Tensor> ep_plan(const Tensor& table, int64_t world, int64_t me, int6
     GM_CHECK(experts % world == 0 && cap_rows % 256 == 0, "ep_plan: experts divisible by the group size, capacity a multiple of 256");
     const int per_rank = experts / world;
     auto opt = table.options().dtype(torch::kInt32);
-    Tensor my_base = torch::empty({experts}, opt), seg = torch::empty({per_rank}, opt), valid = torch::empty({per_rank}, opt);
-    Tensor tiles = torch::zeros({cap_rows / 128}, opt), meta = torch::empty({2}, opt);
+    Tensor my_base = gm::out_empty({experts}, opt), seg = gm::out_empty({per_rank}, opt), valid = gm::out_empty({per_rank}, opt);
+    Tensor tiles = gm::out_zeros({cap_rows / 128}, opt), meta = gm::out_empty({2}, opt);
     GM_CHECK(launch_ep_plan(table.data_ptr<int>(), my_base.data_ptr<int>(), seg.data_ptr<int>(), valid.data_ptr<int>(), tiles.data_ptr<int>(),
                             meta.data_ptr<int>(), world, me, experts, per_rank, cap_rows, status_word(table.device().index()), stream()),
              "ep_plan: at most 16 ranks and 128 experts");
@@ -521,8 +522,8 @@ std::vector<Tensor> ep_dispatch(const Tensor& src, const Tensor& top_idx, const 
     GM_CHECK(src.size(0) * top_k == slots && recv.size(-1) == d, "ep_dispatch: shapes");
     if (gates.has_value()) GM_CHECK(gates->scalar_type() == torch::kFloat32 && gates->is_contiguous() && gates->numel() == slots, "gates must be contiguous fp32");
     if (saved_rows.has_value()) { check_bf16(*saved_rows, "saved_rows"); GM_CHECK(saved_rows->numel() == static_cast<int64_t>(slots) * d, "saved rows shape"); }
-    Tensor route_row = torch::empty({slots}, dest.options());
-    Tensor dgates = saved_rows.has_value() ? torch::empty({slots / top_k, top_k}, src.options().dtype(torch::kFloat32)) : Tensor();
+    Tensor route_row = gm::out_empty({slots}, dest.options());
+    Tensor dgates = saved_rows.has_value() ? gm::out_empty({slots / top_k, top_k}, src.options().dtype(torch::kFloat32)) : Tensor();
     auto dl = to_deltas(deltas);
     GM_CHECK(launch_ep_dispatch(src.data_ptr(), reinterpret_cast<const long long*>(top_idx.data_ptr<int64_t>()), dest.data_ptr<int>(),
                                 local_seg_ends.data_ptr<int>(), my_base.data_ptr<int>(), gates.has_value() ? gates->data_ptr<float>() : nullptr,
@@ -541,8 +542,8 @@ std::vector<Tensor> ep_combine(const Tensor& ret, const Tensor& top_idx, const T
     check_bf16(ret, "ret");
     const int tokens = top_idx.size(0), top_k = top_idx.size(1), d = ret.size(-1);
     if (gates.has_value()) GM_CHECK(gates->scalar_type() == torch::kFloat32 && gates->is_contiguous(), "gates must be contiguous fp32");
-    Tensor out = torch::empty({tokens, d}, ret.options());
-    Tensor rows = keep ? torch::empty({tokens * top_k, d}, ret.options()) : Tensor();
+    Tensor out = gm::out_empty({tokens, d}, ret.options());
+    Tensor rows = keep ? gm::out_empty({tokens * top_k, d}, ret.options()) : Tensor();
     auto dl = to_deltas(deltas);
     GM_CHECK(launch_ep_combine(ret.data_ptr(), reinterpret_cast<const long long*>(top_idx.data_ptr<int64_t>()), route_row.data_ptr<int>(),
                                gates.has_value() ? gates->data_ptr<float>() : nullptr, out.data_ptr(), keep ? rows.data_ptr() : nullptr, dl.data(),
@@ -558,6 +559,9 @@ int64_t read_bounds_status() {
         if (v != 0) return v;
     return 0;
 }
+// bounds-checked build with GM_CANARIES=1: guard bytes around the bindings' allocations that were overwritten since the last call
+int64_t verify_guards() { return verify_output_guards(); }
+bool guards_enabled() { return output_guards_enabled(); }
 bool bounds_checked() {
 #ifdef GM_CHECK_BOUNDS
     return true;
@@ -588,6 +592,8 @@ void register_kernels(pybind11::module_& m) {
     m.def("combine_fwd", &combine_fwd, py::arg("y"), py::arg("dest"), py::arg("gates"), py::arg("top_k_if_no_gates") = 1);
     m.def("read_bounds_status", &read_bounds_status);
     m.def("bounds_checked", &bounds_checked);
+    m.def("verify_output_guards", &verify_guards);
+    m.def("output_guards_enabled", &guards_enabled);
     m.def("combine_bwd", &combine_bwd, py::arg("dout"), py::arg("y"), py::arg("src_of_row"), py::arg("gates"), py::arg("meta"), py::arg("quantize") = false);
     m.def("activation_fwd", &activation_fwd, py::arg("pre"), py::arg("name"), py::arg("meta") = py::none(), py::arg("quantize") = false);
     m.def("activation_bwd", &activation_bwd, py::arg("dact"), py::arg("pre"), py::arg("name"), py::arg("meta") = py::none(), py::arg("quantize") = false);

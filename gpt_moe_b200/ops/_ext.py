@@ -23,5 +23,32 @@ def load():
         builder.build()
     import torch  # noqa: F401  (libtorch must be loaded before the extension)
     # GM_CHECK_BOUNDS=1 selects the bounds-checked build of the same sources (`_C_checked.so`)
-    _ext = importlib.import_module("gpt_moe_b200." + os.path.splitext(os.path.basename(builder.TARGET))[0])
+    module = importlib.import_module("gpt_moe_b200." + os.path.splitext(os.path.basename(builder.TARGET))[0])
+    if module.bounds_checked() and module.output_guards_enabled():
+        module = _SynchronisingProxy(module)
+    _ext = module
     return _ext
+
+
+class _SynchronisingProxy:
+    """Debugging aid of the bounds-checked build with GM_CANARIES=1: every call into the extension is followed by a device
+    synchronisation, so an asynchronous launch or execution error is raised by the call that caused it rather than by a later one."""
+
+    def __init__(self, module):
+        self._module = module
+
+    def __getattr__(self, name):
+        attr = getattr(self._module, name)
+        if not callable(attr) or name in ("read_status", "reset_status", "bounds_checked", "output_guards_enabled", "verify_output_guards",
+                                          "read_bounds_status", "status_word_tensor"):
+            return attr
+
+        def call(*args, **kwargs):
+            import torch
+            result = attr(*args, **kwargs)
+            if torch.cuda.is_available() and not torch.cuda.is_current_stream_capturing():
+                torch.cuda.synchronize()
+            return result
+
+        call.__name__ = name
+        return call

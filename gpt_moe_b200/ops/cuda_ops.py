@@ -91,6 +91,9 @@ def check_status() -> None:
         code = ext().read_bounds_status()
         if code != 0:
             raise RuntimeError(f"bounds-checked build: a kernel skipped an out-of-range index (code {code})")
+        changed = ext().verify_output_guards()      # GM_CANARIES=1: guard bytes around the bindings' allocations
+        if changed != 0:
+            raise RuntimeError(f"bounds-checked build: {changed} guard bytes around an output or scratch buffer were overwritten")
 
 
 _status_host: dict = {}

@@ -687,3 +687,24 @@ def test_mma_issue_bench_reports_device_clocks(ops):
     ops.check_status()
     assert 0 < issue256 <= done256 and 0 < issue64 <= done64
     assert done64 < done256 < 8 * done64
+
+
+def test_output_guards_report_a_write_past_an_output(ops):
+    """Bounds-checked build with GM_CANARIES=1: the bindings' allocations carry 256 guard bytes on either side.  A byte past the
+    payload is changed here from the host side (a torch write into the underlying storage, standing in for a kernel that stored
+    one element too far) and the status check reports it; a clean call afterwards reports nothing."""
+    c = ops.ext()
+    if not (c.bounds_checked() and c.output_guards_enabled()):
+        pytest.skip("guard bytes exist only in the bounds-checked build with GM_CANARIES=1")
+    ops.check_status()                                     # forget what earlier tests allocated
+    x = torch.randn(256, 128, device="cuda").bfloat16()
+    q, sf = c.mxfp8_quantize(x)
+    assert q.storage_offset() == 256
+    raw = torch.empty(0, dtype=torch.uint8, device="cuda").set_(q.untyped_storage())
+    assert int(raw[255]) == 0xA5 and int(raw[256 + q.numel()]) == 0xA5
+    raw[256 + q.numel()] = 0
+    with pytest.raises(RuntimeError, match="guard bytes"):
+        ops.check_status()
+    q2, _ = c.mxfp8_quantize(x)
+    ops.check_status()
+    assert torch.equal(q, q2)
