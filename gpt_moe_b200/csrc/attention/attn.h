@@ -12,7 +12,8 @@ struct AttnParams {
     int qk_dim;                     // width of a query / key head: 64 or 128
     int q_col0, k_col0, v_col0;     // first column of head 0 inside each tensor map
     int window;                     // inclusive look-back W (a query sees keys q-W..q); >= seq_len means plain causal
-    const int* window_ptr;          // optional device-resident window (overrides `window`)
+    const int* window_ptr;          // optional device-resident window (overrides `window`; clamped to [0, seq_len] by the kernels), so
+                                    // that a window-schedule step is a write to that word and a captured launch stays valid
     const int* doc_start;           // optional [batch * seq]: position (inside its sequence) of the first token of each token's document;
                                     // a query then sees keys max(q - W, doc_start[q]) .. q (documents are contiguous runs of tokens)
     float scale_log2e;              // softmax scale * log2(e)

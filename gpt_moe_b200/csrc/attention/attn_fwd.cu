@@ -124,7 +124,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q_tile = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
     const int q0 = q_tile * AT_BM;
-    const int window = p.window_ptr ? *p.window_ptr : p.window;
+    const int window = p.window_ptr ? min(max(*p.window_ptr, 0), p.seq_len) : p.window;
     const int row0 = batch * p.seq_len;
     // document masking narrows a row's look-back to the start of its document; look-backs shrink monotonically towards
     // later rows of a document, so the first row bounds the tiles to visit and the last row decides whether a tile needs masking

@@ -205,7 +205,7 @@ attn_fwd_dual_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y, batch = blockIdx.z;
     const int q0 = blockIdx.x * 2 * DU_BM;
-    const int window = p.window_ptr ? *p.window_ptr : p.window;
+    const int window = p.window_ptr ? min(max(*p.window_ptr, 0), p.seq_len) : p.window;
     const int row0 = batch * p.seq_len;
     // key tiles (units of 128 keys) of each query tile: from the tile holding the first key its first row sees to its diagonal tile
     const int first_a = q0 - window, first_b = q0 + DU_BM - window;

@@ -266,10 +266,21 @@ const int* doc_start_ptr(const c10::optional<torch::Tensor>& doc_start, int64_t 
     return doc_start->data_ptr<int>();
 }
 
+// `window_tensor`: optional 0-dim (or 1-element) int32 CUDA tensor holding the look-back; the kernels read it on the device, so the same
+// (captured) launch follows a window schedule without a new host value (the reference's device-resident window,
+// experiments/046-fa4-device-window.patch).
+const int* window_word(const c10::optional<torch::Tensor>& window_tensor) {
+    if (!window_tensor.has_value()) return nullptr;
+    GM_CHECK(window_tensor->is_cuda() && window_tensor->scalar_type() == torch::kInt32 && window_tensor->numel() == 1,
+             "window_tensor must be a one-element int32 CUDA tensor");
+    return window_tensor->data_ptr<int>();
+}
+
 // `quantize`: also return the MXFP8 copy of out (payload uint8 [B*T, H*64], scale records), written by the kernel's epilogue.
 // `single_tile`: keep the call on the kernel with one query tile per CTA (the other kernel is checked against it).
 std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, int64_t window, double scale,
-                                    double softcap, const c10::optional<torch::Tensor>& doc_start, bool quantize, bool single_tile) {
+                                    double softcap, const c10::optional<torch::Tensor>& doc_start, bool quantize, bool single_tile,
+                                    const c10::optional<torch::Tensor>& window_tensor) {
     c10::cuda::CUDAGuard guard(q.device());
     const int B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
     GM_CHECK((D == 64 || D == 128) && k.size(3) == D && v.size(3) == 64 && T % 128 == 0 && H % Hkv == 0,
@@ -295,6 +306,7 @@ std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor&
     }
     p.status = status_tensor(q.device().index()).data_ptr<int>();
     p.single_tile = single_tile ? 1 : 0;
+    p.window_ptr = window_word(window_tensor);
     cudaError_t e = gm::launch_attn_fwd(head_map(q, 128), head_map(k, 128), head_map(v, 128), p, current_stream());
     GM_CHECK(e == cudaSuccess, cudaGetErrorString(e));
     if (quantize) return {out, lse, oq, osf};
@@ -306,7 +318,8 @@ std::vector<torch::Tensor> attn_fwd(const torch::Tensor& q, const torch::Tensor&
 // (they may be column slices of a packed gradient buffer).  Returns dq as fp32 [B,T,H,64].
 torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, const torch::Tensor& out,
                        const torch::Tensor& d_out, const torch::Tensor& lse, torch::Tensor& dk, torch::Tensor& dv, int64_t window,
-                       double scale, double softcap, const c10::optional<torch::Tensor>& doc_start, bool unpipelined) {
+                       double scale, double softcap, const c10::optional<torch::Tensor>& doc_start, bool unpipelined,
+                       const c10::optional<torch::Tensor>& window_tensor) {
     c10::cuda::CUDAGuard guard(q.device());
     const int B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
     GM_CHECK((D == 64 || D == 128) && k.size(3) == D && v.size(3) == 64 && T % 128 == 0 && H % Hkv == 0,
@@ -330,6 +343,7 @@ torch::Tensor attn_bwd(const torch::Tensor& q, const torch::Tensor& k, const tor
     p.dk = dk.data_ptr(); p.dv = dv.data_ptr(); p.dkv_stride = dk.stride(1); p.dv_stride = dv.stride(1);
     p.status = status_tensor(q.device().index()).data_ptr<int>();
     p.single_tile = unpipelined ? 1 : 0;
+    p.window_ptr = window_word(window_tensor);
     const CUtensorMap& tdq = cached_map(dq.data_ptr(), 4, static_cast<uint64_t>(H) * D, static_cast<uint64_t>(B) * T, 1,
                                         static_cast<uint64_t>(H) * D * 4, 0, 32, 128, 128);
     cudaError_t e = gm::launch_attn_bwd(head_map(q, 128), head_map(k, 128), head_map(v, 128), head_map(d_out, 128), tdq, p,
@@ -359,9 +373,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_mxfp8", &gemm_mxfp8, py::arg("a"), py::arg("sfa"), py::arg("b"), py::arg("sfb"), py::arg("d"), py::arg("alpha") = 1.0,
           py::arg("tile_expert") = py::none(), py::arg("num_m_tiles") = py::none());
     m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0,
-          py::arg("doc_start") = py::none(), py::arg("quantize") = false, py::arg("single_tile") = false);
+          py::arg("doc_start") = py::none(), py::arg("quantize") = false, py::arg("single_tile") = false, py::arg("window_tensor") = py::none());
     m.def("attn_bwd", &attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("d_out"), py::arg("lse"), py::arg("dk"),
           py::arg("dv"), py::arg("window"), py::arg("scale"), py::arg("softcap") = 0.0, py::arg("doc_start") = py::none(),
-          py::arg("unpipelined") = false);
+          py::arg("unpipelined") = false, py::arg("window_tensor") = py::none());
     gm::register_kernels(m);
 }

@@ -708,3 +708,29 @@ def test_output_guards_report_a_write_past_an_output(ops):
     q2, _ = c.mxfp8_quantize(x)
     ops.check_status()
     assert torch.equal(q, q2)
+
+
+def test_attention_reads_a_device_resident_window(ops):
+    """The look-back may live in a one-element int32 tensor that the kernels read on the device: the same call then follows a
+    window schedule (a `fill_`) without a new host argument.  Forward and backward, both kernels of each direction."""
+    torch.manual_seed(13)
+    b, t, h, d = 2, 1024, 2, 64
+    c = ops.ext()
+    packed = torch.randn(b, t, 3 * h * d, device="cuda").bfloat16()
+    q, k, v = ops.split_qkv(packed, h, h, d)
+    word = torch.zeros((), dtype=torch.int32, device="cuda")
+    for window in (200, 640, 5000):
+        word.fill_(window)
+        for basic in (False, True):
+            want, want_lse = c.attn_fwd(q, k, v, min(window, t), d ** -0.5, 0.0, None, False, basic)
+            got, got_lse = c.attn_fwd(q, k, v, t, d ** -0.5, 0.0, None, False, basic, word)      # the host value is ignored
+            assert torch.equal(got, want) and torch.equal(got_lse, want_lse)
+            g = torch.randn_like(want)
+            grads = []
+            for kwargs in ({}, {"window_tensor": word}):
+                dk, dv = torch.empty_like(k), torch.empty_like(v)
+                dq = c.attn_bwd(q, k, v, want, g, want_lse, dk, dv, min(window, t) if not kwargs else t, d ** -0.5, 0.0, None, basic, **kwargs)
+                grads.append((dq, dk.clone(), dv.clone()))
+            for a_, b_ in zip(grads[0], grads[1]):
+                assert rel(a_, b_) < 2e-3
+    ops.check_status()
