@@ -22,7 +22,6 @@ import argparse
 import json
 import os
 import subprocess
-import sys
 import threading
 import time
 
@@ -85,7 +84,6 @@ MODEL_NAMES = {
 
 def run_ours(args) -> dict:
     import torch
-    import torch.distributed as dist
     from gpt_moe_b200.config import apply_overrides, get_preset
     from gpt_moe_b200.ops import cuda_ops
     from gpt_moe_b200.parallel import dist_utils as du

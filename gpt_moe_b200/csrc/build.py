@@ -12,7 +12,6 @@ from __future__ import annotations
 import hashlib
 import os
 import subprocess
-import sys
 import sysconfig
 from concurrent.futures import ThreadPoolExecutor
 

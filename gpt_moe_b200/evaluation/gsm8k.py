@@ -10,7 +10,6 @@ Data: the `datasets` hub, or `$GSM8K_DIR/{train,test}.jsonl` with keys question 
 from __future__ import annotations
 
 import json
-import math
 import os
 import re
 from decimal import Decimal

@@ -14,12 +14,10 @@ from __future__ import annotations
 
 from typing import Optional, Tuple
 
-import torch
 import torch.nn as nn
 from torch import Tensor
 
 from ..ops import api
-from ..ops import reference as ref
 from .linear import Linear
 from .mlp import MLP
 

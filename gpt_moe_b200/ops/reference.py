@@ -6,7 +6,6 @@ not speed, and use only differentiable torch operations so their gradients come 
 """
 from __future__ import annotations
 
-import math
 from typing import Optional, Tuple
 
 import torch

@@ -19,7 +19,7 @@ collectives and works on CPU/gloo and on CUDA/NCCL — it is the measured NCCL b
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Sequence, Tuple
 
 import torch
 import torch.distributed as dist

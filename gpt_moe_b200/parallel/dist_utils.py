@@ -3,7 +3,6 @@ from __future__ import annotations
 
 import datetime
 import os
-from typing import Optional
 
 import torch
 import torch.distributed as dist

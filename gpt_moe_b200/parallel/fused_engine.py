@@ -42,7 +42,7 @@ import torch.nn as nn
 from torch import Tensor
 
 from . import dist_utils as du
-from .ddp_engine import HostEngine, assign_owners, polar_cost, _to_cpu
+from .ddp_engine import HostEngine, assign_owners, polar_cost
 
 
 class CudaHostEngine(HostEngine):

@@ -2,7 +2,7 @@ import math
 
 import pytest
 
-from gpt_moe_b200.config import GPTConfig, TrainingConfig, apply_overrides, build_resume_config, get_preset
+from gpt_moe_b200.config import TrainingConfig, apply_overrides, build_resume_config, get_preset
 from gpt_moe_b200.schedules import token as sched
 
 

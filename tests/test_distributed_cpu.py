@@ -1,6 +1,5 @@
 """Multi-process CPU tests (gloo, world size 2): data-parallel, sharded-optimizer, expert-parallel and pipeline
 plumbing must reproduce the single-process result."""
-import copy
 
 import pytest
 import torch
@@ -57,7 +56,6 @@ def _single(model_kw, train_kw, steps, world):
     model = GPT(gc, tc)
     opts = model.configure_optimizers(tc.adamw_max_lr, tc.adamw_betas, tc.adamw_eps, tc.adamw_weight_decay, "cpu")
     rows = tc.gpu_batch_size_train
-    from gpt_moe_b200.schedules.token import get_token_based_adamw_lr
     losses, tokens = [], 0
     for ids in _batches(steps, rows * world, tc.seq_len_train, gc.vocab_size):
         step_losses = []

@@ -12,8 +12,6 @@ os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 
 import argparse
 
-import torch
-
 from gpt_moe_b200.config import apply_overrides, get_preset
 from gpt_moe_b200.runtime.trainer import Trainer
 
