@@ -47,8 +47,9 @@ class AsyncQueue:
         return False
 
 
-def run(roles, queues, rng, limit=200000):
-    """Random interleaving of the role generators; each yields (barrier, parity) to wait or None to be rescheduled."""
+def run(roles, queues, rng, limit=400000, starved=None, starve=0.0):
+    """Random interleaving of the role generators; each yields (barrier, parity) to wait or None to be rescheduled.
+    `starved`: a role that is skipped with probability `starve` each round (a thread that is slow to notice its barrier)."""
     waiting = {name: None for name in roles}
     live = dict(roles)
     for _ in range(limit):
@@ -59,6 +60,8 @@ def run(roles, queues, rng, limit=200000):
         names = list(live)
         rng.shuffle(names)
         for name in names:
+            if name == starved and rng.random() < starve:
+                continue
             cond = waiting[name]
             if cond is not None and not cond[0].done(cond[1]):
                 continue
@@ -73,7 +76,7 @@ def run(roles, queues, rng, limit=200000):
 
 # ---- forward: two query tiles per CTA -------------------------------------------------------------------------------------------
 
-def forward_dual(q0, window, seq_len, rng, max_delay, stages=4):
+def forward_dual(q0, window, seq_len, rng, max_delay, stages=4, starved=None):
     tile = 128
     first_a, first_b = q0 - window, q0 + tile - window
     lo_a, lo_b = (first_a // tile if first_a > 0 else 0), (first_b // tile if first_b > 0 else 0)
@@ -160,7 +163,7 @@ def forward_dual(q0, window, seq_len, rng, max_delay, stages=4):
         finished.append(f"softmax{x}")
 
     roles = {"loader": loader(), "issuer0": issuer(0), "issuer1": issuer(1), "softmax0": softmax(0), "softmax1": softmax(1)}
-    run(roles, [tma] + mma, rng)
+    run(roles, [tma] + mma, rng, starved=starved, starve=0.95)
     assert len(finished) == 5
 
 
@@ -186,7 +189,7 @@ def test_forward_model_notices_a_ring_that_is_too_shallow():
 
 # ---- backward: score products of the next query tile ahead of the gradient products ------------------------------------------------
 
-def backward_pipe(n_iter, rng, max_delay, stages=3):
+def backward_pipe(n_iter, rng, max_delay, stages=3, starved=None):
     bar_kv, bar_sdp, bar_sread, bar_pds, bar_mma = Barrier(1), Barrier(1), Barrier(1), Barrier(1), Barrier(1)   # 256-thread barriers as one
     bar_qdo = [Barrier(1) for _ in range(stages)]
     tma, mma_s, mma_g = AsyncQueue(rng, max_delay), AsyncQueue(rng, max_delay), AsyncQueue(rng, max_delay)
@@ -282,7 +285,7 @@ def backward_pipe(n_iter, rng, max_delay, stages=3):
         finished.append("softmax")
 
     roles = {"loader": loader(), "score_issuer": score_issuer(), "gradient_issuer": gradient_issuer(), "softmax": softmax()}
-    run(roles, [tma, mma_s, mma_g], rng)
+    run(roles, [tma, mma_s, mma_g], rng, starved=starved, starve=0.95)
     assert len(finished) == 4 and drained == list(range(n_iter))
 
 
@@ -292,3 +295,19 @@ def test_pipelined_backward_never_stalls_and_never_reuses_a_live_buffer(n_iter, 
     rng = random.Random(n_iter * 17 + max_delay)
     for _ in range(5):
         backward_pipe(n_iter, rng, max_delay)
+
+
+@pytest.mark.parametrize("starved", ["loader", "issuer0", "issuer1", "softmax0", "softmax1"])
+def test_forward_protocol_survives_a_role_that_lags_far_behind(starved):
+    """A role that notices its barriers late (so that a barrier it waits on may have moved on by more than one phase where the
+    protocol allows that) only delays the others; parity tests never mistake a later phase for an earlier one."""
+    rng = random.Random(sum(map(ord, starved)))
+    for q0 in (0, 256, 1280, 1792):
+        forward_dual(q0, 1024, 2048, rng, 5, starved=starved)
+
+
+@pytest.mark.parametrize("starved", ["loader", "score_issuer", "gradient_issuer", "softmax"])
+def test_backward_protocol_survives_a_role_that_lags_far_behind(starved):
+    rng = random.Random(sum(map(ord, starved)))
+    for n_iter in (1, 3, 4, 9, 18):
+        backward_pipe(n_iter, rng, 5, starved=starved)
